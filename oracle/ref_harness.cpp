@@ -1,0 +1,99 @@
+/*
+ * Drives the reference's own MoELayer (CPU arm) behind the same C signature as
+ * moe_oracle_run, so the restatement in moe_oracle.c can be checked against
+ * the real thing and golden vectors can be produced from it.
+ *
+ * TEST INFRASTRUCTURE ONLY. Compiled by oracle/Makefile together with the
+ * reference's sources (read where they lie; none are copied) into
+ * oracle/_ref/libmgpt_ref.so.  This file holds no reference code: it only
+ * calls the layer's public interface (layers/MoELayer.h:37-50) and reads the
+ * tensors the layer caches for its backward pass (layers/MoELayer.h:17-33).
+ */
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <iostream>
+#include <stdexcept>
+#include <vector>
+
+/* The cached routing tensors are private members; open them for this one
+ * translation unit (standard headers are already included above). */
+#define private public
+#include "MoELayer.h"
+#undef private
+
+#include "moe_oracle.h"
+
+namespace {
+
+void copy_as_int(const Tensor& t, int32_t* dst, size_t n)
+{
+    for (size_t i = 0; i < n; ++i) dst[i] = (int32_t)t.data[i];
+}
+
+int run(const moe_oracle_dims* d, const moe_oracle_inputs* in, moe_oracle_outputs* out, bool backward)
+{
+    const int N = d->n_tokens, C = d->C, H = d->H, E = d->E, k = d->k;
+    MoELayer layer(C, H, E, k);
+    std::vector<Tensor*> params = layer.get_parameters();
+    if ((int)params.size() != 2 + 6 * E) return 2;
+    for (size_t i = 0; i < params.size(); ++i) {
+        std::memcpy(params[i]->data.data(), in->params[i], params[i]->size() * sizeof(float));
+        params[i]->zero_grad();
+    }
+    /* One batch row of N tokens: the layer only uses B*T (MoELayer.cpp:30). */
+    Tensor x({1, N, C}, 0.0f, Device::CPU);
+    std::memcpy(x.data.data(), in->x, (size_t)N * C * sizeof(float));
+    Tensor y = layer.forward(x);
+
+    const size_t NE = (size_t)N * E, R = (size_t)N * k;
+    if (out->logits) std::memcpy(out->logits, layer.cached_router_logits.data.data(), NE * sizeof(float));
+    if (out->probs) std::memcpy(out->probs, layer.cached_router_probs.data.data(), NE * sizeof(float));
+    if (out->top_idx) copy_as_int(layer.cached_top_indices, out->top_idx, R);
+    if (out->top_p) std::memcpy(out->top_p, layer.cached_top_probs.data.data(), R * sizeof(float));
+    if (out->counts)
+        for (int e = 0; e < E; ++e) out->counts[e] = (int32_t)layer.get_expert_counts()[e];
+    if (out->offsets)
+        for (int e = 0; e < E; ++e) out->offsets[e] = (int32_t)layer.cached_cpu_offsets[e];
+    if (out->map) copy_as_int(layer.cached_sorted_token_ids, out->map, R);
+    if (out->gathered_out)
+        std::memcpy(out->gathered_out, layer.cached_gathered_outputs.data.data(), R * C * sizeof(float));
+    if (out->y) std::memcpy(out->y, y.data.data(), (size_t)N * C * sizeof(float));
+
+    if (backward && in->dy) {
+        Tensor dy({1, N, C}, 0.0f, Device::CPU);
+        std::memcpy(dy.data.data(), in->dy, (size_t)N * C * sizeof(float));
+        Tensor dx = layer.backward(dy);
+        if (out->dx) std::memcpy(out->dx, dx.data.data(), (size_t)N * C * sizeof(float));
+        if (out->grads)
+            for (size_t i = 0; i < params.size(); ++i)
+                if (out->grads[i])
+                    for (size_t j = 0; j < params[i]->size(); ++j) out->grads[i][j] += params[i]->grad[j];
+        /* d_top_p and dlogits are locals of MoELayer::backward_into and cannot be read. */
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int moe_ref_run(const moe_oracle_dims* d, const moe_oracle_inputs* in,
+                           moe_oracle_outputs* out, int /*n_threads*/)
+{
+    try {
+        return run(d, in, out, true);
+    } catch (const std::exception& e) {
+        std::cerr << "moe_ref_run: " << e.what() << std::endl;
+        return 1;
+    }
+}
+
+extern "C" int moe_ref_route(const moe_oracle_dims* d, const moe_oracle_inputs* in,
+                             moe_oracle_outputs* out, int /*n_threads*/)
+{
+    try {
+        return run(d, in, out, false);
+    } catch (const std::exception& e) {
+        std::cerr << "moe_ref_route: " << e.what() << std::endl;
+        return 1;
+    }
+}

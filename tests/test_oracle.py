@@ -1,0 +1,91 @@
+"""The CPU oracle against the reference's golden vectors (and, where the
+reference build exists, against the reference itself, live)."""
+import numpy as np
+import pytest
+
+from mgpt_b200 import synth
+from oracle import oracle
+from tests.golden import make_golden as G
+
+
+def _dims(w):
+    return oracle.Dims(w.n_tokens, w.C, w.H, w.E, w.k, w.alpha)
+
+
+def _assert_same(got, want, keys=None):
+    for key, ref in want.items():
+        if keys is not None and key not in keys:
+            continue
+        if key == "grads":
+            for i, (a, b) in enumerate(zip(got["grads"], ref)):
+                assert np.array_equal(a.reshape(-1), b.reshape(-1)), f"grad {i}"
+        elif key in got:
+            assert np.array_equal(got[key], ref), key
+
+
+@pytest.mark.parametrize("name", sorted(G.CASES))
+def test_oracle_matches_reference_golden(name):
+    w, x, params, dy = G.build_case(name)
+    gold = G.load_golden(name)
+    assert bytes(gold.pop("input_sha256")).decode() == G.input_digest(x, params, dy), \
+        "seeded inputs drifted from the ones the golden file was made with"
+    gold.pop("n_grads")
+    got = oracle.run(_dims(w), x, params, dy, threads=2)
+    _assert_same(got, gold)
+
+
+@pytest.mark.parametrize("name", ["tiny", "e64k4"])
+def test_route_only_equals_full(name):
+    w, x, params, dy = G.build_case(name)
+    full = oracle.run(_dims(w), x, params, dy)
+    route = oracle.run(_dims(w), x, params, route_only=True)
+    _assert_same(route, {k: full[k] for k in ("logits", "probs", "top_idx", "top_p", "counts", "offsets", "map")})
+
+
+def test_threads_do_not_change_results():
+    w, x, params, dy = G.build_case("mid")
+    a = oracle.run(_dims(w), x, params, dy, threads=1)
+    b = oracle.run(_dims(w), x, params, dy, threads=5)
+    _assert_same(a, b)
+
+
+def test_known_answers_ties_and_floor():
+    # equal probabilities keep the lowest expert index first (utils/Tensor.cpp:1319-1329)
+    w, x, params, dy = G.build_case("ties")
+    r = oracle.run(_dims(w), x, params, route_only=True)
+    p = r["probs"]
+    assert np.array_equal(p[:, 1], p[:, 2]) and np.array_equal(p[:, 1], p[:, 4])
+    for t in range(w.n_tokens):
+        sel = list(r["top_idx"][t])
+        tied = [e for e in sel if e in (1, 2, 4)]
+        assert tied == sorted(tied) and tied == [1, 2, 4][:len(tied)]
+    # the clamp floor is exactly 1e-7 and ties there resolve to the lowest index
+    w, x, params, dy = G.build_case("floor")
+    r = oracle.run(_dims(w), x, params, route_only=True)
+    assert np.all(r["probs"][:, [1, 2, 4, 5, 6, 7]] == np.float32(1e-7))
+    assert np.all(r["top_idx"][:, 2:] == np.array([1, 2]))
+    assert r["counts"].tolist() == [16, 16, 16, 16, 0, 0, 0, 0]
+
+
+def test_plan_invariants():
+    w, x, params, dy = G.build_case("e64k4")
+    r = oracle.run(_dims(w), x, params, route_only=True)
+    R = w.n_tokens * w.k
+    assert r["counts"].sum() == R
+    assert np.array_equal(r["offsets"], np.concatenate([[0], np.cumsum(r["counts"])[:-1]]))
+    assert sorted(r["map"].tolist()) == list(range(R))
+    flat_e = r["top_idx"].reshape(-1)
+    for e in range(w.E):
+        seg = r["map"][r["offsets"][e]: r["offsets"][e] + r["counts"][e]]
+        assert np.all(flat_e[seg] == e) and np.all(np.diff(seg) > 0)   # stable within an expert
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference build (oracle/_ref) not present")
+@pytest.mark.parametrize("shape", [(64, 32, 48, 8, 2), (37, 24, 40, 5, 3), (128, 64, 96, 16, 4)])
+def test_oracle_matches_reference_live(shape):
+    n, C, H, E, k = shape
+    w = synth.Workload("live", n, C, H, E, k, "fp32")
+    x, params, dy = synth.make_inputs(w, seed=99, bias_std=0.1)
+    a = oracle.run(_dims(w), x, params, dy, threads=2)
+    b = oracle.run(_dims(w), x, params, dy, which="ref")
+    _assert_same(a, b)
