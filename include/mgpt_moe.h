@@ -1,0 +1,153 @@
+/*
+ * mgpt_moe.h -- C ABI of the B200 (sm_100a) Mixture-of-Experts layer.
+ *
+ * The library replaces the body of the reference's MoELayer
+ * (src/main/neuralnetwork/layers/MoELayer.{h,cpp}) and, below it, the
+ * cuda_ops MoE kernels (src/main/utils/cuda_ops.h:52-62, 29, 36-37, 95-96).
+ * The reference engine keeps owning parameters (FP32 Tensor data/grad),
+ * the Scratchpad arena and the optimiser; this ABI only sees raw device
+ * pointers, sizes and a stream.
+ *
+ * Conventions
+ *   - every function returns 0 on success, a MGPT_MOE_E* code otherwise;
+ *     mgpt_moe_last_error() returns the message of the calling thread's
+ *     last failure;
+ *   - all work is enqueued on the stream passed in (0 = the legacy default
+ *     stream the reference uses everywhere) and nothing synchronises unless
+ *     the comment says so;
+ *   - token tensors are row-major [n_tokens, embed_dim] (the reference's
+ *     [B,T,C] flattened, MoELayer.cpp:30);
+ *   - parameter order is the reference's get_parameters() order
+ *     (MoELayer.cpp:225-236): Wr[C,E], br[E], then per expert
+ *     Wg[C,H], bg[H], Wu[C,H], bu[H], Wd[H,C], bd[C]  (2+6E tensors).
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point fails with MGPT_MOE_ECUDA.
+ */
+#ifndef MGPT_MOE_H
+#define MGPT_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MGPT_MOE_OK       0
+#define MGPT_MOE_EINVAL   1   /* bad argument / unsupported shape            */
+#define MGPT_MOE_ECUDA    2   /* a CUDA runtime or driver call failed         */
+#define MGPT_MOE_ESTATE   3   /* call order (e.g. backward before forward)    */
+#define MGPT_MOE_ENOMEM   4   /* workspace too small                          */
+
+/* arithmetic modes */
+#define MGPT_MOE_FP32     0   /* FP32 SIMT validation mode (reference dtype)  */
+#define MGPT_MOE_BF16     1   /* BF16 operands, FP32 accumulate, tcgen05/TMEM */
+
+/* element type of x / y / dy / dx at the boundary */
+#define MGPT_MOE_IO_F32   0
+#define MGPT_MOE_IO_BF16  1
+
+typedef struct mgpt_moe_layer mgpt_moe_layer;   /* opaque */
+typedef void* mgpt_stream_t;                    /* cudaStream_t */
+
+/* Mirrors MoELayer(int embed_dim, int hidden_dim, int num_experts, int top_k)
+ * (MoELayer.h:37); hidden_dim -1 means 4*embed_dim (SwiGLU.cpp:4-8).
+ * lb_alpha is the literal 0.01f at MoELayer.cpp:194. */
+typedef struct {
+    int   embed_dim;
+    int   hidden_dim;
+    int   num_experts;
+    int   top_k;
+    float lb_alpha;
+    int   mode;        /* MGPT_MOE_FP32 | MGPT_MOE_BF16                       */
+    int   device;      /* CUDA device ordinal                                 */
+    int   gemm_impl;   /* 0 = default for the mode, 1 = force SIMT products   */
+} mgpt_moe_config;
+
+/* Replaces the MoELayer constructor (MoELayer.cpp:4-12). Allocates only the
+ * layer's own BF16 weight shadows and small tables; parameters stay with the
+ * caller. */
+int  mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out);
+void mgpt_moe_destroy(mgpt_moe_layer* layer);
+const char* mgpt_moe_last_error(void);
+
+/* get_parameters() (MoELayer.cpp:225-236): number of tensors and their shapes. */
+int  mgpt_moe_num_params(const mgpt_moe_layer* layer);
+int  mgpt_moe_param_shape(const mgpt_moe_layer* layer, int index, int* rows, int* cols);
+
+/* Hands the layer the engine-owned FP32 device buffers: data[i] is
+ * Tensor::cuda_data and grad[i] Tensor::cuda_grad of get_parameters()[i]
+ * (Tensor.h:22-23). grad may be NULL for inference. Gradients are
+ * accumulated (+=) like Tensor::add_grad (Tensor.cpp:638-650). */
+int  mgpt_moe_bind_params(mgpt_moe_layer* layer, float* const* data, float* const* grad, int n);
+
+/* Rebuilds the BF16 shadows from the FP32 masters. Call after binding and
+ * after every optimiser step or checkpoint load (no-op in FP32 mode). */
+int  mgpt_moe_sync_weights(mgpt_moe_layer* layer, mgpt_stream_t stream);
+
+/* get_footprint() (MoELayer.cpp:238-251): bytes of arena the layer needs for
+ * n_tokens (forward activations kept for backward + backward temporaries). */
+size_t mgpt_moe_workspace_bytes(const mgpt_moe_layer* layer, int n_tokens);
+
+/* forward_into() (MoELayer.cpp:28-128). x, y: device [n_tokens, C] of io_dtype.
+ * workspace: device memory of at least mgpt_moe_workspace_bytes(n_tokens),
+ * 256-byte aligned (Scratchpad::get_address alignment, Scratchpad.cpp:27-29);
+ * it must stay untouched until the matching backward has run. */
+int  mgpt_moe_forward(mgpt_moe_layer* layer, const void* x, void* y, int n_tokens, int io_dtype,
+                      void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
+/* backward_into() (MoELayer.cpp:135-223). dy, dx: device [n_tokens, C]; x is
+ * the forward input (the reference keeps it as LinearLayer::cached_input,
+ * LinearLayer.cpp:24). Accumulates all 2+6E parameter gradients. */
+int  mgpt_moe_backward(mgpt_moe_layer* layer, const void* x, const void* dy, void* dx, int io_dtype,
+                       void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
+/* get_expert_counts() (MoELayer.h:39): per-expert routed rows of the last
+ * forward, as integers. Synchronises the stream of that forward. */
+int  mgpt_moe_expert_counts(mgpt_moe_layer* layer, int32_t* host_counts);
+
+/* Offset and size of a named buffer inside the workspace for n_tokens, for
+ * tests and for callers that read routing results in place. Names:
+ * logits probs top_idx top_p counts offsets padded_offsets map pos row_src
+ * tile_expert n_tiles Xg G U Hh Yg dYg dG dU dXg d_top_p dlogits status. */
+int  mgpt_moe_workspace_view(const mgpt_moe_layer* layer, int n_tokens, const char* name,
+                             size_t* offset, size_t* bytes);
+
+/* Whole step with HOST buffers: copies x (and dy) to the device, runs forward
+ * (and backward when dy != NULL), copies y (and dx) back and synchronises.
+ * Stands where the reference's caller does Tensor::to(Device::CUDA) /
+ * copy_to_host around the layer (Tensor.h:37-44). The layer keeps its own
+ * device staging buffers, grown on demand. */
+int  mgpt_moe_step_host(mgpt_moe_layer* layer, const void* x_host, const void* dy_host,
+                        void* y_host, void* dx_host, int n_tokens, int io_dtype, mgpt_stream_t stream);
+
+/* Per-stage device timing for benchmarks. When enabled, forward and backward
+ * bracket each stage with CUDA events on the caller's stream;
+ * mgpt_moe_stage_ms synchronises those events and writes the milliseconds of
+ * the LAST forward/backward pair, one float per stage (0 for stages that did
+ * not run). Stage i is named by mgpt_moe_stage_name(i). No reference
+ * counterpart (the reference times whole steps with std::chrono,
+ * pipeline/Trainer.cpp:314-323). */
+#define MGPT_MOE_N_STAGES 12
+int  mgpt_moe_set_profiling(mgpt_moe_layer* layer, int enabled);
+int  mgpt_moe_stage_ms(mgpt_moe_layer* layer, float* ms);
+const char* mgpt_moe_stage_name(int stage);
+
+/* Number of kernels the library launched since the counter was last reset
+ * (host-side count of its own launches; for benchmark bookkeeping). */
+long mgpt_moe_launch_count(int reset);
+
+/* ---- operator level: the cuda_ops seam (cuda_ops.h:52-62), typed ---------
+ * Device pointers; indices are int32 (the reference stores them as floats). */
+
+/* linear + softmax(clamp 1e-7..1) + top_k in one pass
+ * (LinearLayer.cpp:23-28, Tensor.cpp:850-883, cuda_ops.h:53). logits may be NULL. */
+int  mgpt_moe_op_router(const void* x, int io_dtype, const float* Wr, const float* br,
+                        int n_tokens, int C, int E, int k,
+                        float* logits, float* probs, int32_t* top_idx, float* top_p,
+                        mgpt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MGPT_MOE_H */

@@ -1,0 +1,76 @@
+"""ctypes binding of ``libmgpt_moe.so`` (the C ABI in ``include/mgpt_moe.h``)."""
+from __future__ import annotations
+
+import ctypes as ct
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libmgpt_moe.so")
+
+FP32, BF16 = 0, 1
+IO_F32, IO_BF16 = 0, 1
+
+# every symbol include/mgpt_moe.h declares
+SYMBOLS = [
+    "mgpt_moe_create", "mgpt_moe_destroy", "mgpt_moe_last_error", "mgpt_moe_num_params",
+    "mgpt_moe_param_shape", "mgpt_moe_bind_params", "mgpt_moe_sync_weights", "mgpt_moe_workspace_bytes",
+    "mgpt_moe_forward", "mgpt_moe_backward", "mgpt_moe_expert_counts", "mgpt_moe_workspace_view",
+    "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
+    "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name",
+]
+N_STAGES = 12
+
+
+class Config(ct.Structure):
+    _fields_ = [("embed_dim", ct.c_int), ("hidden_dim", ct.c_int), ("num_experts", ct.c_int),
+                ("top_k", ct.c_int), ("lb_alpha", ct.c_float), ("mode", ct.c_int), ("device", ct.c_int),
+                ("gemm_impl", ct.c_int)]
+
+
+class MoeError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load() -> ct.CDLL:
+    """Loads the CUDA library. There is no fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise MoeError(f"{LIB_PATH} is missing: build it with `python -m mgpt_b200.build` "
+                       "(the layer has no CPU or PyTorch fallback)")
+    lib = ct.CDLL(LIB_PATH)
+    vp, i32, sz = ct.c_void_p, ct.c_int, ct.c_size_t
+    lib.mgpt_moe_create.argtypes = [ct.POINTER(Config), ct.POINTER(vp)]
+    lib.mgpt_moe_destroy.argtypes = [vp]
+    lib.mgpt_moe_destroy.restype = None
+    lib.mgpt_moe_last_error.restype = ct.c_char_p
+    lib.mgpt_moe_num_params.argtypes = [vp]
+    lib.mgpt_moe_param_shape.argtypes = [vp, i32, ct.POINTER(i32), ct.POINTER(i32)]
+    lib.mgpt_moe_bind_params.argtypes = [vp, ct.POINTER(vp), ct.POINTER(vp), i32]
+    lib.mgpt_moe_sync_weights.argtypes = [vp, vp]
+    lib.mgpt_moe_workspace_bytes.argtypes = [vp, i32]
+    lib.mgpt_moe_workspace_bytes.restype = sz
+    lib.mgpt_moe_forward.argtypes = [vp, vp, vp, i32, i32, vp, sz, vp]
+    lib.mgpt_moe_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]
+    lib.mgpt_moe_expert_counts.argtypes = [vp, ct.POINTER(ct.c_int32)]
+    lib.mgpt_moe_workspace_view.argtypes = [vp, i32, ct.c_char_p, ct.POINTER(sz), ct.POINTER(sz)]
+    lib.mgpt_moe_step_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp]
+    lib.mgpt_moe_launch_count.argtypes = [i32]
+    lib.mgpt_moe_launch_count.restype = ct.c_long
+    lib.mgpt_moe_set_profiling.argtypes = [vp, i32]
+    lib.mgpt_moe_stage_ms.argtypes = [vp, ct.POINTER(ct.c_float)]
+    lib.mgpt_moe_stage_name.argtypes = [i32]
+    lib.mgpt_moe_stage_name.restype = ct.c_char_p
+    lib.mgpt_moe_op_router.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = load().mgpt_moe_last_error()
+        raise MoeError(f"mgpt_moe error {rc}: {msg.decode() if msg else '?'}")

@@ -1,0 +1,432 @@
+// C ABI of the MoE layer: layer lifetime, parameter binding, workspace layout
+// and the forward / backward schedules.  See include/mgpt_moe.h for the
+// contract and the reference interfaces each entry point stands in for.
+#include <atomic>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace mgpt {
+
+static thread_local std::string g_error;
+static std::atomic<long> g_launches{0};
+
+void set_error(const std::string& msg) { g_error = msg; }
+int fail(int code, const std::string& msg)
+{
+    g_error = msg;
+    return code;
+}
+int cuda_fail(cudaError_t e, const char* what)
+{
+    g_error = std::string(what) + ": " + cudaGetErrorString(e);
+    return MGPT_MOE_ECUDA;
+}
+void count_launch(int n) { g_launches += n; }
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+Workspace make_workspace(const Dims& d, int n_tokens)
+{
+    Workspace w = {};
+    const size_t N = (size_t)n_tokens, E = d.E, k = d.k, C = d.C, H = d.H;
+    w.n_tokens = n_tokens;
+    w.R = (int)(N * k);
+    w.max_tiles = (int)((N * k + E * (ROW_TILE - 1)) / ROW_TILE);
+    if (w.max_tiles < 1) w.max_tiles = 1;
+    w.row_cap = w.max_tiles * ROW_TILE;
+    w.plan_blocks = (int)((N * k + 1023) / 1024);
+    if (w.plan_blocks < 1) w.plan_blocks = 1;
+    w.act_bytes = d.mode == MGPT_MOE_BF16 ? 2 : 4;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off = align_up(off + (bytes ? bytes : 1), 256);
+        return o;
+    };
+    const size_t rc = (size_t)w.row_cap, ab = w.act_bytes;
+    w.logits = take(N * E * 4);
+    w.probs = take(N * E * 4);
+    w.top_idx = take(N * k * 4);
+    w.top_p = take(N * k * 4);
+    w.counts = take(E * 4);
+    w.offsets = take(E * 4);
+    w.padded_offsets = take((E + 1) * 4);
+    w.tile_expert = take((size_t)w.max_tiles * 4);
+    w.n_tiles = take(4);
+    w.status = take(4);
+    w.map = take(N * k * 4);
+    w.pos = take(N * k * 4);
+    w.row_src = take(rc * 4);
+    w.blk_cnt = take((size_t)w.plan_blocks * E * 4);
+    w.Xg = take(rc * C * ab);
+    w.G = take(rc * H * ab);
+    w.U = take(rc * H * ab);
+    w.Hh = take(rc * H * ab);
+    w.Yg = take(rc * C * ab);
+    w.dYg = take(rc * C * ab);
+    w.dG = take(rc * H * ab);
+    w.dU = take(rc * H * ab);
+    w.dXg = take(rc * C * ab);
+    w.d_top_p = take(N * k * 4);
+    w.dlogits = take(N * E * 4);
+    w.total = off;
+    return w;
+}
+
+static bool use_tc(const mgpt_moe_layer* L) { return L->d.mode == MGPT_MOE_BF16 && L->d.gemm_impl == 0; }
+
+}  // namespace mgpt
+
+using namespace mgpt;
+
+extern "C" {
+
+const char* mgpt_moe_last_error(void) { return g_error.c_str(); }
+
+long mgpt_moe_launch_count(int reset)
+{
+    return reset ? g_launches.exchange(0) : g_launches.load();
+}
+
+int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
+{
+    if (!cfg || !out) return fail(MGPT_MOE_EINVAL, "null argument");
+    const int C = cfg->embed_dim, E = cfg->num_experts, k = cfg->top_k;
+    const int H = cfg->hidden_dim == -1 ? 4 * C : cfg->hidden_dim;
+    if (C <= 0 || H <= 0 || E <= 0 || k <= 0) return fail(MGPT_MOE_EINVAL, "dimensions must be positive");
+    if (E > MAX_EXPERTS) return fail(MGPT_MOE_EINVAL, "num_experts > 128 is not supported");
+    if (k > MAX_TOPK || k > E) return fail(MGPT_MOE_EINVAL, "top_k must be <= min(8, num_experts)");
+    if (C % 8 || H % 8) return fail(MGPT_MOE_EINVAL, "embed_dim and hidden_dim must be multiples of 8");
+    if (cfg->mode != MGPT_MOE_FP32 && cfg->mode != MGPT_MOE_BF16) return fail(MGPT_MOE_EINVAL, "unknown mode");
+    int ndev = 0;
+    MGPT_CUDA(cudaGetDeviceCount(&ndev));
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(MGPT_MOE_ECUDA, "no such CUDA device");
+    MGPT_CUDA(cudaSetDevice(cfg->device));
+
+    mgpt_moe_layer* L = new mgpt_moe_layer();
+    L->d = Dims{C, H, E, k, cfg->lb_alpha, cfg->mode, cfg->gemm_impl};
+    L->device = cfg->device;
+    L->n_params = 2 + 6 * E;
+    L->p_data.assign(L->n_params, nullptr);
+    L->p_grad.assign(L->n_params, nullptr);
+
+    // 15 tables of E pointers: 12 master (W, b, gW, gb) + 3 shadow W
+    cudaError_t e = cudaMalloc(&L->d_tables, (size_t)15 * E * sizeof(void*));
+    if (e != cudaSuccess) {
+        delete L;
+        return cuda_fail(e, "cudaMalloc(tables)");
+    }
+    void** t = (void**)L->d_tables;
+    auto tab = [&](int i) { return t + (size_t)i * E; };
+    L->master.Wg = (const void**)tab(0); L->master.Wu = (const void**)tab(1); L->master.Wd = (const void**)tab(2);
+    L->master.bg = (const float**)tab(3); L->master.bu = (const float**)tab(4); L->master.bd = (const float**)tab(5);
+    L->master.gWg = (float**)tab(6); L->master.gWu = (float**)tab(7); L->master.gWd = (float**)tab(8);
+    L->master.gbg = (float**)tab(9); L->master.gbu = (float**)tab(10); L->master.gbd = (float**)tab(11);
+    L->shadow = L->master;
+    L->shadow.Wg = (const void**)tab(12); L->shadow.Wu = (const void**)tab(13); L->shadow.Wd = (const void**)tab(14);
+
+    if (cfg->mode == MGPT_MOE_BF16) {
+        const size_t n = (size_t)E * C * H;
+        bf16** s[6] = {&L->sWg, &L->sWu, &L->sWd, &L->sWgT, &L->sWuT, &L->sWdT};
+        for (auto p : s) {
+            e = cudaMalloc(p, n * sizeof(bf16));
+            if (e != cudaSuccess) {
+                mgpt_moe_destroy(L);
+                return cuda_fail(e, "cudaMalloc(shadows)");
+            }
+        }
+    }
+    *out = L;
+    return 0;
+}
+
+void mgpt_moe_destroy(mgpt_moe_layer* L)
+{
+    if (!L) return;
+    cudaSetDevice(L->device);
+    tc_destroy(L);
+    cudaFree(L->d_tables);
+    cudaFree(L->sWg); cudaFree(L->sWu); cudaFree(L->sWd);
+    cudaFree(L->sWgT); cudaFree(L->sWuT); cudaFree(L->sWdT);
+    cudaFree(L->h_x); cudaFree(L->h_dy); cudaFree(L->h_y); cudaFree(L->h_dx); cudaFree(L->h_ws);
+    for (int s = 0; s < ST_COUNT; ++s) {
+        if (L->ev_begin[s]) cudaEventDestroy(L->ev_begin[s]);
+        if (L->ev_end[s]) cudaEventDestroy(L->ev_end[s]);
+    }
+    delete L;
+}
+
+int mgpt_moe_num_params(const mgpt_moe_layer* L) { return L ? L->n_params : 0; }
+
+int mgpt_moe_param_shape(const mgpt_moe_layer* L, int i, int* rows, int* cols)
+{
+    if (!L || !rows || !cols || i < 0 || i >= L->n_params) return fail(MGPT_MOE_EINVAL, "bad parameter index");
+    const Dims& d = L->d;
+    if (i == 0) { *rows = d.C; *cols = d.E; return 0; }
+    if (i == 1) { *rows = 1; *cols = d.E; return 0; }
+    switch ((i - 2) % 6) {
+        case 0: case 2: *rows = d.C; *cols = d.H; break;
+        case 1: case 3: *rows = 1; *cols = d.H; break;
+        case 4: *rows = d.H; *cols = d.C; break;
+        default: *rows = 1; *cols = d.C; break;
+    }
+    return 0;
+}
+
+int mgpt_moe_bind_params(mgpt_moe_layer* L, float* const* data, float* const* grad, int n)
+{
+    if (!L || !data) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (n != L->n_params) return fail(MGPT_MOE_EINVAL, "expected 2+6E parameter tensors");
+    for (int i = 0; i < n; ++i) {
+        if (!data[i]) return fail(MGPT_MOE_EINVAL, "null parameter pointer");
+        if (grad && !grad[i]) return fail(MGPT_MOE_EINVAL, "null gradient pointer");
+        L->p_data[i] = data[i];
+        L->p_grad[i] = grad ? grad[i] : nullptr;
+    }
+    L->has_grad = grad != nullptr;
+    MGPT_CUDA(cudaSetDevice(L->device));
+    const int E = L->d.E;
+    const size_t CH = (size_t)L->d.C * L->d.H;
+    std::vector<void*> h((size_t)15 * E, nullptr);
+    for (int e = 0; e < E; ++e) {
+        const int b = 2 + 6 * e;
+        h[0 * E + e] = data[b + 0]; h[1 * E + e] = data[b + 2]; h[2 * E + e] = data[b + 4];
+        h[3 * E + e] = data[b + 1]; h[4 * E + e] = data[b + 3]; h[5 * E + e] = data[b + 5];
+        if (grad) {
+            h[6 * E + e] = grad[b + 0]; h[7 * E + e] = grad[b + 2]; h[8 * E + e] = grad[b + 4];
+            h[9 * E + e] = grad[b + 1]; h[10 * E + e] = grad[b + 3]; h[11 * E + e] = grad[b + 5];
+        }
+        if (L->sWg) {
+            h[12 * E + e] = L->sWg + e * CH; h[13 * E + e] = L->sWu + e * CH; h[14 * E + e] = L->sWd + e * CH;
+        }
+    }
+    MGPT_CUDA(cudaMemcpy(L->d_tables, h.data(), h.size() * sizeof(void*), cudaMemcpyHostToDevice));
+    L->bound = true;
+    L->shadows_fresh = false;
+    return 0;
+}
+
+int mgpt_moe_sync_weights(mgpt_moe_layer* L, mgpt_stream_t stream)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    return launch_sync_weights(L, (cudaStream_t)stream);
+}
+
+size_t mgpt_moe_workspace_bytes(const mgpt_moe_layer* L, int n_tokens)
+{
+    if (!L || n_tokens < 0) return 0;
+    return make_workspace(L->d, n_tokens).total;
+}
+
+int mgpt_moe_workspace_view(const mgpt_moe_layer* L, int n_tokens, const char* name, size_t* offset, size_t* bytes)
+{
+    if (!L || !name || !offset || !bytes || n_tokens < 0) return fail(MGPT_MOE_EINVAL, "bad argument");
+    const Workspace w = make_workspace(L->d, n_tokens);
+    const Dims& d = L->d;
+    const size_t N = n_tokens, E = d.E, k = d.k, C = d.C, H = d.H, rc = w.row_cap, ab = w.act_bytes;
+    struct { const char* n; size_t o, b; } tab[] = {
+        {"logits", w.logits, N * E * 4}, {"probs", w.probs, N * E * 4}, {"top_idx", w.top_idx, N * k * 4},
+        {"top_p", w.top_p, N * k * 4}, {"counts", w.counts, E * 4}, {"offsets", w.offsets, E * 4},
+        {"padded_offsets", w.padded_offsets, (E + 1) * 4}, {"tile_expert", w.tile_expert, (size_t)w.max_tiles * 4},
+        {"n_tiles", w.n_tiles, 4}, {"status", w.status, 4}, {"map", w.map, N * k * 4}, {"pos", w.pos, N * k * 4},
+        {"row_src", w.row_src, rc * 4}, {"Xg", w.Xg, rc * C * ab}, {"G", w.G, rc * H * ab}, {"U", w.U, rc * H * ab},
+        {"Hh", w.Hh, rc * H * ab}, {"Yg", w.Yg, rc * C * ab}, {"dYg", w.dYg, rc * C * ab}, {"dG", w.dG, rc * H * ab},
+        {"dU", w.dU, rc * H * ab}, {"dXg", w.dXg, rc * C * ab}, {"d_top_p", w.d_top_p, N * k * 4},
+        {"dlogits", w.dlogits, N * E * 4},
+    };
+    for (auto& t : tab)
+        if (!strcmp(t.n, name)) {
+            *offset = t.o;
+            *bytes = t.b;
+            return 0;
+        }
+    return fail(MGPT_MOE_EINVAL, std::string("unknown workspace buffer: ") + name);
+}
+
+static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, size_t ws_bytes, Workspace* w)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
+    if (n_tokens < 0) return fail(MGPT_MOE_EINVAL, "negative token count");
+    if (io != MGPT_MOE_IO_F32 && io != MGPT_MOE_IO_BF16) return fail(MGPT_MOE_EINVAL, "unknown io dtype");
+    if (L->d.mode == MGPT_MOE_FP32 && io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 tokens");
+    if ((long long)n_tokens * L->d.k > (1ll << 30)) return fail(MGPT_MOE_EINVAL, "too many routed rows");
+    *w = make_workspace(L->d, n_tokens);
+    if (!ws || ((uintptr_t)ws & 255)) return fail(MGPT_MOE_EINVAL, "workspace must be 256-byte aligned");
+    if (ws_bytes < w->total) return fail(MGPT_MOE_ENOMEM, "workspace smaller than mgpt_moe_workspace_bytes()");
+    if (L->d.mode == MGPT_MOE_BF16 && !L->shadows_fresh)
+        return fail(MGPT_MOE_ESTATE, "sync_weights after bind_params / optimiser step");
+    return 0;
+}
+
+int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io,
+                     void* workspace, size_t ws_bytes, mgpt_stream_t stream)
+{
+    Workspace w;
+    MGPT_TRY(check_call(L, n_tokens, io, workspace, ws_bytes, &w));
+    if (n_tokens > 0 && (!x || !y)) return fail(MGPT_MOE_EINVAL, "null token buffer");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    char* ws = (char*)workspace;
+    const Dims& d = L->d;
+    L->fwd_done = false;
+    for (int s = 0; s < ST_COUNT; ++s) L->ev_used[s] = false;
+    if (n_tokens > 0) {
+        L->stage_begin(ST_ROUTER, st);
+        MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
+                                   (float*)(ws + w.logits), (float*)(ws + w.probs),
+                                   (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
+        L->stage_end(ST_ROUTER, st);
+    }
+    L->stage_begin(ST_PLAN, st);
+    MGPT_TRY(launch_plan(d, w, ws, st));
+    L->stage_end(ST_PLAN, st);
+    if (n_tokens > 0) {
+        L->stage_begin(ST_DISPATCH, st);
+        MGPT_TRY(launch_dispatch(d, w, ws, x, io, st));
+        L->stage_end(ST_DISPATCH, st);
+        if (use_tc(L)) MGPT_TRY(tc_experts_forward(L, w, ws, st));
+        else MGPT_TRY(simt_experts_forward(L, w, ws, st));
+        L->stage_begin(ST_COMBINE, st);
+        MGPT_TRY(launch_combine_fwd(d, w, ws, y, io, st));
+        L->stage_end(ST_COMBINE, st);
+    }
+    L->last_n = n_tokens;
+    L->last_io = io;
+    L->last_ws = workspace;
+    L->last_stream = st;
+    L->fwd_done = true;
+    return 0;
+}
+
+int mgpt_moe_backward(mgpt_moe_layer* L, const void* x, const void* dy, void* dx, int io,
+                      void* workspace, size_t ws_bytes, mgpt_stream_t stream)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (!L->fwd_done) return fail(MGPT_MOE_ESTATE, "backward without a forward");
+    if (workspace != L->last_ws || io != L->last_io)
+        return fail(MGPT_MOE_ESTATE, "backward must reuse the forward's workspace and io dtype");
+    Workspace w;
+    MGPT_TRY(check_call(L, L->last_n, io, workspace, ws_bytes, &w));
+    if (L->last_n == 0) return 0;
+    if (!x || !dy || !dx) return fail(MGPT_MOE_EINVAL, "null token buffer");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    char* ws = (char*)workspace;
+    L->stage_begin(ST_COMBINE_BWD, st);
+    MGPT_TRY(launch_combine_bwd(L->d, w, ws, dy, io, st));
+    L->stage_end(ST_COMBINE_BWD, st);
+    if (use_tc(L)) MGPT_TRY(tc_experts_backward(L, w, ws, st));
+    else MGPT_TRY(simt_experts_backward(L, w, ws, st));
+    if (L->has_grad) {
+        L->stage_begin(ST_BIAS_GRAD, st);
+        MGPT_TRY(launch_bias_grads(L, w, ws, st));
+        L->stage_end(ST_BIAS_GRAD, st);
+    }
+    L->stage_begin(ST_ROUTER_BWD, st);
+    MGPT_TRY(launch_router_bwd(L, w, ws, x, io, dx, st));
+    L->stage_end(ST_ROUTER_BWD, st);
+    return 0;
+}
+
+int mgpt_moe_expert_counts(mgpt_moe_layer* L, int32_t* host_counts)
+{
+    if (!L || !host_counts) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (!L->fwd_done) return fail(MGPT_MOE_ESTATE, "no forward has run");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    const Workspace w = make_workspace(L->d, L->last_n);
+    MGPT_CUDA(cudaMemcpyAsync(host_counts, (char*)L->last_ws + w.counts, (size_t)L->d.E * sizeof(int32_t),
+                              cudaMemcpyDeviceToHost, L->last_stream));
+    MGPT_CUDA(cudaStreamSynchronize(L->last_stream));
+    return 0;
+}
+
+int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_host, void* y_host, void* dx_host,
+                       int n_tokens, int io, mgpt_stream_t stream)
+{
+    if (!L || !x_host || !y_host) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (dy_host && !dx_host) return fail(MGPT_MOE_EINVAL, "dx_host is required with dy_host");
+    if (n_tokens <= 0) return fail(MGPT_MOE_EINVAL, "n_tokens must be positive");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t io_bytes = (size_t)n_tokens * L->d.C * (io == MGPT_MOE_IO_BF16 ? 2 : 4);
+    const size_t ws_bytes = mgpt_moe_workspace_bytes(L, n_tokens);
+    if (io_bytes > L->h_io_bytes) {             // staging grows on demand, never inside a steady-state step
+        MGPT_CUDA(cudaStreamSynchronize(st));
+        cudaFree(L->h_x); cudaFree(L->h_dy); cudaFree(L->h_y); cudaFree(L->h_dx);
+        L->h_x = L->h_dy = L->h_y = L->h_dx = nullptr;
+        L->h_io_bytes = 0;
+        MGPT_CUDA(cudaMalloc(&L->h_x, io_bytes));
+        MGPT_CUDA(cudaMalloc(&L->h_dy, io_bytes));
+        MGPT_CUDA(cudaMalloc(&L->h_y, io_bytes));
+        MGPT_CUDA(cudaMalloc(&L->h_dx, io_bytes));
+        L->h_io_bytes = io_bytes;
+    }
+    if (ws_bytes > L->h_ws_bytes) {
+        MGPT_CUDA(cudaStreamSynchronize(st));
+        cudaFree(L->h_ws);
+        L->h_ws = nullptr;
+        L->h_ws_bytes = 0;
+        MGPT_CUDA(cudaMalloc(&L->h_ws, ws_bytes));
+        L->h_ws_bytes = ws_bytes;
+    }
+    MGPT_CUDA(cudaMemcpyAsync(L->h_x, x_host, io_bytes, cudaMemcpyHostToDevice, st));
+    if (dy_host) MGPT_CUDA(cudaMemcpyAsync(L->h_dy, dy_host, io_bytes, cudaMemcpyHostToDevice, st));
+    MGPT_TRY(mgpt_moe_forward(L, L->h_x, L->h_y, n_tokens, io, L->h_ws, L->h_ws_bytes, stream));
+    MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, st));
+    if (dy_host) {
+        MGPT_TRY(mgpt_moe_backward(L, L->h_x, L->h_dy, L->h_dx, io, L->h_ws, L->h_ws_bytes, stream));
+        MGPT_CUDA(cudaMemcpyAsync(dx_host, L->h_dx, io_bytes, cudaMemcpyDeviceToHost, st));
+    }
+    MGPT_CUDA(cudaStreamSynchronize(st));
+    return 0;
+}
+
+static const char* const kStageNames[ST_COUNT] = {
+    "router", "plan", "dispatch", "gateup_gemm", "down_gemm", "combine",
+    "combine_bwd", "dhh_gemm", "dxg_gemm", "wgrad_gemm", "bias_grad", "router_bwd"};
+
+const char* mgpt_moe_stage_name(int stage)
+{
+    return (stage >= 0 && stage < ST_COUNT) ? kStageNames[stage] : "";
+}
+
+int mgpt_moe_set_profiling(mgpt_moe_layer* L, int enabled)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    if (enabled && !L->ev_begin[0]) {
+        for (int s = 0; s < ST_COUNT; ++s) {
+            MGPT_CUDA(cudaEventCreate(&L->ev_begin[s]));
+            MGPT_CUDA(cudaEventCreate(&L->ev_end[s]));
+        }
+    }
+    L->profiling = enabled != 0;
+    return 0;
+}
+
+int mgpt_moe_stage_ms(mgpt_moe_layer* L, float* ms)
+{
+    if (!L || !ms) return fail(MGPT_MOE_EINVAL, "null argument");
+    for (int s = 0; s < ST_COUNT; ++s) {
+        ms[s] = 0.0f;
+        if (!L->ev_used[s]) continue;
+        MGPT_CUDA(cudaEventSynchronize(L->ev_end[s]));
+        MGPT_CUDA(cudaEventElapsedTime(&ms[s], L->ev_begin[s], L->ev_end[s]));
+    }
+    return 0;
+}
+
+int mgpt_moe_op_router(const void* x, int io, const float* Wr, const float* br, int n_tokens, int C, int E, int k,
+                       float* logits, float* probs, int32_t* top_idx, float* top_p, mgpt_stream_t stream)
+{
+    if (!x || !Wr || !br || !probs || !top_idx || !top_p) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (E <= 0 || E > MAX_EXPERTS || k <= 0 || k > MAX_TOPK || k > E || C <= 0 || n_tokens < 0)
+        return fail(MGPT_MOE_EINVAL, "unsupported router shape");
+    return launch_router_fwd(x, io, Wr, br, n_tokens, C, E, k, logits, probs, top_idx, top_p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

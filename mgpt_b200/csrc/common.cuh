@@ -1,0 +1,165 @@
+// Shared declarations of the MoE layer library: layer state, workspace layout,
+// error plumbing and the launch prototypes of every stage.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/mgpt_moe.h"
+
+namespace mgpt {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int ROW_TILE = 128;   // rows of one expert segment are padded to this
+constexpr int MAX_EXPERTS = 128;
+constexpr int MAX_TOPK = 8;
+
+enum Stage {
+    ST_ROUTER = 0, ST_PLAN, ST_DISPATCH, ST_GATEUP, ST_DOWN, ST_COMBINE,
+    ST_COMBINE_BWD, ST_DHH, ST_DXG, ST_WGRAD, ST_BIAS_GRAD, ST_ROUTER_BWD, ST_COUNT
+};
+static_assert(ST_COUNT == MGPT_MOE_N_STAGES, "stage list and header disagree");
+
+// ---- errors ---------------------------------------------------------------
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+
+#define MGPT_CUDA(call)                                             \
+    do {                                                            \
+        cudaError_t e__ = (call);                                   \
+        if (e__ != cudaSuccess) return ::mgpt::cuda_fail(e__, #call); \
+    } while (0)
+
+#define MGPT_LAUNCHED(name)                                          \
+    do {                                                             \
+        ::mgpt::count_launch();                                      \
+        cudaError_t e__ = cudaGetLastError();                        \
+        if (e__ != cudaSuccess) return ::mgpt::cuda_fail(e__, name); \
+    } while (0)
+
+#define MGPT_TRY(expr)                 \
+    do {                               \
+        int rc__ = (expr);             \
+        if (rc__ != 0) return rc__;    \
+    } while (0)
+
+// ---- workspace ------------------------------------------------------------
+// One arena per forward/backward pair, carved deterministically from
+// (config, n_tokens).  Offsets are bytes, every buffer 256-byte aligned.
+struct Workspace {
+    // routing (kept for backward)
+    size_t logits, probs, top_idx, top_p;
+    // plan
+    size_t counts, offsets, padded_offsets, tile_expert, n_tiles, status;
+    size_t map, pos, row_src, blk_cnt;
+    // forward activations (kept for backward)
+    size_t Xg, G, U, Hh, Yg;
+    // backward temporaries
+    size_t dYg, dG, dU, dXg, d_top_p, dlogits;
+    size_t total;
+    // derived sizes
+    int n_tokens, R, max_tiles, row_cap, plan_blocks;
+    size_t act_bytes;   // bytes per activation element (2 or 4)
+};
+
+struct Dims {
+    int C, H, E, k;
+    float alpha;
+    int mode;       // MGPT_MOE_FP32 / MGPT_MOE_BF16
+    int gemm_impl;  // 0 default, 1 SIMT
+};
+
+Workspace make_workspace(const Dims& d, int n_tokens);
+
+// Device-side tables of per-expert pointers (index = expert).
+struct ExpertPtrs {
+    const void** Wg;  const void** Wu;  const void** Wd;     // [C,H],[C,H],[H,C]
+    const float** bg; const float** bu; const float** bd;
+    float** gWg; float** gWu; float** gWd; float** gbg; float** gbu; float** gbd;
+};
+
+}  // namespace mgpt
+
+struct mgpt_moe_layer {
+    mgpt::Dims d;
+    int device;
+    int n_params;
+    std::vector<float*> p_data, p_grad;      // host copies of the bound pointers
+    bool bound = false, has_grad = false, shadows_fresh = false;
+
+    // device tables: pointers to FP32 masters / grads per expert
+    void* d_tables = nullptr;                // one allocation holding all tables
+    mgpt::ExpertPtrs master;                 // W pointers -> FP32 masters
+    mgpt::ExpertPtrs shadow;                 // W pointers -> BF16 shadows (BF16 mode)
+
+    // BF16 shadows, contiguous over experts (BF16 mode only)
+    mgpt::bf16 *sWg = nullptr, *sWu = nullptr, *sWd = nullptr;      // [E][C][H],[E][C][H],[E][H][C]
+    mgpt::bf16 *sWgT = nullptr, *sWuT = nullptr, *sWdT = nullptr;   // [E][H][C],[E][H][C],[E][C][H]
+
+    // last forward (for backward / counts)
+    int last_n = 0, last_io = 0;
+    void* last_ws = nullptr;
+    cudaStream_t last_stream = 0;
+    bool fwd_done = false;
+
+    // host staging for mgpt_moe_step_host
+    void *h_x = nullptr, *h_dy = nullptr, *h_y = nullptr, *h_dx = nullptr, *h_ws = nullptr;
+    size_t h_io_bytes = 0, h_ws_bytes = 0;
+
+    // TMA descriptors (opaque, built per workspace pointer)
+    void* tc_state = nullptr;
+
+    // optional per-stage timing
+    bool profiling = false;
+    cudaEvent_t ev_begin[mgpt::ST_COUNT] = {}, ev_end[mgpt::ST_COUNT] = {};
+    bool ev_used[mgpt::ST_COUNT] = {};
+    void stage_begin(int s, cudaStream_t st) const
+    {
+        if (profiling) cudaEventRecord(ev_begin[s], st);
+    }
+    void stage_end(int s, cudaStream_t st)
+    {
+        if (profiling) {
+            cudaEventRecord(ev_end[s], st);
+            ev_used[s] = true;
+        }
+    }
+};
+
+namespace mgpt {
+
+// ---- stage launchers (each enqueues on `st`, returns 0 or an error code) ---
+
+// router.cu
+int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, int N, int C, int E, int k,
+                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st);
+int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
+                      void* dx, cudaStream_t st);
+
+// plan.cu
+int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st);
+int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st);
+int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st);
+int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st);
+int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+
+// gemm_simt.cu
+int simt_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int simt_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+
+// gemm_tc.cu (tcgen05 / TMEM / TMA)
+int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+void tc_destroy(mgpt_moe_layer* L);
+
+// weights.cu
+int launch_sync_weights(mgpt_moe_layer* L, cudaStream_t st);
+
+}  // namespace mgpt

@@ -1,0 +1,340 @@
+// Dispatch plan, token permutation and combine of the MoE layer.
+//
+// Reference semantics (paths relative to the reference's src/main/):
+//   counts / offsets   utils/Tensor.cpp:1336-1352, layers/MoELayer.cpp:61-80
+//   slot assignment    utils/Tensor.cpp:1368-1381 (flat index ascending => stable)
+//   combine            utils/Tensor.cpp:1398-1406
+//   combine backward   utils/Tensor.cpp:1424-1436
+//
+// The reference claims slots with a float atomicAdd on the GPU and a host
+// round trip for the prefix sum.  Here the plan is built on the device with
+// no atomics on the slot order and no host synchronisation: block histograms,
+// one scan, then a stable rank per flat index.  The slot map therefore equals
+// the CPU reference's bit for bit.
+//
+// Rows are stored expert-major with every expert's segment padded to a
+// multiple of ROW_TILE rows; padding rows are zero.  Every product tile is
+// then a full tile of one expert, and zero rows contribute nothing to the
+// weight gradients.
+#include "common.cuh"
+
+namespace mgpt {
+
+namespace {
+
+constexpr int PLAN_BLOCK = 1024;   // flat indices per block
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16(v); }
+
+// (1) per-block expert histogram
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_count_kernel(const int32_t* __restrict__ top_idx, int R, int E, int32_t* __restrict__ blk_cnt)
+{
+    __shared__ int cnt[MAX_EXPERTS];
+    if (threadIdx.x < E) cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
+    if (i < R) atomicAdd(&cnt[top_idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x < E) blk_cnt[(size_t)blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
+}
+
+// (2) scan: per expert over blocks, then over experts (compact and padded), tile list
+__global__ void __launch_bounds__(MAX_EXPERTS)
+plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
+                 int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                 int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert,
+                 int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ status)
+{
+    __shared__ int tot[MAX_EXPERTS];
+    __shared__ int poff[MAX_EXPERTS + 1];
+    const int e = threadIdx.x;
+    if (e < E) {
+        int run = 0;
+        for (int b = 0; b < n_blocks; ++b) {
+            const int c = blk_cnt[(size_t)b * E + e];
+            blk_cnt[(size_t)b * E + e] = run;      // becomes the block's base within the expert
+            run += c;
+        }
+        tot[e] = run;
+        counts[e] = run;
+    }
+    __syncthreads();
+    if (e == 0) {
+        int off = 0, p = 0;
+        for (int i = 0; i < E; ++i) {
+            offsets[i] = off;
+            poff[i] = p;
+            padded_offsets[i] = p;
+            off += tot[i];
+            p += (tot[i] + ROW_TILE - 1) / ROW_TILE * ROW_TILE;
+        }
+        poff[E] = p;
+        padded_offsets[E] = p;
+        const int nt = p / ROW_TILE;
+        *n_tiles = nt;
+        if (nt > max_tiles) atomicOr(status, 1);   // cannot happen: max_tiles bounds sum(ceil)
+    }
+    __syncthreads();
+    if (e < E) {
+        const int t0 = poff[e] / ROW_TILE, t1 = poff[e + 1] / ROW_TILE;
+        for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+    }
+}
+
+// (3) stable rank of every flat index within its expert -> map / pos / row_src
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
+                   const int32_t* __restrict__ blk_base, const int32_t* __restrict__ offsets,
+                   const int32_t* __restrict__ padded_offsets,
+                   int32_t* __restrict__ map, int32_t* __restrict__ pos, int32_t* __restrict__ row_src)
+{
+    __shared__ int warp_cnt[PLAN_BLOCK / 32][MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < (PLAN_BLOCK / 32) * MAX_EXPERTS; i += PLAN_BLOCK) (&warp_cnt[0][0])[i] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
+    const bool valid = i < R;
+    const int e = valid ? top_idx[i] : -1 - lane;                 // distinct keys for idle lanes
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (valid) {
+        int base = 0;
+        for (int w = 0; w < warp; ++w) base += warp_cnt[w][e];
+        const int r = blk_base[(size_t)blockIdx.x * E + e] + base + rank_in_warp;
+        const int slot = offsets[e] + r;
+        const int p = padded_offsets[e] + r;
+        map[slot] = i;
+        pos[i] = p;
+        row_src[p] = i;
+    }
+}
+
+// Xg[p,:] = x[row_src[p]/k,:]  (zero for padding rows).  One warp per row, 16-byte accesses.
+template <typename TIn, typename TAct>
+__global__ void __launch_bounds__(256)
+dispatch_rows_kernel(const TIn* __restrict__ x, const int32_t* __restrict__ row_src,
+                     const int32_t* __restrict__ n_tiles, int C, int k, TAct* __restrict__ Xg)
+{
+    const int lane = threadIdx.x & 31;
+    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (p >= *n_tiles * ROW_TILE) return;
+    const int src = row_src[p];
+    TAct* dst = Xg + (size_t)p * C;
+    constexpr int VIN = 16 / sizeof(TIn), VOUT = 16 / sizeof(TAct);
+    constexpr int V = VIN < VOUT ? VIN : VOUT;     // elements per lane per step
+    if (src < 0) {
+        for (int c = lane * V; c < C; c += 32 * V)
+#pragma unroll
+            for (int i = 0; i < V; ++i) dst[c + i] = from_f32<TAct>(0.0f);
+        return;
+    }
+    const TIn* s = x + (size_t)(src / k) * C;
+    if constexpr (sizeof(TIn) == sizeof(TAct)) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(s);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        const int n4 = C / VIN;
+        for (int i = lane; i < n4; i += 32) d4[i] = s4[i];
+        for (int c = n4 * VIN + lane; c < C; c += 32) dst[c] = from_f32<TAct>(to_f32(s[c]));
+    } else {
+        for (int c = lane; c < C; c += 32) dst[c] = from_f32<TAct>(to_f32(s[c]));
+    }
+}
+
+// y[tok,:] = sum_j p[tok,j] * Yg[pos(tok,j),:], slots visited in ascending order
+// like the reference's scatter-add.  One warp per token.
+template <typename TAct, typename TIo>
+__global__ void __launch_bounds__(256)
+combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos, const float* __restrict__ top_p,
+                   int N, int C, int k, TIo* __restrict__ y)
+{
+    const int lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (tok >= N) return;
+    int ps[MAX_TOPK];
+    float pr[MAX_TOPK];
+#pragma unroll
+    for (int j = 0; j < MAX_TOPK; ++j) {
+        ps[j] = j < k ? pos[(size_t)tok * k + j] : 0x7fffffff;
+        pr[j] = j < k ? top_p[(size_t)tok * k + j] : 0.0f;
+    }
+#pragma unroll
+    for (int a = 0; a < MAX_TOPK - 1; ++a)          // tiny sorting network (bubble), static indices
+#pragma unroll
+        for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
+            if (ps[b] > ps[b + 1]) {
+                int ti = ps[b]; ps[b] = ps[b + 1]; ps[b + 1] = ti;
+                float tf = pr[b]; pr[b] = pr[b + 1]; pr[b + 1] = tf;
+            }
+    for (int c = lane * 2; c < C; c += 64) {
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) {
+            if (j < k) {
+                const TAct* r = Yg + (size_t)ps[j] * C + c;
+                a0 = __fadd_rn(a0, __fmul_rn(to_f32(r[0]), pr[j]));
+                if (c + 1 < C) a1 = __fadd_rn(a1, __fmul_rn(to_f32(r[1]), pr[j]));
+            }
+        }
+        y[(size_t)tok * C + c] = from_f32<TIo>(a0);
+        if (c + 1 < C) y[(size_t)tok * C + c + 1] = from_f32<TIo>(a1);
+    }
+}
+
+// dYg[p,:] = p * dy[tok,:],  d_top_p[flat] = <Yg[p,:], dy[tok,:]>; padding rows -> 0.
+template <typename TAct, typename TIo>
+__global__ void __launch_bounds__(256)
+combine_bwd_kernel(const TIo* __restrict__ dy, const TAct* __restrict__ Yg, const int32_t* __restrict__ row_src,
+                   const float* __restrict__ top_p, const int32_t* __restrict__ n_tiles, int C, int k,
+                   TAct* __restrict__ dYg, float* __restrict__ d_top_p)
+{
+    const int lane = threadIdx.x & 31;
+    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (p >= *n_tiles * ROW_TILE) return;
+    const int src = row_src[p];
+    TAct* dst = dYg + (size_t)p * C;
+    if (src < 0) {
+        for (int c = lane; c < C; c += 32) dst[c] = from_f32<TAct>(0.0f);
+        return;
+    }
+    const float prob = top_p[src];
+    const TIo* g = dy + (size_t)(src / k) * C;
+    const TAct* yg = Yg + (size_t)p * C;
+    float dot = 0.0f;
+    for (int c = lane; c < C; c += 32) {
+        const float gv = to_f32(g[c]);
+        dst[c] = from_f32<TAct>(__fmul_rn(gv, prob));
+        dot = fmaf(to_f32(yg[c]), gv, dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) d_top_p[src] = dot;
+}
+
+// Column sums of one activation matrix over each expert's (padded) rows:
+// gb[e][c] += sum_rows M[p,c]  (layers/LinearLayer.cpp:56-57).  grid (E, col blocks, row splits)
+constexpr int BG_ROWS = 512;
+template <typename TAct>
+__global__ void __launch_bounds__(128)
+bias_grad_kernel(const TAct* __restrict__ M, int cols, const int32_t* __restrict__ padded_offsets,
+                 float* const* __restrict__ gb)
+{
+    const int e = blockIdx.x;
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    const int r0 = padded_offsets[e] + blockIdx.z * BG_ROWS;
+    const int r1 = min(padded_offsets[e + 1], r0 + BG_ROWS);
+    if (c >= cols || r0 >= r1) return;
+    float s = 0.0f;
+    for (int r = r0; r < r1; ++r) s += to_f32(M[(size_t)r * cols + c]);
+    atomicAdd(&gb[e][c], s);
+}
+
+}  // namespace
+
+int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st)
+{
+    const int R = w.R, E = d.E;
+    int32_t* top_idx = (int32_t*)(ws + w.top_idx);
+    int32_t* blk = (int32_t*)(ws + w.blk_cnt);
+    MGPT_CUDA(cudaMemsetAsync(ws + w.row_src, 0xFF, (size_t)w.row_cap * sizeof(int32_t), st));
+    MGPT_CUDA(cudaMemsetAsync(ws + w.status, 0, sizeof(int32_t), st));
+    plan_count_kernel<<<w.plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
+    MGPT_LAUNCHED("plan_count_kernel");
+    plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, w.plan_blocks, E, (int32_t*)(ws + w.counts),
+                                                (int32_t*)(ws + w.offsets), (int32_t*)(ws + w.padded_offsets),
+                                                (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
+                                                w.max_tiles, (int32_t*)(ws + w.status));
+    MGPT_LAUNCHED("plan_scan_kernel");
+    plan_assign_kernel<<<w.plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, (int32_t*)(ws + w.offsets),
+                                                             (int32_t*)(ws + w.padded_offsets),
+                                                             (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos),
+                                                             (int32_t*)(ws + w.row_src));
+    MGPT_LAUNCHED("plan_assign_kernel");
+    return 0;
+}
+
+int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st)
+{
+    const int grid = (w.row_cap + 7) / 8;
+    const int32_t* row_src = (const int32_t*)(ws + w.row_src);
+    const int32_t* nt = (const int32_t*)(ws + w.n_tiles);
+    void* Xg = ws + w.Xg;
+    if (w.act_bytes == 4) {
+        if (io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 tokens");
+        dispatch_rows_kernel<float, float><<<grid, 256, 0, st>>>((const float*)x, row_src, nt, d.C, d.k, (float*)Xg);
+    } else if (io == MGPT_MOE_IO_F32) {
+        dispatch_rows_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)x, row_src, nt, d.C, d.k, (bf16*)Xg);
+    } else {
+        dispatch_rows_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)x, row_src, nt, d.C, d.k, (bf16*)Xg);
+    }
+    MGPT_LAUNCHED("dispatch_rows_kernel");
+    return 0;
+}
+
+int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st)
+{
+    const int N = w.n_tokens, grid = (N + 7) / 8;
+    const int32_t* pos = (const int32_t*)(ws + w.pos);
+    const float* tp = (const float*)(ws + w.top_p);
+    const void* Yg = ws + w.Yg;
+    if (w.act_bytes == 4)
+        combine_fwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)Yg, pos, tp, N, d.C, d.k, (float*)y);
+    else if (io == MGPT_MOE_IO_F32)
+        combine_fwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)Yg, pos, tp, N, d.C, d.k, (float*)y);
+    else
+        combine_fwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)Yg, pos, tp, N, d.C, d.k, (bf16*)y);
+    MGPT_LAUNCHED("combine_fwd_kernel");
+    return 0;
+}
+
+int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st)
+{
+    const int grid = (w.row_cap + 7) / 8;
+    const int32_t* row_src = (const int32_t*)(ws + w.row_src);
+    const int32_t* nt = (const int32_t*)(ws + w.n_tiles);
+    const float* tp = (const float*)(ws + w.top_p);
+    float* dtp = (float*)(ws + w.d_top_p);
+    if (w.act_bytes == 4)
+        combine_bwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)dy, (const float*)(ws + w.Yg), row_src, tp,
+                                                               nt, d.C, d.k, (float*)(ws + w.dYg), dtp);
+    else if (io == MGPT_MOE_IO_F32)
+        combine_bwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const float*)dy, (const bf16*)(ws + w.Yg), row_src, tp,
+                                                              nt, d.C, d.k, (bf16*)(ws + w.dYg), dtp);
+    else
+        combine_bwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)(ws + w.Yg), row_src, tp,
+                                                             nt, d.C, d.k, (bf16*)(ws + w.dYg), dtp);
+    MGPT_LAUNCHED("combine_bwd_kernel");
+    return 0;
+}
+
+int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
+{
+    const Dims& d = L->d;
+    const int32_t* poff = (const int32_t*)(ws + w.padded_offsets);
+    const int zs = (w.row_cap + BG_ROWS - 1) / BG_ROWS;
+    dim3 gH(d.E, (d.H + 127) / 128, zs), gC(d.E, (d.C + 127) / 128, zs);
+    if (w.act_bytes == 4) {
+        bias_grad_kernel<float><<<gC, 128, 0, st>>>((const float*)(ws + w.dYg), d.C, poff, L->master.gbd);
+        MGPT_LAUNCHED("bias_grad_kernel");
+        bias_grad_kernel<float><<<gH, 128, 0, st>>>((const float*)(ws + w.dG), d.H, poff, L->master.gbg);
+        MGPT_LAUNCHED("bias_grad_kernel");
+        bias_grad_kernel<float><<<gH, 128, 0, st>>>((const float*)(ws + w.dU), d.H, poff, L->master.gbu);
+        MGPT_LAUNCHED("bias_grad_kernel");
+    } else {
+        bias_grad_kernel<bf16><<<gC, 128, 0, st>>>((const bf16*)(ws + w.dYg), d.C, poff, L->master.gbd);
+        MGPT_LAUNCHED("bias_grad_kernel");
+        bias_grad_kernel<bf16><<<gH, 128, 0, st>>>((const bf16*)(ws + w.dG), d.H, poff, L->master.gbg);
+        MGPT_LAUNCHED("bias_grad_kernel");
+        bias_grad_kernel<bf16><<<gH, 128, 0, st>>>((const bf16*)(ws + w.dU), d.H, poff, L->master.gbu);
+        MGPT_LAUNCHED("bias_grad_kernel");
+    }
+    return 0;
+}
+
+}  // namespace mgpt

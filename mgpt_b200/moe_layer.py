@@ -1,0 +1,172 @@
+"""Host-side mirror of the reference's ``MoELayer`` over the C ABI.
+
+Same constructor arguments and method names as the reference class
+(src/main/neuralnetwork/layers/MoELayer.h:37-50): ``forward`` / ``forward_into``,
+``backward`` / ``backward_into``, ``get_parameters``, ``get_footprint``,
+``get_expert_counts``.  torch is used for device memory and streams only; all
+arithmetic happens in ``libmgpt_moe.so``.  The parameters are FP32 device
+tensors owned by this object, standing where the engine's ``Tensor`` masters
+stand; gradients accumulate into ``param.grad`` like ``Tensor::add_grad``.
+"""
+from __future__ import annotations
+
+import ctypes as ct
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import BF16, FP32, IO_BF16, IO_F32, MoeError  # noqa: F401
+
+
+class MoELayer:
+    def __init__(self, embed_dim: int, hidden_dim: int, num_experts: int, top_k: int, *,
+                 mode: str = "bf16", device: int = 0, lb_alpha: float = 0.01, gemm_impl: int = 0):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise MoeError("mgpt_b200.MoELayer needs a CUDA device; there is no CPU path")
+        self.C = embed_dim
+        self.H = 4 * embed_dim if hidden_dim == -1 else hidden_dim
+        self.E, self.k = num_experts, top_k
+        self.mode = {"fp32": FP32, "bf16": BF16}[mode]
+        self.device = torch.device("cuda", device)
+        cfg = _lib.Config(embed_dim, hidden_dim, num_experts, top_k, lb_alpha, self.mode, device, gemm_impl)
+        self._h = ct.c_void_p()
+        _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(self._h)))
+        self.params = []
+        r, c = ct.c_int(), ct.c_int()
+        for i in range(self.lib.mgpt_moe_num_params(self._h)):
+            _lib.check(self.lib.mgpt_moe_param_shape(self._h, i, ct.byref(r), ct.byref(c)))
+            p = torch.zeros((r.value, c.value), dtype=torch.float32, device=self.device)
+            p.grad = torch.zeros_like(p)
+            self.params.append(p)
+        self._bind()
+        self._ws = None
+        self._x = None
+        self._n = 0
+        self.cached_out = None
+        self.cached_dX = None
+
+    # -- lifetime ----------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            self.lib.mgpt_moe_destroy(self._h)
+            self._h = ct.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _bind(self):
+        n = len(self.params)
+        data = (ct.c_void_p * n)(*[p.data_ptr() for p in self.params])
+        grad = (ct.c_void_p * n)(*[p.grad.data_ptr() for p in self.params])
+        _lib.check(self.lib.mgpt_moe_bind_params(self._h, data, grad, n))
+
+    @staticmethod
+    def _stream():
+        return ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # -- parameters --------------------------------------------------------
+    def get_parameters(self):
+        """2+6E FP32 tensors in the reference's order (MoELayer.cpp:225-236)."""
+        return self.params
+
+    def load_parameters(self, arrays):
+        assert len(arrays) == len(self.params)
+        for p, a in zip(self.params, arrays):
+            p.copy_(torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).reshape(p.shape))
+        self.sync_weights()
+
+    def sync_weights(self):
+        """Refresh the BF16 shadows after the FP32 masters changed."""
+        _lib.check(self.lib.mgpt_moe_sync_weights(self._h, self._stream()))
+
+    def zero_grad(self):
+        for p in self.params:
+            p.grad.zero_()
+
+    # -- memory ------------------------------------------------------------
+    def get_footprint(self, B: int, T: int) -> int:
+        """Arena bytes for B*T tokens (the reference reports floats, MoELayer.cpp:238-251)."""
+        return int(self.lib.mgpt_moe_workspace_bytes(self._h, B * T))
+
+    def _workspace(self, n: int):
+        need = int(self.lib.mgpt_moe_workspace_bytes(self._h, n))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    def workspace_view(self, name: str, dtype, shape=None):
+        """A tensor view of a named workspace buffer of the last forward."""
+        off, nbytes = ct.c_size_t(), ct.c_size_t()
+        _lib.check(self.lib.mgpt_moe_workspace_view(self._h, self._n, name.encode(), ct.byref(off), ct.byref(nbytes)))
+        t = self._ws[off.value: off.value + nbytes.value].view(dtype)
+        return t.view(shape) if shape is not None else t
+
+    # -- compute -----------------------------------------------------------
+    def _io(self, t: torch.Tensor) -> int:
+        if t.dtype == torch.float32:
+            return IO_F32
+        if t.dtype == torch.bfloat16:
+            return IO_BF16
+        raise MoeError(f"unsupported token dtype {t.dtype}")
+
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        assert x.is_cuda and x.is_contiguous() and x.shape[-1] == self.C
+        assert out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous()
+        n = x.numel() // self.C
+        ws = self._workspace(n)
+        _lib.check(self.lib.mgpt_moe_forward(self._h, x.data_ptr(), out.data_ptr(), n, self._io(x),
+                                             ws.data_ptr(), ws.numel(), self._stream()))
+        self._x, self._n = x, n
+        self.cached_out = out
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(x)
+        self.forward_into(x, out)
+        return out
+
+    def backward_into(self, dout: torch.Tensor, din: torch.Tensor) -> None:
+        if self._x is None:
+            raise MoeError("backward before forward")
+        assert dout.shape == self._x.shape and dout.dtype == self._x.dtype and dout.is_contiguous()
+        assert din.shape == dout.shape and din.dtype == dout.dtype and din.is_contiguous()
+        ws = self._ws
+        _lib.check(self.lib.mgpt_moe_backward(self._h, self._x.data_ptr(), dout.data_ptr(), din.data_ptr(),
+                                              self._io(dout), ws.data_ptr(), ws.numel(), self._stream()))
+        self.cached_dX = din
+
+    def backward(self, dout: torch.Tensor) -> torch.Tensor:
+        din = torch.empty_like(dout)
+        self.backward_into(dout, din)
+        return din
+
+    def get_expert_counts(self):
+        """Per-expert routed rows of the last forward (MoELayer.h:39), as a list of ints."""
+        buf = (ct.c_int32 * self.E)()
+        _lib.check(self.lib.mgpt_moe_expert_counts(self._h, buf))
+        return list(buf)
+
+    def set_profiling(self, enabled: bool) -> None:
+        _lib.check(self.lib.mgpt_moe_set_profiling(self._h, 1 if enabled else 0))
+
+    def stage_ms(self) -> dict:
+        """Milliseconds per stage of the last forward/backward pair (profiling must be on)."""
+        buf = (ct.c_float * _lib.N_STAGES)()
+        _lib.check(self.lib.mgpt_moe_stage_ms(self._h, buf))
+        return {self.lib.mgpt_moe_stage_name(i).decode(): float(buf[i]) for i in range(_lib.N_STAGES)}
+
+    def step_host(self, x_host: torch.Tensor, dy_host, y_host: torch.Tensor, dx_host) -> None:
+        """Forward (+ backward) with host buffers; copies in and out inside the call."""
+        n = x_host.numel() // self.C
+        _lib.check(self.lib.mgpt_moe_step_host(
+            self._h, x_host.data_ptr(), dy_host.data_ptr() if dy_host is not None else None,
+            y_host.data_ptr(), dx_host.data_ptr() if dx_host is not None else None,
+            n, self._io(x_host), self._stream()))
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(_lib.load().mgpt_moe_launch_count(1 if reset else 0))
