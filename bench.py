@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE layer hot path: tokens/s of one forward+backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  ``value`` is device-timed throughput with inputs
+resident in HBM; ``e2e`` is the same step through the host-buffer entry point
+(H2D of x and dy, D2H of y and dx inside the timed region); ``roofline`` scores
+the dominant kernel against the measured peaks; ``cpu_baseline`` is the
+reference's own CPU code (or the C restatement of it) timed on a bounded sample.
+For N > 1 launch under torchrun: one rank per GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_fwd_bwd_tokens_per_sec"
+UNIT = "tokens/s"
+
+
+def describe(w) -> str:
+    return (f"{w.name}: {w.n_tokens} tokens, C={w.C}, H={w.H}, E={w.E}, top-{w.k}, "
+            f"{'fwd+bwd' if w.backward else 'fwd only'}, {w.dtype}" + (", skewed router" if w.skew else ""))
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_step(w, sample_tokens: int, threads: int = 1, iters: int = 1):
+    """Forward+backward of the reference's CPU code on `sample_tokens` tokens of workload w
+    (layer construction and parameter loading untimed).  Returns (seconds per iteration list, kind, cores)."""
+    from mgpt_b200 import synth
+    from oracle import oracle
+
+    ws = w.scaled(sample_tokens)
+    x, params, dy = synth.make_inputs(ws, seed=1234)
+    d = oracle.Dims(ws.n_tokens, ws.C, ws.H, ws.E, ws.k, ws.alpha)
+    if oracle.have_ref():
+        which, kind, cores = "ref", "reference", 1      # the reference has no threads of its own
+    else:
+        which, kind, cores = "oracle", "port", threads
+    secs = oracle.bench(d, x, params, dy if w.backward else None, which=which, iters=iters, threads=cores)
+    return secs, kind, cores
+
+
+def run_reference_arm(args, w):
+    """--impl reference: the reference's CPU implementation of the path, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = min(w.n_tokens, args.cpu_sample or 256)
+    secs, kind, cores = cpu_reference_step(w, sample, threads=os.cpu_count() or 1,
+                                           iters=args.warmup + args.steps)
+    times = secs[args.warmup:]
+    sec = sum(times) / max(1, len(times))
+    value = sample / sec
+    sample_txt = f"{sample} tokens of {w.name} per step (same C,H,E,k), forward+backward"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": describe(w), "sample": sample_txt},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample_txt},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            f = [c.strip() for c in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- our arm
+def stage_model(w):
+    """Algorithmic work per launch of each stage: flops for the products, bytes for the rest."""
+    N, C, H, E, k = w.n_tokens, w.C, w.H, w.E, w.k
+    R, b = N * k, 2
+    flops = {"gateup_gemm": 4.0 * R * C * H, "down_gemm": 2.0 * R * C * H, "dhh_gemm": 2.0 * R * C * H,
+             "dxg_gemm": 4.0 * R * C * H, "wgrad_gemm": 6.0 * R * C * H}
+    byts = {
+        "router": N * C * b + C * E * 4 + N * k * 8 + N * E * 4,
+        "dispatch": N * C * b + R * C * b + R * 4,
+        "combine": R * C * b + N * k * 4 + N * C * b,
+        "combine_bwd": N * C * b + R * C * b + R * C * b + N * k * 4,
+        "router_bwd": R * C * b + N * C * b + N * C * b + N * E * 8 + C * E * 4,
+    }
+    return flops, byts
+
+
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+
+    from mgpt_b200 import MoELayer, launch_count, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    N, C = w.n_tokens, w.C
+    io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha)
+    # random-init weights of the architecture, N(0, 0.02); biases 0 (router bias carries the skew)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    for i, p in enumerate(layer.get_parameters()):
+        if p.shape[0] == 1:
+            p.zero_()
+            if i == 1 and w.skew:
+                p.copy_((2.0 * torch.log(1.0 / (torch.arange(w.E, device=dev, dtype=torch.float64) + 1.0))).float()[None, :])
+        else:
+            p.normal_(0.0, 0.02, generator=g)
+            if w.dtype == "bf16":
+                p.copy_(p.to(torch.bfloat16).float())
+    layer.sync_weights()
+    x_host = torch.randn(N, C, generator=torch.Generator().manual_seed(99 + rank)).to(io).pin_memory()
+    dy_host = torch.randn(N, C, generator=torch.Generator().manual_seed(199 + rank)).to(io).pin_memory()
+    y_host = torch.empty_like(x_host).pin_memory()
+    dx_host = torch.empty_like(x_host).pin_memory()
+    x, dy = x_host.to(dev), dy_host.to(dev)
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
+
+    def step():
+        layer.forward_into(x, y)
+        if w.backward:
+            layer.backward_into(dy, dx)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    layer.zero_grad()
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    layer.set_profiling(True)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    stage_sum = {}
+    launch_count(reset=True)
+    for s, e in ev:
+        flush.zero_()                      # L2 flush between timed iterations, outside the events
+        s.record()
+        step()
+        e.record()
+        e.synchronize()
+        for name, ms in layer.stage_ms().items():
+            stage_sum[name] = stage_sum.get(name, 0.0) + ms
+    launches = launch_count()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    layer.set_profiling(False)
+    total_ms = sum(s.elapsed_time(e) for s, e in ev)
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * N / (ms_per_step * 1e-3)
+
+    # end to end through the host-buffer entry point
+    for _ in range(2):
+        layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
+    barrier()
+    e2e_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
+        e2e_ms += (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    io_bytes = x_host.numel() * x_host.element_size()
+    e2e = {"value": world * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": io_bytes * (2 if w.backward else 1),
+           "d2h_bytes_per_step": io_bytes * (2 if w.backward else 1), "checksum": float(y_host.float().abs().mean())}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # per-stage scores and the roofline of the dominant kernel
+    flops, byts = stage_model(w)
+    stages = {}
+    for name, ms in stage_sum.items():
+        ms /= args.steps
+        if ms <= 0:
+            continue
+        ent = {"ms": round(ms, 4)}
+        if name in flops:
+            ent["tflops"] = round(flops[name] / (ms * 1e-3) / 1e12, 1)
+        elif name in byts:
+            ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
+        stages[name] = ent
+    launches_per = {"gateup_gemm": 1, "down_gemm": 1, "dhh_gemm": 1, "dxg_gemm": 1, "wgrad_gemm": 3}
+    gemm = {k: v for k, v in stages.items() if k in flops}
+    roofline = None
+    if gemm:
+        dom = max(gemm, key=lambda k: gemm[k]["ms"] / launches_per[k])
+        per_launch_ms = gemm[dom]["ms"] / launches_per[dom]
+        achieved = flops[dom] / launches_per[dom] / (per_launch_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "unit": "TFLOP/s",
+                    "frac": round(achieved / peak, 4), "traffic": None,
+                    "all_gemms_tflops": round(sum(flops[k] for k in gemm) / (sum(v["ms"] for v in gemm.values()) * 1e-3) / 1e12, 1)}
+
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        sample = min(N, args.cpu_sample or 1024)
+        secs, kind, cores = cpu_reference_step(w, sample, threads=os.cpu_count() or 1, iters=2)
+        sec = min(secs)
+        cpu = {"value": sample / sec, "unit": UNIT, "cores": cores, "kind": kind,
+               "sample": f"{sample} tokens of {w.name} (same C,H,E,k), one forward+backward, {sec:.1f} s"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": describe(w), "parallelism": "one replica per GPU, tokens sharded, no exchange" if world > 1 else "single GPU",
+                   "l2": "flushed between timed steps by a 256 MiB write", "hbm_peak_gbs": peaks["hbm_gbs"]},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "stages": stages,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, help="c1 c2 c3 c4 c5-8 c5-64 c5-256 (default c2)")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="tokens per CPU-baseline step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+
+    from mgpt_b200 import synth
+    w = synth.WORKLOADS[args.workload or "c2"]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

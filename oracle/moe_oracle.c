@@ -16,6 +16,7 @@
 #include <pthread.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 /* Minimal row-parallel helper (POSIX threads): calls fn(lo, hi, arg) on
  * disjoint row ranges.  Only whole output rows are split, never a sum. */
@@ -422,4 +423,48 @@ int moe_oracle_run(const moe_oracle_dims* d, const moe_oracle_inputs* in,
     free(Yg);
     route_free(&rb);
     return 0;
+}
+
+/* Timed CPU baseline of the restatement: `iters` runs of forward (+ backward
+ * when dy is given); seconds[i] receives run i.  Gradients are accumulated
+ * into scratch buffers that are cleared, untimed, before each run. */
+int moe_oracle_bench(const moe_oracle_dims* d, const moe_oracle_inputs* in, int iters, double* seconds,
+                     int n_threads)
+{
+    const int np = 2 + 6 * d->E;
+    float** grads = (float**)calloc((size_t)np, sizeof(float*));
+    size_t* sizes = (size_t*)calloc((size_t)np, sizeof(size_t));
+    for (int i = 0; i < np; ++i) {
+        size_t n;
+        if (i == 0) n = (size_t)d->C * d->E;
+        else if (i == 1) n = (size_t)d->E;
+        else {
+            int r = (i - 2) % 6;
+            n = (r == 0 || r == 2 || r == 4) ? (size_t)d->C * d->H : (r == 5 ? (size_t)d->C : (size_t)d->H);
+        }
+        sizes[i] = n;
+        grads[i] = (float*)malloc(n * sizeof(float));
+    }
+    float* y = (float*)malloc((size_t)d->n_tokens * d->C * sizeof(float));
+    float* dx = (float*)malloc((size_t)d->n_tokens * d->C * sizeof(float));
+    int rc = 0;
+    for (int it = 0; it < iters && rc == 0; ++it) {
+        for (int i = 0; i < np; ++i) memset(grads[i], 0, sizes[i] * sizeof(float));
+        moe_oracle_outputs out;
+        memset(&out, 0, sizeof(out));
+        out.y = y;
+        out.dx = dx;
+        out.grads = grads;
+        struct timespec t0, t1;
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+        rc = moe_oracle_run(d, in, &out, n_threads);
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        seconds[it] = (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+    }
+    for (int i = 0; i < np; ++i) free(grads[i]);
+    free(grads);
+    free(sizes);
+    free(y);
+    free(dx);
+    return rc;
 }

@@ -65,6 +65,10 @@ int moe_oracle_run(const moe_oracle_dims* d, const moe_oracle_inputs* in,
 int moe_oracle_route(const moe_oracle_dims* d, const moe_oracle_inputs* in,
                      moe_oracle_outputs* out, int n_threads);
 
+/* Timed runs for the CPU baseline (setup and gradient clearing are untimed). */
+int moe_oracle_bench(const moe_oracle_dims* d, const moe_oracle_inputs* in, int iters, double* seconds,
+                     int n_threads);
+
 #ifdef __cplusplus
 }
 #endif

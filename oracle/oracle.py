@@ -150,3 +150,30 @@ def run(dims: Dims, x, params, dy=None, *, which: str = "oracle", threads: int =
         res.pop("d_top_p", None)   # locals of the reference's backward; not observable
         res.pop("dlogits", None)
     return res
+
+
+def bench(dims: Dims, x, params, dy=None, *, which: str = "oracle", iters: int = 1, threads: int = 1):
+    """Times forward (+backward) on the CPU; returns the list of per-iteration seconds.
+    Layer construction, parameter loading and gradient clearing are outside the timed region."""
+    N, C = dims.n_tokens, dims.C
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(N, C)
+    params = [np.ascontiguousarray(p, dtype=np.float32) for p in params]
+    if dy is not None:
+        dy = np.ascontiguousarray(dy, dtype=np.float32).reshape(N, C)
+    d = _Dims(N, C, dims.H, dims.E, dims.k, dims.alpha)
+    parr = (_FP * len(params))(*[_fp(p) for p in params])
+    inp = _Inputs(_fp(x), parr, _fp(dy) if dy is not None else None)
+    secs = (ct.c_double * iters)()
+    _load(which)
+    lib = ct.CDLL(ORACLE_SO if which == "oracle" else REF_SO)
+    if which == "oracle":
+        fn = lib.moe_oracle_bench
+        fn.argtypes = [ct.POINTER(_Dims), ct.POINTER(_Inputs), ct.c_int, ct.POINTER(ct.c_double), ct.c_int]
+        rc = fn(ct.byref(d), ct.byref(inp), iters, secs, int(threads))
+    else:
+        fn = lib.moe_ref_bench
+        fn.argtypes = [ct.POINTER(_Dims), ct.POINTER(_Inputs), ct.c_int, ct.POINTER(ct.c_double)]
+        rc = fn(ct.byref(d), ct.byref(inp), iters, secs)
+    if rc != 0:
+        raise RuntimeError(f"{which} bench returned {rc}")
+    return list(secs)

@@ -9,6 +9,7 @@
  * calls the layer's public interface (layers/MoELayer.h:37-50) and reads the
  * tensors the layer caches for its backward pass (layers/MoELayer.h:17-33).
  */
+#include <chrono>
 #include <cstdint>
 #include <cstring>
 #include <functional>
@@ -83,6 +84,37 @@ extern "C" int moe_ref_run(const moe_oracle_dims* d, const moe_oracle_inputs* in
         return run(d, in, out, true);
     } catch (const std::exception& e) {
         std::cerr << "moe_ref_run: " << e.what() << std::endl;
+        return 1;
+    }
+}
+
+/* Timed CPU baseline: the layer is built and loaded once (untimed); each of
+ * `iters` iterations zeroes the gradients (untimed) and then times
+ * forward()+backward() (forward only when dy is NULL) with std::chrono, the
+ * clock the reference's trainer uses (pipeline/Trainer.cpp:314-323).
+ * seconds[i] receives iteration i. */
+extern "C" int moe_ref_bench(const moe_oracle_dims* d, const moe_oracle_inputs* in, int iters, double* seconds)
+{
+    try {
+        const int N = d->n_tokens, C = d->C;
+        MoELayer layer(C, d->H, d->E, d->k);
+        std::vector<Tensor*> params = layer.get_parameters();
+        for (size_t i = 0; i < params.size(); ++i)
+            std::memcpy(params[i]->data.data(), in->params[i], params[i]->size() * sizeof(float));
+        Tensor x({1, N, C}, 0.0f, Device::CPU), dy({1, N, C}, 0.0f, Device::CPU);
+        std::memcpy(x.data.data(), in->x, (size_t)N * C * sizeof(float));
+        if (in->dy) std::memcpy(dy.data.data(), in->dy, (size_t)N * C * sizeof(float));
+        for (int it = 0; it < iters; ++it) {
+            for (Tensor* p : params) p->zero_grad();
+            auto t0 = std::chrono::steady_clock::now();
+            Tensor y = layer.forward(x);
+            if (in->dy) Tensor dx = layer.backward(dy);
+            auto t1 = std::chrono::steady_clock::now();
+            seconds[it] = std::chrono::duration<double>(t1 - t0).count();
+        }
+        return 0;
+    } catch (const std::exception& e) {
+        std::cerr << "moe_ref_bench: " << e.what() << std::endl;
         return 1;
     }
 }

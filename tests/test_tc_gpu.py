@@ -1,0 +1,73 @@
+"""tcgen05 grouped products: against the CPU oracle (2e-2) and, buffer by buffer,
+against the SIMT products run on the same BF16 data."""
+import numpy as np
+import pytest
+import torch
+
+from mgpt_b200 import synth
+from oracle import oracle
+from tests.golden import make_golden as G
+from tests.util import assert_routing_exact, assert_values, dims_of, rel_l2, run_layer
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 2e-2
+ACT = ("Xg", "G", "U", "Hh", "Yg", "dYg", "dG", "dU", "dXg")
+
+
+def _bf16_inputs(w, x, params, dy):
+    return synth.bf16_round(x), [synth.bf16_round(p) for p in params], synth.bf16_round(dy)
+
+
+def _buffers(got, w):
+    layer = got["layer"]
+    rows = int(got["padded_offsets"][-1])
+    out = {}
+    for name in ACT:
+        width = w.C if name in ("Xg", "Yg", "dYg", "dXg") else w.H
+        out[name] = layer.workspace_view(name, torch.bfloat16).view(-1, width)[:rows].float().cpu().numpy()
+    return out
+
+
+@pytest.mark.parametrize("name", sorted(G.CASES))
+def test_tc_matches_oracle_small(name):
+    w, x, params, dy = G.build_case(name)
+    x, params, dy = _bf16_inputs(w, x, params, dy)
+    ref = oracle.run(dims_of(w), x, params, dy, threads=4)
+    got = run_layer(w, x, params, dy, mode="bf16")
+    assert_routing_exact(got, ref)
+    assert_values(got, ref, TOL_BF16, w)
+
+
+@pytest.mark.parametrize("shape", [
+    (1000, 256, 384, 8, 2, False),     # several row tiles per expert, full 64-wide k blocks
+    (700, 192, 200, 5, 2, False),      # ragged k (200 = 3*64+8) and column tails
+    (3000, 128, 96, 16, 4, True),      # skewed: empty and one-row experts next to large ones
+])
+def test_tc_against_simt_and_oracle(shape):
+    n, C, H, E, k, skew = shape
+    w = synth.Workload("tc", n, C, H, E, k, "bf16", skew=skew)
+    x, params, dy = synth.make_inputs(w, seed=11, bias_std=0.02)
+    if skew:
+        params[0] = synth.bf16_round(params[0] * np.float32(10.0))
+    ref = oracle.run(dims_of(w), x, params, dy, threads=16)
+    tc = run_layer(w, x, params, dy, mode="bf16")
+    assert tc["status"] == 0
+    simt = run_layer(w, x, params, dy, mode="bf16", gemm_impl=1)
+    assert_routing_exact(tc, ref)
+    a, b = _buffers(tc, w), _buffers(simt, w)
+    for name in ACT:
+        assert rel_l2(a[name], b[name]) < 6e-3, (name, rel_l2(a[name], b[name]))
+    for i, (ga, gb) in enumerate(zip(tc["grads"], simt["grads"])):
+        assert rel_l2(ga, gb) < 6e-3, (f"grad {i}", rel_l2(ga, gb))
+    assert_values(tc, ref, TOL_BF16, w)
+
+
+def test_tc_c2_reduced_tokens():
+    """Config-2 dimensions (C=512, H=1376, E=16, k=2) on 2048 tokens."""
+    w = synth.WORKLOADS["c2"].scaled(2048)
+    x, params, dy = synth.make_inputs(w)
+    ref = oracle.run(dims_of(w), x, params, dy, threads=32)
+    got = run_layer(w, x, params, dy, mode="bf16", io=torch.bfloat16)
+    assert_routing_exact(got, ref)
+    assert_values(got, ref, TOL_BF16, w)
