@@ -147,6 +147,23 @@ int  mgpt_moe_op_router(const void* x, int io_dtype, const float* Wr, const floa
                         float* logits, float* probs, int32_t* top_idx, float* top_p,
                         mgpt_stream_t stream);
 
+/* histogram + prefix sum + stable slot assignment in one call, on the device
+ * (cuda_ops.h:56-57 moe_histogram / moe_gather's slot claim, MoELayer.cpp:61-80's
+ * host prefix sum). top_idx: [n_rows] expert id per flat index tok*k+j.
+ * Outputs: counts[E], offsets[E] (compact), padded_offsets[E+1] (every expert's
+ * segment rounded up to 128 rows), tile_expert[row_cap/128], n_tiles[1],
+ * map[n_rows] (compact slot -> flat index, the reference's sorted_token_ids),
+ * pos[n_rows] (flat index -> padded row), row_src[row_cap] (padded row -> flat
+ * index, -1 for padding), status[1] (0 = ok).
+ * row_cap: a multiple of 128, at least (n_rows + E*127) rounded down to 128.
+ * scratch: device memory of mgpt_moe_op_plan_scratch_bytes(n_rows, E) bytes. */
+size_t mgpt_moe_op_plan_scratch_bytes(int n_rows, int E);
+int  mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E,
+                      int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
+                      int32_t* tile_expert, int32_t* n_tiles, int32_t* map, int32_t* pos,
+                      int32_t* row_src, int row_cap, int32_t* status,
+                      void* scratch, size_t scratch_bytes, mgpt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

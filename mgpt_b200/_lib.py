@@ -17,6 +17,7 @@ SYMBOLS = [
     "mgpt_moe_forward", "mgpt_moe_backward", "mgpt_moe_expert_counts", "mgpt_moe_workspace_view",
     "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
     "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name",
+    "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes",
 ]
 N_STAGES = 12
 
@@ -66,6 +67,9 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_stage_name.argtypes = [i32]
     lib.mgpt_moe_stage_name.restype = ct.c_char_p
     lib.mgpt_moe_op_router.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]
+    lib.mgpt_moe_op_plan_scratch_bytes.argtypes = [i32, i32]
+    lib.mgpt_moe_op_plan_scratch_bytes.restype = sz
+    lib.mgpt_moe_op_plan.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, sz, vp]
     _lib = lib
     return lib
 

@@ -237,26 +237,31 @@ bias_grad_kernel(const TAct* __restrict__ M, int cols, const int32_t* __restrict
 
 }  // namespace
 
-int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st)
+// The three plan kernels on explicit buffers.  `blk` is scratch of plan_blocks*E ints:
+// every element is written by plan_count_kernel before it is read, so it needs no clearing.
+int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
+             int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
+             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st)
 {
-    const int R = w.R, E = d.E;
-    int32_t* top_idx = (int32_t*)(ws + w.top_idx);
-    int32_t* blk = (int32_t*)(ws + w.blk_cnt);
-    MGPT_CUDA(cudaMemsetAsync(ws + w.row_src, 0xFF, (size_t)w.row_cap * sizeof(int32_t), st));
-    MGPT_CUDA(cudaMemsetAsync(ws + w.status, 0, sizeof(int32_t), st));
-    plan_count_kernel<<<w.plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
+    const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
+    MGPT_CUDA(cudaMemsetAsync(row_src, 0xFF, (size_t)row_cap * sizeof(int32_t), st));
+    MGPT_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+    plan_count_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
     MGPT_LAUNCHED("plan_count_kernel");
-    plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, w.plan_blocks, E, (int32_t*)(ws + w.counts),
-                                                (int32_t*)(ws + w.offsets), (int32_t*)(ws + w.padded_offsets),
-                                                (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
-                                                w.max_tiles, (int32_t*)(ws + w.status));
+    plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, plan_blocks, E, counts, offsets, padded_offsets, tile_expert,
+                                                n_tiles, max_tiles, status);
     MGPT_LAUNCHED("plan_scan_kernel");
-    plan_assign_kernel<<<w.plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, (int32_t*)(ws + w.offsets),
-                                                             (int32_t*)(ws + w.padded_offsets),
-                                                             (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos),
-                                                             (int32_t*)(ws + w.row_src));
+    plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, offsets, padded_offsets, map, pos, row_src);
     MGPT_LAUNCHED("plan_assign_kernel");
     return 0;
+}
+
+int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st)
+{
+    return run_plan((const int32_t*)(ws + w.top_idx), w.R, d.E, (int32_t*)(ws + w.counts), (int32_t*)(ws + w.offsets),
+                    (int32_t*)(ws + w.padded_offsets), (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
+                    w.max_tiles, (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos), (int32_t*)(ws + w.row_src),
+                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st);
 }
 
 int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st)
@@ -337,4 +342,39 @@ int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cud
     return 0;
 }
 
+static int check_plan_args(const int32_t* top_idx, int n_rows, int E, const void* const* outs, int n_outs,
+                           int row_cap)
+{
+    if (!top_idx) return fail(MGPT_MOE_EINVAL, "null top_idx");
+    for (int i = 0; i < n_outs; ++i)
+        if (!outs[i]) return fail(MGPT_MOE_EINVAL, "null output buffer");
+    if (E <= 0 || E > MAX_EXPERTS) return fail(MGPT_MOE_EINVAL, "num_experts must be in 1..128");
+    if (n_rows < 0) return fail(MGPT_MOE_EINVAL, "negative row count");
+    const long long need = ((long long)n_rows + (long long)E * (ROW_TILE - 1)) / ROW_TILE * ROW_TILE;
+    if (row_cap < need || row_cap % ROW_TILE) return fail(MGPT_MOE_EINVAL, "row_cap too small or not a multiple of 128");
+    return 0;
+}
+
 }  // namespace mgpt
+
+using namespace mgpt;
+
+extern "C" size_t mgpt_moe_op_plan_scratch_bytes(int n_rows, int E)
+{
+    if (n_rows < 0 || E <= 0) return 0;
+    const size_t blocks = n_rows > 0 ? ((size_t)n_rows + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
+    return blocks * (size_t)E * sizeof(int32_t);
+}
+
+extern "C" int mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E, int32_t* counts, int32_t* offsets,
+                                int32_t* padded_offsets, int32_t* tile_expert, int32_t* n_tiles, int32_t* map,
+                                int32_t* pos, int32_t* row_src, int row_cap, int32_t* status, void* scratch,
+                                size_t scratch_bytes, mgpt_stream_t stream)
+{
+    const void* outs[] = {counts, offsets, padded_offsets, tile_expert, n_tiles, map, pos, row_src, status, scratch};
+    MGPT_TRY(check_plan_args(top_idx, n_rows, E, outs, 10, row_cap));
+    if (scratch_bytes < mgpt_moe_op_plan_scratch_bytes(n_rows, E))
+        return fail(MGPT_MOE_ENOMEM, "scratch smaller than mgpt_moe_op_plan_scratch_bytes()");
+    return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
+                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream);
+}

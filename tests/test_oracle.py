@@ -89,3 +89,14 @@ def test_oracle_matches_reference_live(shape):
     a = oracle.run(_dims(w), x, params, dy, threads=2)
     b = oracle.run(_dims(w), x, params, dy, which="ref")
     _assert_same(a, b)
+
+
+@pytest.mark.parametrize("name", sorted(G.CASES))
+def test_numpy_plan_reference_matches_golden(name):
+    """The numpy statement of the dispatch plan used by the operator-level GPU tests is itself pinned."""
+    from tests.util import plan_reference
+    w, x, params, dy = G.build_case(name)
+    gold = G.load_golden(name)
+    r = plan_reference(gold["top_idx"], w.E)
+    for key in ("counts", "offsets", "map"):
+        assert np.array_equal(r[key], gold[key]), key

@@ -114,3 +114,26 @@ def test_errors_are_reported():
     bf._bind()                                                       # rebinding marks the shadows stale
     with pytest.raises(MoeError):
         bf.forward(torch.zeros(4, 16, device="cuda"))
+
+
+@pytest.mark.parametrize("n_rows,E", [(0, 4), (1, 1), (37, 3), (5000, 16), (70000, 64), (4096, 128)])
+def test_op_plan_matches_numpy(n_rows, E):
+    """Operator-level dispatch plan through the C ABI: counts, offsets, slot map, padded rows."""
+    import ctypes as ct
+    from mgpt_b200 import _lib
+    from tests.util import assert_plan_equal, plan_buffers, plan_reference, plan_row_cap
+    lib = _lib.load()
+    rng = np.random.default_rng(n_rows + E)
+    # a skewed draw: low expert ids are much more likely, some experts may stay empty
+    idx = np.minimum((rng.random(n_rows) ** 3 * E).astype(np.int32), E - 1)
+    top_idx = torch.from_numpy(idx).cuda() if n_rows else torch.zeros(1, dtype=torch.int32, device="cuda")
+    bufs = plan_buffers(n_rows, E)
+    nbytes = lib.mgpt_moe_op_plan_scratch_bytes(n_rows, E)
+    scratch = torch.empty(max(1, nbytes), dtype=torch.uint8, device="cuda")
+    rc = lib.mgpt_moe_op_plan(top_idx.data_ptr(), n_rows, E, *[bufs[k].data_ptr() for k in
+                              ("counts", "offsets", "padded_offsets", "tile_expert", "n_tiles", "map", "pos", "row_src")],
+                              plan_row_cap(n_rows, E), bufs["status"].data_ptr(), scratch.data_ptr(), nbytes,
+                              ct.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(rc)
+    torch.cuda.synchronize()
+    assert_plan_equal(bufs, plan_reference(idx, E), n_rows)

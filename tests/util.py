@@ -66,3 +66,53 @@ def assert_values(got, ref, tol, w):
             e = rel_l2(a, b)
             # an expert with no rows has exactly zero gradients on both sides
             assert e <= tol, (f"grad {i}", e)
+
+
+# ---- dispatch plan, operator level ---------------------------------------------------------------
+PLAN_OUTPUTS = ("counts", "offsets", "padded_offsets", "tile_expert", "n_tiles", "map", "pos", "row_src", "status")
+
+
+def plan_row_cap(n_rows: int, E: int) -> int:
+    return max(1, (n_rows + E * 127) // 128) * 128
+
+
+def plan_reference(top_idx: np.ndarray, E: int) -> dict:
+    """numpy statement of the plan (stable slots, segments padded to 128 rows)."""
+    flat = np.asarray(top_idx, dtype=np.int64).reshape(-1)
+    R = flat.size
+    counts = np.bincount(flat, minlength=E).astype(np.int32)
+    offsets = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
+    padded = (counts + 127) // 128 * 128
+    poff = np.concatenate([[0], np.cumsum(padded)]).astype(np.int32)
+    order = np.argsort(flat, kind="stable").astype(np.int32)          # slot -> flat index
+    rank = np.empty(R, np.int64)
+    rank[order] = np.arange(R) - offsets[flat[order]]
+    pos = (poff[flat] + rank).astype(np.int32)
+    row_cap = plan_row_cap(R, E)
+    row_src = np.full(row_cap, -1, np.int32)
+    row_src[pos] = np.arange(R, dtype=np.int32)
+    n_tiles = int(poff[-1]) // 128
+    tile_expert = np.repeat(np.arange(E, dtype=np.int32), padded // 128)
+    return {"counts": counts, "offsets": offsets, "padded_offsets": poff, "tile_expert": tile_expert,
+            "n_tiles": np.array([n_tiles], np.int32), "map": order, "pos": pos, "row_src": row_src,
+            "status": np.array([0], np.int32)}
+
+
+def plan_buffers(n_rows: int, E: int, device="cuda") -> dict:
+    row_cap = plan_row_cap(n_rows, E)
+    sizes = {"counts": E, "offsets": E, "padded_offsets": E + 1, "tile_expert": row_cap // 128, "n_tiles": 1,
+             "map": max(1, n_rows), "pos": max(1, n_rows), "row_src": row_cap, "status": 1}
+    return {k: torch.full((v,), -7, dtype=torch.int32, device=device) for k, v in sizes.items()}
+
+
+def assert_plan_equal(bufs: dict, ref: dict, n_rows: int) -> None:
+    """Integer work: every output must match exactly (tile_expert only over the tiles in use)."""
+    nt = int(ref["n_tiles"][0])
+    for key in PLAN_OUTPUTS:
+        got = bufs[key].cpu().numpy()
+        want = ref[key]
+        if key == "tile_expert":
+            got = got[:nt]
+        elif key in ("map", "pos"):
+            got = got[:n_rows]
+        assert np.array_equal(got, want), key
