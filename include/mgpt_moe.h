@@ -164,6 +164,26 @@ int  mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E,
                       int32_t* row_src, int row_cap, int32_t* status,
                       void* scratch, size_t scratch_bytes, mgpt_stream_t stream);
 
+/* The same plan for callers that can neither pass scratch nor let the library
+ * allocate: an engine whose arena already owns all device memory, or a step
+ * loop that must never run into cudaMalloc (it synchronises the whole device).
+ * This entry point has no counterpart in the reference. Identical outputs to
+ * mgpt_moe_op_plan; its scratch is a fixed 512 KiB array inside the library,
+ * held by every GPU that loads the library until the process exits, so:
+ *   - n_rows may be at most MGPT_MOE_PLAN_NOALLOC_MAX_ROWS (else MGPT_MOE_EINVAL);
+ *   - all calls on one GPU share that array: two calls whose kernels may overlap
+ *     (different streams, no ordering between them) race on it; keep them in
+ *     stream order or use mgpt_moe_op_plan with separate scratch;
+ *   - the first call on each device looks up the array's device address
+ *     (once, with that device current); make that first call before any
+ *     stream capture begins.
+ * It calls no cudaMalloc, cudaFree or other allocating routine. */
+#define MGPT_MOE_PLAN_NOALLOC_MAX_ROWS 1048576
+int  mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int E,
+                              int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
+                              int32_t* tile_expert, int32_t* n_tiles, int32_t* map, int32_t* pos,
+                              int32_t* row_src, int row_cap, int32_t* status, mgpt_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,8 +17,9 @@ SYMBOLS = [
     "mgpt_moe_forward", "mgpt_moe_backward", "mgpt_moe_expert_counts", "mgpt_moe_workspace_view",
     "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
     "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name",
-    "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes",
+    "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes", "mgpt_moe_op_plan_noalloc",
 ]
+PLAN_NOALLOC_MAX_ROWS = 1048576
 N_STAGES = 12
 
 
@@ -70,6 +71,7 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_op_plan_scratch_bytes.argtypes = [i32, i32]
     lib.mgpt_moe_op_plan_scratch_bytes.restype = sz
     lib.mgpt_moe_op_plan.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, sz, vp]
+    lib.mgpt_moe_op_plan_noalloc.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
     _lib = lib
     return lib
 

@@ -16,6 +16,8 @@
 // multiple of ROW_TILE rows; padding rows are zero.  Every product tile is
 // then a full tile of one expert, and zero rows contribute nothing to the
 // weight gradients.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mgpt {
@@ -377,4 +379,57 @@ extern "C" int mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E, int32
         return fail(MGPT_MOE_ENOMEM, "scratch smaller than mgpt_moe_op_plan_scratch_bytes()");
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
                     pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream);
+}
+
+// ---- dispatch plan without any allocation ------------------------------------------
+// Some callers cannot give the plan scratch memory of their own and cannot let the
+// library allocate it either: an engine that has already handed all device memory to
+// its own arena (the reference sizes its Scratchpad from a footprint predictor and
+// leaves nothing over), or a step loop that must not meet cudaMalloc's device-wide
+// synchronisation.  For them the per-block histogram lives in a fixed array inside the
+// library image.  Every GPU that loads the library holds these 512 KiB until exit.
+#define PLAN_STATIC_BLOCKS (MGPT_MOE_PLAN_NOALLOC_MAX_ROWS / 1024)
+static __device__ __align__(256) int32_t g_plan_scratch[PLAN_STATIC_BLOCKS * mgpt::MAX_EXPERTS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int32_t* g_scratch_dev_ptr[kMaxDevices] = {};   // device address of g_plan_scratch, per device
+
+// In host code `g_plan_scratch` names a host-side shadow, not device memory; the
+// address a kernel may use has to be asked for, on the device that will run it.
+int plan_static_scratch(int32_t** out)
+{
+    int dev = -1;
+    MGPT_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MGPT_MOE_EINVAL, "device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_dev_ptr[dev]) {
+        void* p = nullptr;
+        MGPT_CUDA(cudaGetSymbolAddress(&p, g_plan_scratch));
+        if (!p) return fail(MGPT_MOE_ECUDA, "cudaGetSymbolAddress returned a null address");
+        g_scratch_dev_ptr[dev] = (int32_t*)p;
+    }
+    *out = g_scratch_dev_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" int mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int E, int32_t* counts, int32_t* offsets,
+                                        int32_t* padded_offsets, int32_t* tile_expert, int32_t* n_tiles,
+                                        int32_t* map, int32_t* pos, int32_t* row_src, int row_cap, int32_t* status,
+                                        mgpt_stream_t stream)
+{
+    if (n_rows > MGPT_MOE_PLAN_NOALLOC_MAX_ROWS)
+        return fail(MGPT_MOE_EINVAL, "mgpt_moe_op_plan_noalloc handles at most " +
+                                         std::to_string(MGPT_MOE_PLAN_NOALLOC_MAX_ROWS) + " routed rows, got " +
+                                         std::to_string(n_rows) + "; use mgpt_moe_op_plan with your own scratch");
+    const void* outs[] = {counts, offsets, padded_offsets, tile_expert, n_tiles, map, pos, row_src, status};
+    MGPT_TRY(check_plan_args(top_idx, n_rows, E, outs, 9, row_cap));
+    int32_t* scratch = nullptr;
+    MGPT_TRY(plan_static_scratch(&scratch));
+    // The array still holds the previous call's block bases.  Nothing has to be cleared:
+    // plan_count_kernel writes all plan_blocks*E entries this call reads before they are read.
+    return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
+                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream);
 }
