@@ -35,9 +35,12 @@ constexpr uint32_t A_BYTES = BM * BK * 2;            // 16 KiB
 constexpr uint32_t B_BYTES = BN * BK * 2;            // 32 KiB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB
 constexpr uint32_t HALF_B = B_BYTES / 2;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_WARPS = 8;
+constexpr uint32_t STAGING_BYTES = 4096;             // per epilogue warp: 32 rows x 128 B
+constexpr uint32_t TMEM_COLS = 2 * BN;               // two accumulators
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int TC_THREADS = 192;                      // warp0 TMA, warp1 MMA, warps2-5 epilogue
+constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-9 epilogue
 
 enum { ERR_FULL_WAIT = 2, ERR_EMPTY_WAIT = 4, ERR_ACC_WAIT = 8 };
 
@@ -51,6 +54,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 {
@@ -73,6 +80,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
 {
@@ -139,25 +151,6 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn_major, 
 
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
-// 32 floats -> 32 bf16, written as up to four 16-byte stores; `valid` columns (multiple of 8) are kept
-__device__ __forceinline__ void store_bf16x32(bf16* dst, const float (&v)[32], int valid)
-{
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (q * 8 < valid) {
-            uint4 u;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
-            u.x = *reinterpret_cast<uint32_t*>(&h0);
-            u.y = *reinterpret_cast<uint32_t*>(&h1);
-            u.z = *reinterpret_cast<uint32_t*>(&h2);
-            u.w = *reinterpret_cast<uint32_t*>(&h3);
-            reinterpret_cast<uint4*>(dst)[q] = u;
-        }
-    }
-}
 __device__ __forceinline__ void load_bf16x32(const bf16* src, float (&v)[32], int valid)
 {
 #pragma unroll
@@ -178,25 +171,108 @@ __device__ __forceinline__ void load_bf16x32(const bf16* src, float (&v)[32], in
     }
 }
 
+// Shared memory of one CTA: operand ring, one 4 KiB staging tile per epilogue warp, barriers.
 struct Pipe {
-    uint32_t bars, acc, tmem_slot;     // shared-space addresses
+    uint32_t bars, tmem_slot;          // shared-space addresses
     uint8_t* tiles;
+    uint8_t* staging;
     __device__ __forceinline__ uint32_t full(int s) const { return bars + 8u * s; }
     __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8u * (STAGES + s); }
+    __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + 8u * (2 * STAGES + b); }
+    __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + 8u * (2 * STAGES + 2 + b); }
 };
 
-// Carves dynamic shared memory: 1024-aligned tile ring, then the barriers.
 __device__ __forceinline__ Pipe carve(uint8_t* raw)
 {
     Pipe p;
     const uint32_t base = smem_u32(raw);
     const uint32_t pad = (1024u - (base & 1023u)) & 1023u;
     p.tiles = raw + pad;
-    p.bars = smem_u32(p.tiles + STAGES * STAGE_BYTES);
-    p.acc = p.bars + 8u * (2 * STAGES);
-    p.tmem_slot = p.acc + 8u;
+    p.staging = p.tiles + STAGES * STAGE_BYTES;
+    p.bars = smem_u32(p.staging + EPI_WARPS * STAGING_BYTES);
+    p.tmem_slot = p.bars + 8u * (2 * STAGES + 4);
     return p;
 }
+
+// Common prologue: barriers, TMEM (both accumulators), returns the TMEM base address.
+__device__ __forceinline__ uint32_t cta_setup(const Pipe& pipe, int warp)
+{
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(pipe.full(s), 1);
+            mbar_init(pipe.empty(s), 1);
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(pipe.acc_full(b), 1);
+            mbar_init(pipe.acc_empty(b), EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(pipe.tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(pipe.tmem_slot));
+    return tmem_base;
+}
+
+__device__ __forceinline__ void cta_teardown(uint32_t tmem_base, int warp)
+{
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// Epilogue warp -> accumulator buffer is free again (all its tcgen05.ld of this tile are done).
+__device__ __forceinline__ void release_acc(uint32_t bar, int lane)
+{
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+
+// Writes this thread's row of a [32 rows x 64 bf16] tile into the warp's staging tile in the
+// 128-byte swizzle a TMA store with SWIZZLE_128B expects (16-byte chunk j of row r at j ^ (r & 7)).
+__device__ __forceinline__ void stage_row_bf16(uint8_t* stage, int lane, const uint32_t (&packed)[32])
+{
+    const uint32_t row = smem_u32(stage) + lane * 128;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t a = row + (((uint32_t)j ^ ((uint32_t)lane & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(packed[4 * j]), "r"(packed[4 * j + 1]),
+                     "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3]) : "memory");
+    }
+}
+// The staged tile -> global through TMA (columns beyond the tensor are clipped by the hardware).
+__device__ __forceinline__ void flush_stage(uint8_t* stage, const CUtensorMap* map, int x, int y, int lane)
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(map, x, y, smem_u32(stage));
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging tile may be rewritten
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void pack64(const float (&a)[32], const float (&b)[32], uint32_t (&out)[32])
+{
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        out[i] = *reinterpret_cast<uint32_t*>(&h);
+        __nv_bfloat162 g = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+        out[16 + i] = *reinterpret_cast<uint32_t*>(&g);
+    }
+}
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 // ---- token-major products ------------------------------------------------------
 enum { MODE_GATEUP = 0, MODE_DOWN = 1, MODE_DHH = 2, MODE_DXG = 3 };
@@ -207,162 +283,209 @@ struct RowsP {
     int32_t* status;
     int kblocks;            // k-blocks (of 64) per operand pair
     int n_out;              // output columns (H or C)
+    int n_col_tiles;        // column tiles per row tile
     int b_rows_per_expert;  // rows of one expert in the B tensor map (= n_out)
-    bf16 *D0, *D1, *D2;     // outputs, row stride n_out
-    const bf16 *G, *U;      // saved pre-activations (MODE_DHH)
+    const bf16 *G, *U;      // saved pre-activations (MODE_DHH), row stride n_out
     const float* const* bias0;
     const float* const* bias1;
 };
 
+// Persistent: CTA b works on items b, b+grid, ... where item = row_tile * n_col_tiles + col_tile.
+// Two 256-column accumulators in TMEM alternate, so the epilogue of one item runs while the
+// tensor core works on the next.
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
-               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1, const RowsP p)
+               const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+               const __grid_constant__ CUtensorMap tmD0, const __grid_constant__ CUtensorMap tmD1,
+               const __grid_constant__ CUtensorMap tmD2, const RowsP p)
 {
     extern __shared__ uint8_t smem_raw[];
-    const int row_tile = blockIdx.y;
-    if (row_tile >= *p.n_tiles) return;                 // whole CTA leaves before any barrier or TMEM use
+    const int total_items = *p.n_tiles * p.n_col_tiles;
+    if ((int)blockIdx.x >= total_items) return;          // whole CTA leaves before any barrier or TMEM use
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = p.tile_expert[row_tile];
-    // GATEUP: 128 hidden units per CTA (128 gate + 128 up accumulator columns); others: 256 columns
-    const int n0 = blockIdx.x * (MODE == MODE_GATEUP ? BN / 2 : BN);
-    const int row0 = row_tile * BM;
-    const int total_kb = (MODE == MODE_DXG ? 2 : 1) * p.kblocks;
+    constexpr int COLS_PER_ITEM = MODE == MODE_GATEUP ? BN / 2 : BN;
+    const int kb_per_item = (MODE == MODE_DXG ? 2 : 1) * p.kblocks;
 
-    Pipe pipe = carve(smem_raw);
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(pipe.full(s), 1);
-            mbar_init(pipe.empty(s), 1);
-        }
-        mbar_init(pipe.acc, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) tmem_alloc(pipe.tmem_slot, BN);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    uint32_t tmem_base;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(pipe.tmem_slot));
+    const Pipe pipe = carve(smem_raw);
+    const uint32_t tmem_base = cta_setup(pipe, warp);
 
     if (warp == 0) {
         if (lane == 0) {
-            const int brow = e * p.b_rows_per_expert + n0;
-            for (int kb = 0; kb < total_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(pipe.empty(s), ((kb / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) break;
-                const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(pipe.full(s), STAGE_BYTES);
-                const bool second = MODE == MODE_DXG && kb >= p.kblocks;
-                const int kx = (second ? kb - p.kblocks : kb) * BK;
-                tma_load_2d(a_dst, second ? &tmA1 : &tmA0, kx, row0, pipe.full(s));
-                if (MODE == MODE_GATEUP) {
-                    tma_load_2d(b_dst, &tmB0, kx, brow, pipe.full(s));
-                    tma_load_2d(b_dst + HALF_B, &tmB1, kx, brow, pipe.full(s));
-                } else {
-                    const CUtensorMap* mb = second ? &tmB1 : &tmB0;
-                    tma_load_2d(b_dst, mb, kx, brow, pipe.full(s));
-                    tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+                const int brow = p.tile_expert[row_tile] * p.b_rows_per_expert + n0;
+                const int row0 = row_tile * BM;
+                for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(pipe.full(s), STAGE_BYTES);
+                    const bool second = MODE == MODE_DXG && kb >= p.kblocks;
+                    const int kx = (second ? kb - p.kblocks : kb) * BK;
+                    tma_load_2d(a_dst, second ? &tmA1 : &tmA0, kx, row0, pipe.full(s));
+                    if (MODE == MODE_GATEUP) {
+                        tma_load_2d(b_dst, &tmB0, kx, brow, pipe.full(s));
+                        tma_load_2d(b_dst + HALF_B, &tmB1, kx, brow, pipe.full(s));
+                    } else {
+                        const CUtensorMap* mb = second ? &tmB1 : &tmB0;
+                        tma_load_2d(b_dst, mb, kx, brow, pipe.full(s));
+                        tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0);
+            uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int kb = 0; kb < total_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(pipe.full(s), (kb / STAGES) & 1, p.status, ERR_FULL_WAIT);
-                if (!ok) break;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++t) {
+                const uint32_t buf = t & 1u;
+                if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(pipe.tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(pipe.full(s), (it / STAGES) & 1, p.status, ERR_FULL_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(pipe.tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint64_t ad = make_desc(a_addr + k * 32, 16, 1024);
-                    const uint64_t bd = make_desc(b_addr + k * 32, 16, 1024);
-                    umma_bf16(tmem_base, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = make_desc(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = make_desc(b_addr + k * 32, 16, 1024);
+                        umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(pipe.empty(s));           // frees the stage once these MMAs have read it
                 }
-                umma_commit(pipe.empty(s));            // frees the stage once these MMAs have read it
+                umma_commit(pipe.acc_full(buf));          // accumulator of this item complete
             }
-            umma_commit(pipe.acc);                      // accumulator complete (arrives even after a failed wait)
         }
     } else {
-        // epilogue warps 2..5 own TMEM lanes 32*(warp%4) .. +31  (row = lane)
-        const int quarter = warp & 3;
-        const int row = row0 + quarter * 32 + lane;
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const bool ok = mbar_wait(pipe.acc, 0, p.status, ERR_ACC_WAIT);
-        tc_fence_after();
-        if (ok) {
+        // 8 epilogue warps: TMEM lane quarter q = warp % 4 (rows q*32..+31), column half h
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        uint8_t* stage = pipe.staging + (warp - 2) * STAGING_BYTES;
+        uint32_t t = 0;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++t) {
+            const uint32_t buf = t & 1u;
+            const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+            const int e = p.tile_expert[row_tile];
+            const int row_w = row_tile * BM + q * 32;           // first row of this warp
+            if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
+            tc_fence_after();
+            const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
             if (MODE == MODE_GATEUP) {
-                const float* bg = p.bias0[e];
-                const float* bu = p.bias1[e];
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    const int n = n0 + c * 32;
-                    const int valid = min(32, p.n_out - n);
-                    if (valid <= 0) break;
-                    float g[32], u[32];
-                    tmem_ld32(t_lane + c * 32, g);
-                    tmem_ld32(t_lane + BN / 2 + c * 32, u);
+                // this warp: hidden units n0 + h*64 .. +63  (gate columns h*64.., up columns 128 + h*64..)
+                const int n = n0 + h * 64;
+                const bool live = n < p.n_out;
+                float a[32], b[32];
+                uint32_t gp[32], up[32];
+                tmem_ld32(t_lane + h * 64, a);
+                tmem_ld32(t_lane + h * 64 + 32, b);
+                if (live) {
+                    const float* bg = p.bias0[e];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        if (j < valid) {
-                            // round the stored pre-activations first: backward reads them back
-                            g[j] = __bfloat162float(__float2bfloat16(g[j] + bg[n + j]));
-                            u[j] = __bfloat162float(__float2bfloat16(u[j] + bu[n + j]));
-                        }
+                        a[j] += (n + j < p.n_out) ? bg[n + j] : 0.0f;
+                        b[j] += (n + 32 + j < p.n_out) ? bg[n + 32 + j] : 0.0f;
                     }
-                    const size_t o = (size_t)row * p.n_out + n;
-                    store_bf16x32(p.D0 + o, g, valid);
-                    store_bf16x32(p.D1 + o, u, valid);
+                }
+                pack64(a, b, gp);
+                tmem_ld32(t_lane + BN / 2 + h * 64, a);
+                tmem_ld32(t_lane + BN / 2 + h * 64 + 32, b);
+                release_acc(pipe.acc_empty(buf), lane);
+                if (live) {
+                    const float* bu = p.bias1[e];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) g[j] = silu(g[j]) * u[j];
-                    store_bf16x32(p.D2 + o, g, valid);
+                    for (int j = 0; j < 32; ++j) {
+                        a[j] += (n + j < p.n_out) ? bu[n + j] : 0.0f;
+                        b[j] += (n + 32 + j < p.n_out) ? bu[n + 32 + j] : 0.0f;
+                    }
+                    pack64(a, b, up);
+                    stage_row_bf16(stage, lane, gp);
+                    flush_stage(stage, &tmD0, n, row_w, lane);
+                    stage_row_bf16(stage, lane, up);
+                    flush_stage(stage, &tmD1, n, row_w, lane);
+                    // Hh from the rounded G and U (backward reads the stored values)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g0 = bf_lo(gp[i]), g1 = bf_hi(gp[i]);
+                        const float h0 = silu(g0) * bf_lo(up[i]), h1 = silu(g1) * bf_hi(up[i]);
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(h0, h1);
+                        gp[i] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    stage_row_bf16(stage, lane, gp);
+                    flush_stage(stage, &tmD2, n, row_w, lane);
                 }
             } else {
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int n = n0 + c * 32;
-                    const int valid = min(32, p.n_out - n);
-                    if (valid <= 0) break;
-                    float v[32];
-                    tmem_ld32(t_lane + c * 32, v);
-                    const size_t o = (size_t)row * p.n_out + n;
-                    if (MODE == MODE_DOWN) {
-                        const float* b = p.bias0[e];
+                // this warp: columns n0 + h*128 .. +127, two chunks of 64
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) v[j] += b[n + j];
-                        store_bf16x32(p.D0 + o, v, valid);
-                    } else if (MODE == MODE_DHH) {
-                        // utils/Tensor.cpp:2020-2027 with dd = dHh
-                        float g[32], u[32];
-                        load_bf16x32(p.G + o, g, valid);
-                        load_bf16x32(p.U + o, u, valid);
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int n = n0 + h * 128 + cc * 64;
+                    float v0[32], v1[32];
+                    tmem_ld32(t_lane + h * 128 + cc * 64, v0);
+                    tmem_ld32(t_lane + h * 128 + cc * 64 + 32, v1);
+                    if (cc == 1) release_acc(pipe.acc_empty(buf), lane);
+                    if (n >= p.n_out) continue;                      // warp-uniform
+                    uint32_t pk[32];
+                    if (MODE == MODE_DOWN) {
+                        const float* bias = p.bias0[e];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const float sig = 1.0f / (1.0f + __expf(-g[j]));
-                            const float dd = v[j];
-                            v[j] = (dd * u[j]) * (sig * (1.0f + g[j] * (1.0f - sig)));   // dG
-                            u[j] = dd * (g[j] * sig);                                     // dU
+                            v0[j] += (n + j < p.n_out) ? bias[n + j] : 0.0f;
+                            v1[j] += (n + 32 + j < p.n_out) ? bias[n + 32 + j] : 0.0f;
                         }
-                        store_bf16x32(p.D0 + o, v, valid);
-                        store_bf16x32(p.D1 + o, u, valid);
+                        pack64(v0, v1, pk);
+                        stage_row_bf16(stage, lane, pk);
+                        flush_stage(stage, &tmD0, n, row_w, lane);
+                    } else if (MODE == MODE_DHH) {
+                        // utils/Tensor.cpp:2020-2027 with dd = dHh; G, U are this thread's row, 128 B each
+                        const size_t o = (size_t)(row_w + lane) * p.n_out + n;
+                        const int valid = min(64, p.n_out - n);
+                        uint32_t pu[32];
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            float (&v)[32] = half == 0 ? v0 : v1;
+                            float g[32], u[32];
+                            load_bf16x32(p.G + o + half * 32, g, valid - half * 32);
+                            load_bf16x32(p.U + o + half * 32, u, valid - half * 32);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float sig = __fdividef(1.0f, 1.0f + __expf(-g[j]));
+                                const float dd = v[j];
+                                v[j] = (dd * u[j]) * (sig * (1.0f + g[j] * (1.0f - sig)));   // dG
+                                u[j] = dd * (g[j] * sig);                                     // dU
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                __nv_bfloat162 x = __floats2bfloat162_rn(u[2 * i], u[2 * i + 1]);
+                                pu[half * 16 + i] = *reinterpret_cast<uint32_t*>(&x);
+                            }
+                        }
+                        pack64(v0, v1, pk);
+                        stage_row_bf16(stage, lane, pk);
+                        flush_stage(stage, &tmD0, n, row_w, lane);
+                        stage_row_bf16(stage, lane, pu);
+                        flush_stage(stage, &tmD1, n, row_w, lane);
                     } else {
-                        store_bf16x32(p.D0 + o, v, valid);
+                        pack64(v0, v1, pk);
+                        stage_row_bf16(stage, lane, pk);
+                        flush_stage(stage, &tmD0, n, row_w, lane);
                     }
                 }
             }
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores landed before exit
     }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
-    }
+    cta_teardown(tmem_base, warp);
 }
 
 // ---- weight gradients: grad[e][M,N] += A_e^T * B_e over the expert's rows ---------
@@ -370,106 +493,120 @@ struct WgradP {
     const int32_t* padded_offsets;
     int32_t* status;
     float* const* grad;
-    int M, N, n_tiles_n;
+    int M, N, n_tiles_m, n_tiles_n, E;
 };
 
+// Persistent over items (expert, m tile, n tile); experts without rows are skipped.
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const WgradP p)
 {
     extern __shared__ uint8_t smem_raw[];
-    const int e = blockIdx.y;
-    const int r0 = p.padded_offsets[e], r1 = p.padded_offsets[e + 1];
-    const int total_kb = (r1 - r0) / BK;
-    if (total_kb <= 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = (blockIdx.x / p.n_tiles_n) * BM, n0 = (blockIdx.x % p.n_tiles_n) * BN;
+    const int per_expert = p.n_tiles_m * p.n_tiles_n;
+    const int total_items = p.E * per_expert;
+    if ((int)blockIdx.x >= total_items) return;
 
-    Pipe pipe = carve(smem_raw);
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(pipe.full(s), 1);
-            mbar_init(pipe.empty(s), 1);
-        }
-        mbar_init(pipe.acc, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) tmem_alloc(pipe.tmem_slot, BN);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    uint32_t tmem_base;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(pipe.tmem_slot));
-
+    const Pipe pipe = carve(smem_raw);
+    const uint32_t tmem_base = cta_setup(pipe, warp);
     constexpr uint32_t BOX = 64 * BK * 2;      // one {64 MN elements, 64 rows} box = 8 KiB
+
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < total_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(pipe.empty(s), ((kb / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) break;
-                const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(pipe.full(s), STAGE_BYTES);
-                const int r = r0 + kb * BK;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                const int e = item / per_expert, r = item % per_expert;
+                const int r0 = p.padded_offsets[e], nkb = (p.padded_offsets[e + 1] - r0) / BK;
+                const int m0 = (r / p.n_tiles_n) * BM, n0 = (r % p.n_tiles_n) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(pipe.full(s), STAGE_BYTES);
+                    const int row = r0 + kb * BK;
 #pragma unroll
-                for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, &tmA, m0 + 64 * i, r, pipe.full(s));
+                    for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, &tmA, m0 + 64 * i, row, pipe.full(s));
 #pragma unroll
-                for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, &tmB, n0 + 64 * i, r, pipe.full(s));
+                    for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, &tmB, n0 + 64 * i, row, pipe.full(s));
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
-            for (int kb = 0; kb < total_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(pipe.full(s), (kb / STAGES) & 1, p.status, ERR_FULL_WAIT)) break;
+            uint32_t it = 0, t = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                const int e = item / per_expert;
+                const int nkb = (p.padded_offsets[e + 1] - p.padded_offsets[e]) / BK;
+                if (nkb <= 0) continue;
+                const uint32_t buf = t & 1u;
+                if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(pipe.tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(pipe.full(s), (it / STAGES) & 1, p.status, ERR_FULL_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(pipe.tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    // 16 reduction rows = two 8-row groups (1 KiB each); 64-element MN blocks are BOX apart
-                    const uint64_t ad = make_desc(a_addr + k * 2048, BOX, 1024);
-                    const uint64_t bd = make_desc(b_addr + k * 2048, BOX, 1024);
-                    umma_bf16(tmem_base, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 reduction rows = two 8-row groups (1 KiB each); 64-element MN blocks are BOX apart
+                        const uint64_t ad = make_desc(a_addr + k * 2048, BOX, 1024);
+                        const uint64_t bd = make_desc(b_addr + k * 2048, BOX, 1024);
+                        umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(pipe.empty(s));
                 }
-                umma_commit(pipe.empty(s));
+                umma_commit(pipe.acc_full(buf));
+                ++t;
             }
-            umma_commit(pipe.acc);
         }
     } else {
-        const int quarter = warp & 3;
-        const int m = m0 + quarter * 32 + lane;
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const bool ok = mbar_wait(pipe.acc, 0, p.status, ERR_ACC_WAIT);
-        tc_fence_after();
-        if (ok) {
-            float* g = p.grad[e];
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int n = n0 + c * 32;
-                const int valid = min(32, p.N - n);
-                if (valid <= 0) break;
-                float v[32];
-                tmem_ld32(t_lane + c * 32, v);             // warp-collective: every lane takes part
-                if (m < p.M) {
-                    float4* dst = reinterpret_cast<float4*>(g + (size_t)m * p.N + n);
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32][32] floats
+        uint32_t t = 0;
+        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+            const int e = item / per_expert, r = item % per_expert;
+            if (p.padded_offsets[e + 1] - p.padded_offsets[e] < BK) continue;
+            const uint32_t buf = t & 1u;
+            const int m_w = (r / p.n_tiles_n) * BM + q * 32;             // first output row of this warp
+            const int n_w = (r % p.n_tiles_n) * BN + h * 128;            // first output column of this warp
+            if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
+            tc_fence_after();
+            const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + h * 128;
+            float v[4][32];
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        if (q * 4 < valid) {
-                            float4 t = dst[q];
-                            t.x += v[q * 4 + 0]; t.y += v[q * 4 + 1]; t.z += v[q * 4 + 2]; t.w += v[q * 4 + 3];
-                            dst[q] = t;
-                        }
-                    }
+            for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + c * 32, v[c]);
+            release_acc(pipe.acc_empty(buf), lane);
+            float* g = p.grad[e];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int n = n_w + c * 32;
+                if (n >= p.N) break;
+                // transpose through shared memory so that each RED covers one 128-byte row segment
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stage[lane * 32 + (j ^ lane)] = v[c][j];
+                __syncwarp();
+                const int col = n + lane;
+#pragma unroll 4
+                for (int rr = 0; rr < 32; ++rr) {
+                    const int m = m_w + rr;
+                    const float x = stage[rr * 32 + (lane ^ rr)];          // column (lane) of row rr
+                    if (m < p.M && col < p.N) atomicAdd(g + (size_t)m * p.N + col, x);
                 }
+                __syncwarp();
             }
+            ++t;
         }
     }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, BN);
-    }
+    cta_teardown(tmem_base, warp);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------
@@ -510,10 +647,13 @@ struct TcState {
     const void* ws = nullptr;
     int n_tokens = -1;
     bool attr_set = false;
-    // K-major (box 64 x 128 rows)
+    int sms = 0;
+    // K-major operand loads (box 64 x 128 rows)
     CUtensorMap Xg, Hh, dYg, dG, dU, WgT, WuT, WdT, Wg, Wu, Wd;
-    // reduction-over-rows operands (box 64 x 64 rows)
+    // reduction-over-rows operand loads (box 64 x 64 rows)
     CUtensorMap Xg_t, Hh_t, dYg_t, dG_t, dU_t;
+    // epilogue stores (box 64 x 32 rows)
+    CUtensorMap G_s, U_s, Hh_s, Yg_s, dG_s, dU_s, dXg_s;
 };
 
 int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
@@ -526,6 +666,7 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
         MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DHH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
         s->attr_set = true;
     }
     if (s->ws == ws && s->n_tokens == w.n_tokens) return 0;
@@ -547,12 +688,20 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->dYg_t, ws + w.dYg, rc, C, 64));
     MGPT_TRY(make_map(&s->dG_t, ws + w.dG, rc, H, 64));
     MGPT_TRY(make_map(&s->dU_t, ws + w.dU, rc, H, 64));
+    MGPT_TRY(make_map(&s->G_s, ws + w.G, rc, H, 32));
+    MGPT_TRY(make_map(&s->U_s, ws + w.U, rc, H, 32));
+    MGPT_TRY(make_map(&s->Hh_s, ws + w.Hh, rc, H, 32));
+    MGPT_TRY(make_map(&s->Yg_s, ws + w.Yg, rc, C, 32));
+    MGPT_TRY(make_map(&s->dG_s, ws + w.dG, rc, H, 32));
+    MGPT_TRY(make_map(&s->dU_s, ws + w.dU, rc, H, 32));
+    MGPT_TRY(make_map(&s->dXg_s, ws + w.dXg, rc, C, 32));
     s->ws = ws;
     s->n_tokens = w.n_tokens;
     return 0;
 }
 
 int cdiv(int a, int b) { return (a + b - 1) / b; }
+int imin(int a, int b) { return a < b ? a : b; }
 
 }  // namespace
 
@@ -565,21 +714,20 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
     p.status = (int32_t*)(ws + w.status);
-    // gate/up + SwiGLU: K = C, 128 hidden units per CTA
-    p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H;
-    p.D0 = (bf16*)(ws + w.G); p.D1 = (bf16*)(ws + w.U); p.D2 = (bf16*)(ws + w.Hh);
+    // gate/up + SwiGLU: K = C, 128 hidden units per item
+    p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN / 2);
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
     L->stage_begin(ST_GATEUP, st);
-    tc_rows_kernel<MODE_GATEUP><<<dim3(cdiv(d.H, BN / 2), w.max_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->Xg, s->Xg, s->WgT, s->WuT, p);
+    tc_rows_kernel<MODE_GATEUP><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+        s->Xg, s->Xg, s->WgT, s->WuT, s->G_s, s->U_s, s->Hh_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<gateup>");
     L->stage_end(ST_GATEUP, st);
     // down: K = H
-    p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C;
-    p.D0 = (bf16*)(ws + w.Yg); p.D1 = p.D2 = nullptr; p.bias0 = L->master.bd; p.bias1 = nullptr;
+    p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
+    p.bias0 = L->master.bd; p.bias1 = nullptr;
     L->stage_begin(ST_DOWN, st);
-    tc_rows_kernel<MODE_DOWN><<<dim3(cdiv(d.C, BN), w.max_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->Hh, s->Hh, s->WdT, s->WdT, p);
+    tc_rows_kernel<MODE_DOWN><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+        s->Hh, s->Hh, s->WdT, s->WdT, s->Yg_s, s->Yg_s, s->Yg_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<down>");
     L->stage_end(ST_DOWN, st);
     return 0;
@@ -595,20 +743,18 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
     p.status = (int32_t*)(ws + w.status);
     // dHh = dYg * Wd^T  (K = C), SwiGLU backward in the epilogue
-    p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H;
-    p.D0 = (bf16*)(ws + w.dG); p.D1 = (bf16*)(ws + w.dU);
+    p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN);
     p.G = (const bf16*)(ws + w.G); p.U = (const bf16*)(ws + w.U);
     L->stage_begin(ST_DHH, st);
-    tc_rows_kernel<MODE_DHH><<<dim3(cdiv(d.H, BN), w.max_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->dYg, s->dYg, s->Wd, s->Wd, p);
+    tc_rows_kernel<MODE_DHH><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+        s->dYg, s->dYg, s->Wd, s->Wd, s->dG_s, s->dU_s, s->dU_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<dhh>");
     L->stage_end(ST_DHH, st);
     // dXg = dG * Wg^T + dU * Wu^T  (K = 2H)
-    p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C;
-    p.D0 = (bf16*)(ws + w.dXg); p.D1 = nullptr;
+    p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
     L->stage_begin(ST_DXG, st);
-    tc_rows_kernel<MODE_DXG><<<dim3(cdiv(d.C, BN), w.max_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->dG, s->dU, s->Wg, s->Wu, p);
+    tc_rows_kernel<MODE_DXG><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+        s->dG, s->dU, s->Wg, s->Wu, s->dXg_s, s->dXg_s, s->dXg_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<dxg>");
     L->stage_end(ST_DXG, st);
     if (!L->has_grad) return 0;
@@ -616,20 +762,21 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     WgradP g = {};
     g.padded_offsets = (const int32_t*)(ws + w.padded_offsets);
     g.status = (int32_t*)(ws + w.status);
+    g.E = d.E;
     L->stage_begin(ST_WGRAD, st);
     // gWg += Xg^T dG, gWu += Xg^T dU   [C,H]
-    g.M = d.C; g.N = d.H; g.n_tiles_n = cdiv(d.H, BN);
-    dim3 gCH(cdiv(d.C, BM) * g.n_tiles_n, d.E);
+    g.M = d.C; g.N = d.H; g.n_tiles_m = cdiv(d.C, BM); g.n_tiles_n = cdiv(d.H, BN);
+    const int items_ch = d.E * g.n_tiles_m * g.n_tiles_n;
     g.grad = L->master.gWg;
-    tc_wgrad_kernel<<<gCH, TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, g);
+    tc_wgrad_kernel<<<imin(s->sms, items_ch), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wg>");
     g.grad = L->master.gWu;
-    tc_wgrad_kernel<<<gCH, TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dU_t, g);
+    tc_wgrad_kernel<<<imin(s->sms, items_ch), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dU_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wu>");
     // gWd += Hh^T dYg   [H,C]
-    g.M = d.H; g.N = d.C; g.n_tiles_n = cdiv(d.C, BN);
+    g.M = d.H; g.N = d.C; g.n_tiles_m = cdiv(d.H, BM); g.n_tiles_n = cdiv(d.C, BN);
     g.grad = L->master.gWd;
-    tc_wgrad_kernel<<<dim3(cdiv(d.H, BM) * g.n_tiles_n, d.E), TC_THREADS, SMEM_BYTES, st>>>(s->Hh_t, s->dYg_t, g);
+    tc_wgrad_kernel<<<imin(s->sms, d.E * g.n_tiles_m * g.n_tiles_n), TC_THREADS, SMEM_BYTES, st>>>(s->Hh_t, s->dYg_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wd>");
     L->stage_end(ST_WGRAD, st);
     return 0;
