@@ -70,6 +70,17 @@ Workspace make_workspace(const Dims& d, int n_tokens)
     w.dXg = take(rc * C * ab);
     w.d_top_p = take(N * k * 4);
     w.dlogits = take(N * E * 4);
+    // router weight gradient: per-token-chunk partial sums, reduced in a second pass
+    {
+        const int e4 = (d.E + 3) / 4, ch_per_cta = (256 / e4) * 4;
+        const int cblocks = (d.C + ch_per_cta - 1) / ch_per_cta;
+        int chunks = 296 / (cblocks > 0 ? cblocks : 1);
+        if (chunks > 64) chunks = 64;
+        if (chunks > n_tokens) chunks = n_tokens;
+        if (chunks < 1) chunks = 1;
+        w.rw_chunks = chunks;
+    }
+    w.rw_part = take((size_t)w.rw_chunks * (C * E + E) * 4);
     w.total = off;
     return w;
 }

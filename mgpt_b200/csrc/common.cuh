@@ -62,10 +62,10 @@ struct Workspace {
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries
-    size_t dYg, dG, dU, dXg, d_top_p, dlogits;
+    size_t dYg, dG, dU, dXg, d_top_p, dlogits, rw_part;
     size_t total;
     // derived sizes
-    int n_tokens, R, max_tiles, row_cap, plan_blocks;
+    int n_tokens, R, max_tiles, row_cap, plan_blocks, rw_chunks;
     size_t act_bytes;   // bytes per activation element (2 or 4)
 };
 

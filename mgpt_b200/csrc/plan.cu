@@ -219,22 +219,58 @@ combine_bwd_kernel(const TIo* __restrict__ dy, const TAct* __restrict__ Yg, cons
     if (lane == 0) d_top_p[src] = dot;
 }
 
-// Column sums of one activation matrix over each expert's (padded) rows:
-// gb[e][c] += sum_rows M[p,c]  (layers/LinearLayer.cpp:56-57).  grid (E, col blocks, row splits)
-constexpr int BG_ROWS = 512;
+// Column sums over each expert's rows, for the three bias gradients in one launch:
+// gbd[e] += colsum(dYg), gbg[e] += colsum(dG), gbu[e] += colsum(dU)  (layers/LinearLayer.cpp:56-57).
+// One CTA = one 128-row tile (one expert) x 256 columns; a thread reads 8 columns (16 bytes) of
+// every 8th row, the 8 row lanes are folded in shared memory, then one atomicAdd per column.
+struct BiasGradArgs {
+    const void* M[3];
+    float* const* gb[3];
+    int cols[3];
+    const int32_t* tile_expert;
+    const int32_t* n_tiles;
+};
+
 template <typename TAct>
-__global__ void __launch_bounds__(128)
-bias_grad_kernel(const TAct* __restrict__ M, int cols, const int32_t* __restrict__ padded_offsets,
-                 float* const* __restrict__ gb)
+__global__ void __launch_bounds__(256) bias_grad_kernel(BiasGradArgs a)
 {
-    const int e = blockIdx.x;
-    const int c = blockIdx.y * 128 + threadIdx.x;
-    const int r0 = padded_offsets[e] + blockIdx.z * BG_ROWS;
-    const int r1 = min(padded_offsets[e + 1], r0 + BG_ROWS);
-    if (c >= cols || r0 >= r1) return;
-    float s = 0.0f;
-    for (int r = r0; r < r1; ++r) s += to_f32(M[(size_t)r * cols + c]);
-    atomicAdd(&gb[e][c], s);
+    __shared__ float red[8][256 + 8];
+    const int tile = blockIdx.x, which = blockIdx.z;
+    if (tile >= *a.n_tiles) return;
+    const int cols = a.cols[which];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.y * 256 + tx * 8;
+    float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (c < cols) {
+        const TAct* base = (const TAct*)a.M[which] + (size_t)tile * ROW_TILE * cols + c;
+#pragma unroll 4
+        for (int r = ty; r < ROW_TILE; r += 8) {
+            const TAct* p = base + (size_t)r * cols;
+            if constexpr (sizeof(TAct) == 2) {
+                const uint4 u = *reinterpret_cast<const uint4*>(p);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s[2 * i] += __uint_as_float(w[i] << 16);
+                    s[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+                }
+            } else {
+                const float4 f0 = *reinterpret_cast<const float4*>(p), f1 = *reinterpret_cast<const float4*>(p + 4);
+                s[0] += f0.x; s[1] += f0.y; s[2] += f0.z; s[3] += f0.w;
+                s[4] += f1.x; s[5] += f1.y; s[6] += f1.z; s[7] += f1.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[ty][tx * 8 + i] = s[i];
+    __syncthreads();
+    const int col = blockIdx.y * 256 + threadIdx.x;
+    if (col < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += red[r][threadIdx.x];
+        atomicAdd(&a.gb[which][a.tile_expert[tile]][col], t);
+    }
 }
 
 }  // namespace
@@ -323,24 +359,17 @@ int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* 
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
 {
     const Dims& d = L->d;
-    const int32_t* poff = (const int32_t*)(ws + w.padded_offsets);
-    const int zs = (w.row_cap + BG_ROWS - 1) / BG_ROWS;
-    dim3 gH(d.E, (d.H + 127) / 128, zs), gC(d.E, (d.C + 127) / 128, zs);
-    if (w.act_bytes == 4) {
-        bias_grad_kernel<float><<<gC, 128, 0, st>>>((const float*)(ws + w.dYg), d.C, poff, L->master.gbd);
-        MGPT_LAUNCHED("bias_grad_kernel");
-        bias_grad_kernel<float><<<gH, 128, 0, st>>>((const float*)(ws + w.dG), d.H, poff, L->master.gbg);
-        MGPT_LAUNCHED("bias_grad_kernel");
-        bias_grad_kernel<float><<<gH, 128, 0, st>>>((const float*)(ws + w.dU), d.H, poff, L->master.gbu);
-        MGPT_LAUNCHED("bias_grad_kernel");
-    } else {
-        bias_grad_kernel<bf16><<<gC, 128, 0, st>>>((const bf16*)(ws + w.dYg), d.C, poff, L->master.gbd);
-        MGPT_LAUNCHED("bias_grad_kernel");
-        bias_grad_kernel<bf16><<<gH, 128, 0, st>>>((const bf16*)(ws + w.dG), d.H, poff, L->master.gbg);
-        MGPT_LAUNCHED("bias_grad_kernel");
-        bias_grad_kernel<bf16><<<gH, 128, 0, st>>>((const bf16*)(ws + w.dU), d.H, poff, L->master.gbu);
-        MGPT_LAUNCHED("bias_grad_kernel");
-    }
+    BiasGradArgs a;
+    a.M[0] = ws + w.dYg; a.M[1] = ws + w.dG; a.M[2] = ws + w.dU;
+    a.gb[0] = L->master.gbd; a.gb[1] = L->master.gbg; a.gb[2] = L->master.gbu;
+    a.cols[0] = d.C; a.cols[1] = d.H; a.cols[2] = d.H;
+    a.tile_expert = (const int32_t*)(ws + w.tile_expert);
+    a.n_tiles = (const int32_t*)(ws + w.n_tiles);
+    const int mc = d.C > d.H ? d.C : d.H;
+    dim3 grid(w.max_tiles, (mc + 255) / 256, 3);
+    if (w.act_bytes == 4) bias_grad_kernel<float><<<grid, 256, 0, st>>>(a);
+    else bias_grad_kernel<bf16><<<grid, 256, 0, st>>>(a);
+    MGPT_LAUNCHED("bias_grad_kernel");
     return 0;
 }
 

@@ -17,59 +17,66 @@ namespace mgpt {
 
 namespace {
 
-constexpr int R_WARPS = 8;     // warps per CTA
-constexpr int R_TPW = 8;       // tokens per warp (independent accumulation chains)
-constexpr int R_TOK = R_WARPS * R_TPW;
+constexpr int R_WARPS = 4;     // warps per CTA
 constexpr int R_CK = 32;       // channels staged per step
+constexpr int R_XPAD = 36;     // padded row of the staged x tile (floats): rows land in distinct banks
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 
-// One warp owns R_TPW tokens; lane l owns experts l, l+32, ... (EPL of them).
-template <typename TIn, int EPL>
+// EL lanes share one token (lane % EL owns experts el, el+32, ...: EPL of them, EPL > 1 only
+// with EL = 32); a warp therefore works on 32/EL tokens at once and on TPW such groups in
+// sequence, which gives every lane TPW*EPL independent accumulation chains.
+template <typename TIn, int EL, int EPL, int TPW>
 __global__ void __launch_bounds__(R_WARPS * 32)
 router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ br,
                   int N, int C, int E, int k,
                   float* __restrict__ logits, float* __restrict__ probs,
                   int32_t* __restrict__ top_idx, float* __restrict__ top_p)
 {
-    __shared__ __align__(16) float xs[R_TOK][R_CK];
-    __shared__ float wsm[R_CK][EPL * 32];
+    constexpr int SUB = 32 / EL;                    // tokens per warp pass
+    constexpr int TOK_W = TPW * SUB;                // tokens per warp
+    constexpr int TOK = R_WARPS * TOK_W;            // tokens per CTA
+    constexpr int WCOLS = EPL * EL;                 // staged expert columns
+    __shared__ __align__(16) float xs[TOK][R_XPAD];
+    __shared__ float wsm[R_CK][WCOLS];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tok0 = blockIdx.x * R_TOK;
+    const int sub = lane / EL, el = lane % EL;
+    const int tok0 = blockIdx.x * TOK;
 
-    float acc[R_TPW][EPL];
+    float acc[TPW][EPL];
 #pragma unroll
-    for (int t = 0; t < R_TPW; ++t)
+    for (int t = 0; t < TPW; ++t)
 #pragma unroll
         for (int i = 0; i < EPL; ++i) acc[t][i] = 0.0f;
 
     for (int c0 = 0; c0 < C; c0 += R_CK) {
         // stage x[tok0.., c0..c0+31] and Wr[c0..c0+31, :] (zero padded: adding 0*w is exact)
-        for (int i = tid; i < R_TOK * R_CK; i += R_WARPS * 32) {
-            int t = i / R_CK, j = i % R_CK;
-            int tok = tok0 + t, c = c0 + j;
+        for (int i = tid; i < TOK * R_CK; i += R_WARPS * 32) {
+            const int t = i / R_CK, j = i % R_CK;
+            const int tok = tok0 + t, c = c0 + j;
             xs[t][j] = (tok < N && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
         }
-        for (int i = tid; i < R_CK * EPL * 32; i += R_WARPS * 32) {
-            int j = i / (EPL * 32), e = i % (EPL * 32);
-            int c = c0 + j;
+        for (int i = tid; i < R_CK * WCOLS; i += R_WARPS * 32) {
+            const int j = i / WCOLS, e = i % WCOLS;
+            const int c = c0 + j;
             wsm[j][e] = (c < C && e < E) ? Wr[(size_t)c * E + e] : 0.0f;
         }
         __syncthreads();
 #pragma unroll 2
         for (int j = 0; j < R_CK; j += 4) {
-            float4 xv[R_TPW];
+            float4 xv[TPW];
 #pragma unroll
-            for (int t = 0; t < R_TPW; ++t) xv[t] = *reinterpret_cast<const float4*>(&xs[warp * R_TPW + t][j]);
+            for (int t = 0; t < TPW; ++t)
+                xv[t] = *reinterpret_cast<const float4*>(&xs[warp * TOK_W + t * SUB + sub][j]);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
                 float w[EPL];
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) w[i] = wsm[j + jj][lane + 32 * i];
+                for (int i = 0; i < EPL; ++i) w[i] = wsm[j + jj][el + 32 * i];
 #pragma unroll
-                for (int t = 0; t < R_TPW; ++t) {
+                for (int t = 0; t < TPW; ++t) {
                     const float xe = jj == 0 ? xv[t].x : jj == 1 ? xv[t].y : jj == 2 ? xv[t].z : xv[t].w;
 #pragma unroll
                     for (int i = 0; i < EPL; ++i) acc[t][i] = __fadd_rn(acc[t][i], __fmul_rn(xe, w[i]));
@@ -81,38 +88,39 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 
     float bias[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) bias[i] = (lane + 32 * i < E) ? br[lane + 32 * i] : 0.0f;
+    for (int i = 0; i < EPL; ++i) bias[i] = (el + 32 * i < E) ? br[el + 32 * i] : 0.0f;
 
     const unsigned full = 0xffffffffu;
 #pragma unroll
-    for (int t = 0; t < R_TPW; ++t) {
-        const int tok = tok0 + warp * R_TPW + t;
-        if (tok >= N) continue;                    // warp-uniform
+    for (int t = 0; t < TPW; ++t) {
+        // every lane runs the warp-level steps (tokens past N compute on zeros and store nothing)
+        const int tok = tok0 + warp * TOK_W + t * SUB + sub;
+        const bool live = tok < N;
         float lg[EPL], p[EPL];
         float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
             lg[i] = __fadd_rn(acc[t][i], bias[i]);
-            if (lane + 32 * i < E) mx = fmaxf(mx, lg[i]);
+            if (el + 32 * i < E) mx = fmaxf(mx, lg[i]);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
+        for (int o = EL / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
         // exp through double and one rounding: agrees with a correctly rounded expf
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) p[i] = (float)exp((double)__fsub_rn(lg[i], mx));
+        for (int i = 0; i < EPL; ++i) p[i] = (el + 32 * i < E) ? (float)exp((double)__fsub_rn(lg[i], mx)) : 0.0f;
         // the reference adds the E terms in index order
         float sum = 0.0f;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-            const int lim = min(32, E - 32 * i);
-            for (int l = 0; l < lim; ++l) sum = __fadd_rn(sum, __shfl_sync(full, p[i], l));
+            const int lim = min(EL, E - 32 * i);
+            for (int l = 0; l < lim; ++l) sum = __fadd_rn(sum, __shfl_sync(full, p[i], l, EL));
         }
         const float inv = __fdiv_rn(1.0f, fmaxf(sum, 1e-15f));
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
             p[i] = fminf(fmaxf(__fmul_rn(p[i], inv), 1e-7f), 1.0f);
-            const int e = lane + 32 * i;
-            if (e < E) {
+            const int e = el + 32 * i;
+            if (live && e < E) {
                 probs[(size_t)tok * E + e] = p[i];
                 if (logits) logits[(size_t)tok * E + e] = lg[i];
             }
@@ -126,14 +134,14 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
             int bi = 0x7fffffff;
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
-                const int e = lane + 32 * i;
+                const int e = el + 32 * i;
                 if (e < E && !(taken & (1u << i)) && p[i] > bv) {
                     bv = p[i];
                     bi = e;
                 }
             }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
+            for (int o = EL / 2; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(full, bv, o);
                 const int oi = __shfl_xor_sync(full, bi, o);
                 if (ov > bv || (ov == bv && oi < bi)) {
@@ -141,15 +149,15 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
                     bi = oi;
                 }
             }
-            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-            if (lane == r) {
+            if ((bi & 31) == el && bi != 0x7fffffff) taken |= 1u << (bi >> 5);
+            if (el == r) {
                 my_idx = bi;
                 my_val = bv;
             }
         }
-        if (lane < k) {
-            top_idx[(size_t)tok * k + lane] = my_idx;
-            top_p[(size_t)tok * k + lane] = my_val;
+        if (live && el < k) {
+            top_idx[(size_t)tok * k + el] = my_idx;
+            top_p[(size_t)tok * k + el] = my_val;
         }
     }
 }
@@ -199,122 +207,187 @@ router_dlogits_kernel(const float* __restrict__ probs, const int32_t* __restrict
 // dx[tok,:] = sum_j dXg[pos(tok,j),:] (ascending slot order, as the reference's
 // scatter-add visits them, utils/Tensor.cpp:1451-1458) + dlogits[tok,:] * Wr^T
 // (layers/LinearLayer.cpp:68-69, layers/MoELayer.cpp:217).
+// One CTA: DX_TOK tokens x one channel chunk (8192/E_pad channels, Wr^T of the chunk in shared
+// memory); a thread owns 8 consecutive channels and uses 16-byte accesses.
 constexpr int DX_TOK = 32;
+constexpr int DX_WS_FLOATS = 8192;
 template <typename TAct, typename TIo>
 __global__ void __launch_bounds__(256)
 router_dx_kernel(const TAct* __restrict__ dXg, const int32_t* __restrict__ pos, const float* __restrict__ dlogits,
-                 const float* __restrict__ Wr, int N, int C, int E, int k, TIo* __restrict__ dx)
+                 const float* __restrict__ Wr, int N, int C, int E, int k, int chunk, TIo* __restrict__ dx)
 {
-    extern __shared__ float dl[];                 // [DX_TOK][E]
+    extern __shared__ __align__(16) float sm_dx[];
+    float* wt = sm_dx;                         // [E][chunk]  (Wr^T of this channel chunk)
+    float* dl = sm_dx + DX_WS_FLOATS;          // [DX_TOK][E]
     __shared__ int spos[DX_TOK][MAX_TOPK];
-    const int tok0 = blockIdx.x * DX_TOK;
+    const int tok0 = blockIdx.x * DX_TOK, c_base = blockIdx.y * chunk;
+    for (int i = threadIdx.x; i < chunk * E; i += blockDim.x) {
+        const int c = i / E, e = i % E;
+        wt[e * chunk + c] = (c_base + c < C) ? Wr[(size_t)(c_base + c) * E + e] : 0.0f;
+    }
     for (int i = threadIdx.x; i < DX_TOK * E; i += blockDim.x) {
-        const int t = i / E, e = i % E;
-        dl[i] = (tok0 + t < N) ? dlogits[(size_t)(tok0 + t) * E + e] : 0.0f;
+        const int t = i / E;
+        dl[i] = (tok0 + t < N) ? dlogits[(size_t)(tok0 + t) * E + (i % E)] : 0.0f;
     }
     if (threadIdx.x < DX_TOK) {
         const int tok = tok0 + threadIdx.x;
         int v[MAX_TOPK];
-        for (int j = 0; j < k; ++j) v[j] = tok < N ? pos[(size_t)tok * k + j] : 0;
-        for (int a = 1; a < k; ++a) {             // insertion sort, k <= 8
-            int key = v[a], b = a - 1;
-            while (b >= 0 && v[b] > key) {
-                v[b + 1] = v[b];
-                --b;
-            }
-            v[b + 1] = key;
-        }
-        for (int j = 0; j < k; ++j) spos[threadIdx.x][j] = v[j];
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) v[j] = (j < k && tok < N) ? pos[(size_t)tok * k + j] : 0x7fffffff;
+#pragma unroll
+        for (int a = 0; a < MAX_TOPK - 1; ++a)
+#pragma unroll
+            for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
+                if (v[b] > v[b + 1]) {
+                    const int tmp = v[b];
+                    v[b] = v[b + 1];
+                    v[b + 1] = tmp;
+                }
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) spos[threadIdx.x][j] = v[j];
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc[DX_TOK];
+    const int groups = chunk / 8;                       // 8-channel groups in the chunk
+    const int g = threadIdx.x % groups, tl = threadIdx.x / groups, tstep = blockDim.x / groups;
+    const int c = c_base + g * 8;
+    if (c >= C) return;
+    for (int t = tl; t < DX_TOK; t += tstep) {
+        const int tok = tok0 + t;
+        if (tok >= N) break;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int e = 0; e < E; ++e) {
+            const float d = dl[t * E + e];
+            const float4 w0 = *reinterpret_cast<const float4*>(&wt[e * chunk + g * 8]);
+            const float4 w1 = *reinterpret_cast<const float4*>(&wt[e * chunk + g * 8 + 4]);
+            acc[0] = fmaf(d, w0.x, acc[0]); acc[1] = fmaf(d, w0.y, acc[1]);
+            acc[2] = fmaf(d, w0.z, acc[2]); acc[3] = fmaf(d, w0.w, acc[3]);
+            acc[4] = fmaf(d, w1.x, acc[4]); acc[5] = fmaf(d, w1.y, acc[5]);
+            acc[6] = fmaf(d, w1.z, acc[6]); acc[7] = fmaf(d, w1.w, acc[7]);
+        }
+        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j = 0; j < k; ++j) {
+            const TAct* r = dXg + (size_t)spos[t][j] * C + c;
+            if constexpr (sizeof(TAct) == 2) {
+                const uint4 u = *reinterpret_cast<const uint4*>(r);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int t = 0; t < DX_TOK; ++t) acc[t] = 0.0f;
-        for (int e0 = 0; e0 < E; e0 += 8) {
-            float w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = (e0 + i < E) ? Wr[(size_t)c * E + e0 + i] : 0.0f;
-#pragma unroll
-            for (int t = 0; t < DX_TOK; ++t)
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (e0 + i < E) acc[t] = __fadd_rn(acc[t], __fmul_rn(dl[t * E + e0 + i], w[i]));
+                for (int i = 0; i < 4; ++i) {
+                    s[2 * i] = __fadd_rn(s[2 * i], __uint_as_float(w[i] << 16));
+                    s[2 * i + 1] = __fadd_rn(s[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+                }
+            } else {
+                const float4 a = *reinterpret_cast<const float4*>(r), b = *reinterpret_cast<const float4*>(r + 4);
+                s[0] = __fadd_rn(s[0], a.x); s[1] = __fadd_rn(s[1], a.y); s[2] = __fadd_rn(s[2], a.z); s[3] = __fadd_rn(s[3], a.w);
+                s[4] = __fadd_rn(s[4], b.x); s[5] = __fadd_rn(s[5], b.y); s[6] = __fadd_rn(s[6], b.z); s[7] = __fadd_rn(s[7], b.w);
+            }
         }
 #pragma unroll
-        for (int t = 0; t < DX_TOK; ++t) {
-            const int tok = tok0 + t;
-            if (tok >= N) continue;
-            float s = 0.0f;
-            for (int j = 0; j < k; ++j) s = __fadd_rn(s, to_f32(dXg[(size_t)spos[t][j] * C + c]));
-            const float r = __fadd_rn(s, acc[t]);
-            if constexpr (sizeof(TIo) == 4) dx[(size_t)tok * C + c] = r;
-            else dx[(size_t)tok * C + c] = __float2bfloat16(r);
+        for (int i = 0; i < 8; ++i) s[i] = __fadd_rn(s[i], acc[i]);
+        TIo* o = dx + (size_t)tok * C + c;
+        if constexpr (sizeof(TIo) == 4) {
+            *reinterpret_cast<float4*>(o) = make_float4(s[0], s[1], s[2], s[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        } else {
+            uint4 u;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(s[0], s[1]), h1 = __floats2bfloat162_rn(s[2], s[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(s[4], s[5]), h3 = __floats2bfloat162_rn(s[6], s[7]);
+            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(o) = u;
         }
     }
 }
 
-// gWr[c,e] += sum_tok x[tok,c]*dlogits[tok,e];  gbr[e] += sum_tok dlogits[tok,e]
-// (layers/LinearLayer.cpp:56-66).  grid (ceil(C/32), token chunks).
-constexpr int WG_CH = 32, WG_TT = 32, WG_CHUNK = 256;
+// Router weight gradient in two deterministic steps (layers/LinearLayer.cpp:56-66):
+//   part[chunk][c][e] = sum over the chunk's tokens of x[tok,c]*dlogits[tok,e]   (and column sums of dlogits)
+//   gWr[c,e] += sum_chunk part[chunk][c][e];  gbr[e] += sum_chunk partb[chunk][e]
+// A thread keeps a 4 channel x 4 expert block of accumulators.
 template <typename TIo>
 __global__ void __launch_bounds__(256)
-router_wgrad_kernel(const TIo* __restrict__ x, const float* __restrict__ dlogits, int N, int C, int E,
-                    float* __restrict__ gWr, float* __restrict__ gbr)
+router_wgrad_partial_kernel(const TIo* __restrict__ x, const float* __restrict__ dlogits, int N, int C, int E,
+                            int tok_per_chunk, float* __restrict__ part, float* __restrict__ partb)
 {
-    extern __shared__ float sm[];
-    float* xs = sm;                  // [WG_TT][WG_CH]
-    float* dls = sm + WG_TT * WG_CH; // [WG_TT][E]
-    const int c_l = threadIdx.x & 31, eg = threadIdx.x >> 5;
-    const int c0 = blockIdx.x * WG_CH;
-    const int t_begin = blockIdx.y * WG_CHUNK, t_end = min(N, t_begin + WG_CHUNK);
-    float acc[MAX_EXPERTS / 8];
+    const int E4 = (E + 3) / 4;                         // expert groups of 4
+    const int cg_per_cta = 256 / E4;                    // channel groups of 4 handled by this CTA
+    const int eg = threadIdx.x % E4, cgi = threadIdx.x / E4;
+    if (cgi >= cg_per_cta) return;
+    const int c = (blockIdx.x * cg_per_cta + cgi) * 4, e0 = eg * 4;
+    const int t0 = blockIdx.y * tok_per_chunk, t1 = min(N, t0 + tok_per_chunk);
+    const bool c_ok = c < C;
+    float acc[4][4] = {};
+    float bs[4] = {0, 0, 0, 0};
+    for (int tok = t0; tok < t1; ++tok) {
+        float xv[4] = {0, 0, 0, 0}, dv[4];
+        if (c_ok) {
+            if constexpr (sizeof(TIo) == 2) {
+                const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)tok * C + c);
+                xv[0] = __uint_as_float(u.x << 16); xv[1] = __uint_as_float(u.x & 0xffff0000u);
+                xv[2] = __uint_as_float(u.y << 16); xv[3] = __uint_as_float(u.y & 0xffff0000u);
+            } else {
+                const float4 f = *reinterpret_cast<const float4*>(x + (size_t)tok * C + c);
+                xv[0] = f.x; xv[1] = f.y; xv[2] = f.z; xv[3] = f.w;
+            }
+        }
 #pragma unroll
-    for (int i = 0; i < MAX_EXPERTS / 8; ++i) acc[i] = 0.0f;
-    float bsum = 0.0f;
-    for (int t0 = t_begin; t0 < t_end; t0 += WG_TT) {
-        for (int i = threadIdx.x; i < WG_TT * WG_CH; i += blockDim.x) {
-            const int t = i / WG_CH, j = i % WG_CH;
-            const int tok = t0 + t, c = c0 + j;
-            xs[i] = (tok < t_end && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
-        }
-        for (int i = threadIdx.x; i < WG_TT * E; i += blockDim.x) {
-            const int t = i / E;
-            dls[i] = (t0 + t < t_end) ? dlogits[(size_t)(t0 + t) * E + (i % E)] : 0.0f;
-        }
-        __syncthreads();
-        for (int t = 0; t < WG_TT; ++t) {
-            const float xv = xs[t * WG_CH + c_l];
+        for (int j = 0; j < 4; ++j) dv[j] = (e0 + j < E) ? dlogits[(size_t)tok * E + e0 + j] : 0.0f;
 #pragma unroll
-            for (int i = 0; i < MAX_EXPERTS / 8; ++i)
-                if (eg + 8 * i < E) acc[i] = fmaf(xv, dls[t * E + eg + 8 * i], acc[i]);
-        }
-        if (blockIdx.x == 0 && threadIdx.x < E)
-            for (int t = 0; t < WG_TT; ++t) bsum += dls[t * E + threadIdx.x];
-        __syncthreads();
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], dv[j], acc[i][j]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bs[j] += dv[j];
     }
-    const int c = c0 + c_l;
-    if (c < C) {
+    if (c_ok) {
+        float* dst = part + ((size_t)blockIdx.y * C + c) * E;
 #pragma unroll
-        for (int i = 0; i < MAX_EXPERTS / 8; ++i)
-            if (eg + 8 * i < E) atomicAdd(&gWr[(size_t)c * E + eg + 8 * i], acc[i]);
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (e0 + j < E) dst[(size_t)i * E + e0 + j] = acc[i][j];
     }
-    if (blockIdx.x == 0 && threadIdx.x < E) atomicAdd(&gbr[threadIdx.x], bsum);
+    if (blockIdx.x == 0 && cgi == 0)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (e0 + j < E) partb[(size_t)blockIdx.y * E + e0 + j] = bs[j];
+}
+
+__global__ void __launch_bounds__(256)
+router_wgrad_reduce_kernel(const float* __restrict__ part, const float* __restrict__ partb, int n_chunks, int CE, int E,
+                           float* __restrict__ gWr, float* __restrict__ gbr)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < CE) {
+        float s = 0.0f;
+        for (int ch = 0; ch < n_chunks; ++ch) s += part[(size_t)ch * CE + i];
+        gWr[i] += s;
+    }
+    if (i < E) {
+        float s = 0.0f;
+        for (int ch = 0; ch < n_chunks; ++ch) s += partb[(size_t)ch * E + i];
+        gbr[i] += s;
+    }
+}
+
+template <typename TIn, int EL, int EPL, int TPW>
+int router_fwd_launch(const TIn* x, const float* Wr, const float* br, int N, int C, int E, int k,
+                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
+{
+    constexpr int TOK = R_WARPS * TPW * (32 / EL);
+    router_fwd_kernel<TIn, EL, EPL, TPW><<<(N + TOK - 1) / TOK, R_WARPS * 32, 0, st>>>(
+        x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
+    MGPT_LAUNCHED("router_fwd_kernel");
+    return 0;
 }
 
 template <typename TIn>
 int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, int C, int E, int k,
                         float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
 {
-    const int grid = (N + R_TOK - 1) / R_TOK;
-    if (E <= 32)
-        router_fwd_kernel<TIn, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
-    else if (E <= 64)
-        router_fwd_kernel<TIn, 2><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
-    else
-        router_fwd_kernel<TIn, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
-    MGPT_LAUNCHED("router_fwd_kernel");
-    return 0;
+    if (E <= 8) return router_fwd_launch<TIn, 8, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+    if (E <= 16) return router_fwd_launch<TIn, 16, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+    if (E <= 32) return router_fwd_launch<TIn, 32, 1, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+    if (E <= 64) return router_fwd_launch<TIn, 32, 2, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+    return router_fwd_launch<TIn, 32, 4, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
 }
 
 }  // namespace
@@ -350,30 +423,43 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
         MGPT_LAUNCHED("router_dlogits_kernel");
     }
     {
-        const int grid = (N + DX_TOK - 1) / DX_TOK;
-        const size_t sm = (size_t)DX_TOK * E * sizeof(float);
+        int epad = 8;
+        while (epad < E) epad <<= 1;
+        const int chunk = DX_WS_FLOATS / epad;                 // channels per CTA (multiple of 8)
+        dim3 grid((N + DX_TOK - 1) / DX_TOK, (C + chunk - 1) / chunk);
+        const size_t sm = (size_t)(DX_WS_FLOATS + DX_TOK * E) * sizeof(float);
         const void* dXg = ws + w.dXg;
+        static bool attr_done = false;
+        if (!attr_done) {
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            attr_done = true;
+        }
         if (w.act_bytes == 4) {
-            if (io == MGPT_MOE_IO_F32)
-                router_dx_kernel<float, float><<<grid, 256, sm, st>>>((const float*)dXg, pos, dl, Wr, N, C, E, k, (float*)dx);
-            else
-                router_dx_kernel<float, bf16><<<grid, 256, sm, st>>>((const float*)dXg, pos, dl, Wr, N, C, E, k, (bf16*)dx);
+            router_dx_kernel<float, float><<<grid, 256, sm, st>>>((const float*)dXg, pos, dl, Wr, N, C, E, k, chunk, (float*)dx);
+        } else if (io == MGPT_MOE_IO_F32) {
+            router_dx_kernel<bf16, float><<<grid, 256, sm, st>>>((const bf16*)dXg, pos, dl, Wr, N, C, E, k, chunk, (float*)dx);
         } else {
-            if (io == MGPT_MOE_IO_F32)
-                router_dx_kernel<bf16, float><<<grid, 256, sm, st>>>((const bf16*)dXg, pos, dl, Wr, N, C, E, k, (float*)dx);
-            else
-                router_dx_kernel<bf16, bf16><<<grid, 256, sm, st>>>((const bf16*)dXg, pos, dl, Wr, N, C, E, k, (bf16*)dx);
+            router_dx_kernel<bf16, bf16><<<grid, 256, sm, st>>>((const bf16*)dXg, pos, dl, Wr, N, C, E, k, chunk, (bf16*)dx);
         }
         MGPT_LAUNCHED("router_dx_kernel");
     }
     if (L->has_grad) {
-        dim3 grid((C + WG_CH - 1) / WG_CH, (N + WG_CHUNK - 1) / WG_CHUNK);
-        const size_t sm = (size_t)(WG_TT * WG_CH + WG_TT * E) * sizeof(float);
+        const int E4 = (E + 3) / 4, ch_per_cta = (256 / E4) * 4;
+        const int cblocks = (C + ch_per_cta - 1) / ch_per_cta;
+        float* part = (float*)(ws + w.rw_part);
+        float* partb = part + (size_t)w.rw_chunks * C * E;
+        const int tpc = (N + w.rw_chunks - 1) / w.rw_chunks;
+        dim3 grid(cblocks, w.rw_chunks);
         if (io == MGPT_MOE_IO_F32)
-            router_wgrad_kernel<float><<<grid, 256, sm, st>>>((const float*)x, dl, N, C, E, L->p_grad[0], L->p_grad[1]);
+            router_wgrad_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)x, dl, N, C, E, tpc, part, partb);
         else
-            router_wgrad_kernel<bf16><<<grid, 256, sm, st>>>((const bf16*)x, dl, N, C, E, L->p_grad[0], L->p_grad[1]);
-        MGPT_LAUNCHED("router_wgrad_kernel");
+            router_wgrad_partial_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)x, dl, N, C, E, tpc, part, partb);
+        MGPT_LAUNCHED("router_wgrad_partial_kernel");
+        router_wgrad_reduce_kernel<<<(C * E + 255) / 256, 256, 0, st>>>(part, partb, w.rw_chunks, C * E, E,
+                                                                      L->p_grad[0], L->p_grad[1]);
+        MGPT_LAUNCHED("router_wgrad_reduce_kernel");
     }
     return 0;
 }
