@@ -74,7 +74,7 @@ Workspace make_workspace(const Dims& d, int n_tokens)
     {
         const int e4 = (d.E + 3) / 4, ch_per_cta = (256 / e4) * 4;
         const int cblocks = (d.C + ch_per_cta - 1) / ch_per_cta;
-        int chunks = 296 / (cblocks > 0 ? cblocks : 1);
+        int chunks = 1184 / (cblocks > 0 ? cblocks : 1);
         if (chunks > 64) chunks = 64;
         if (chunks > n_tokens) chunks = n_tokens;
         if (chunks < 1) chunks = 1;

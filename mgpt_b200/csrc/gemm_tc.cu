@@ -86,6 +86,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
+// grad += x for four consecutive floats, no return value (one L2 reduction per 16 bytes)
+__device__ __forceinline__ void red_add_v4(float* dst, float4 x)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -590,16 +596,20 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int c = 0; c < 4; ++c) {
                 const int n = n_w + c * 32;
                 if (n >= p.N) break;
-                // transpose through shared memory so that each RED covers one 128-byte row segment
+                // transpose through shared memory (16-byte pieces, XOR-swizzled by row) so that one
+                // vector RED instruction covers four full 128-byte row segments
 #pragma unroll
-                for (int j = 0; j < 32; ++j) stage[lane * 32 + (j ^ lane)] = v[c][j];
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4*>(&stage[lane * 32 + ((j ^ (lane & 7)) << 2)]) =
+                        make_float4(v[c][4 * j], v[c][4 * j + 1], v[c][4 * j + 2], v[c][4 * j + 3]);
                 __syncwarp();
-                const int col = n + lane;
-#pragma unroll 4
-                for (int rr = 0; rr < 32; ++rr) {
-                    const int m = m_w + rr;
-                    const float x = stage[rr * 32 + (lane ^ rr)];          // column (lane) of row rr
-                    if (m < p.M && col < p.N) atomicAdd(g + (size_t)m * p.N + col, x);
+                const int sub = lane >> 3, piece = lane & 7;
+                const int col = n + piece * 4;
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int r = rr * 4 + sub, m = m_w + r;
+                    const float4 x = *reinterpret_cast<const float4*>(&stage[r * 32 + ((piece ^ (r & 7)) << 2)]);
+                    if (m < p.M && col < p.N) red_add_v4(g + (size_t)m * p.N + col, x);
                 }
                 __syncwarp();
             }

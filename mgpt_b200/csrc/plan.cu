@@ -149,8 +149,41 @@ dispatch_rows_kernel(const TIn* __restrict__ x, const int32_t* __restrict__ row_
     }
 }
 
+// 8 consecutive elements <-> 8 floats (16 bytes of bf16, 32 bytes of float)
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8])
+{
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8])
+{
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8])
+{
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float (&v)[8])
+{
+    uint4 u;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
 // y[tok,:] = sum_j p[tok,j] * Yg[pos(tok,j),:], slots visited in ascending order
-// like the reference's scatter-add.  One warp per token.
+// like the reference's scatter-add.  One warp per token, 8 channels per lane per step.
 template <typename TAct, typename TIo>
 __global__ void __launch_bounds__(256)
 combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos, const float* __restrict__ top_p,
@@ -174,18 +207,18 @@ combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos,
                 int ti = ps[b]; ps[b] = ps[b + 1]; ps[b + 1] = ti;
                 float tf = pr[b]; pr[b] = pr[b + 1]; pr[b + 1] = tf;
             }
-    for (int c = lane * 2; c < C; c += 64) {
-        float a0 = 0.0f, a1 = 0.0f;
+    for (int c = lane * 8; c < C; c += 256) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
         for (int j = 0; j < MAX_TOPK; ++j) {
             if (j < k) {
-                const TAct* r = Yg + (size_t)ps[j] * C + c;
-                a0 = __fadd_rn(a0, __fmul_rn(to_f32(r[0]), pr[j]));
-                if (c + 1 < C) a1 = __fadd_rn(a1, __fmul_rn(to_f32(r[1]), pr[j]));
+                float v[8];
+                load8(Yg + (size_t)ps[j] * C + c, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], pr[j]));
             }
         }
-        y[(size_t)tok * C + c] = from_f32<TIo>(a0);
-        if (c + 1 < C) y[(size_t)tok * C + c + 1] = from_f32<TIo>(a1);
+        store8(y + (size_t)tok * C + c, acc);
     }
 }
 
@@ -202,17 +235,24 @@ combine_bwd_kernel(const TIo* __restrict__ dy, const TAct* __restrict__ Yg, cons
     const int src = row_src[p];
     TAct* dst = dYg + (size_t)p * C;
     if (src < 0) {
-        for (int c = lane; c < C; c += 32) dst[c] = from_f32<TAct>(0.0f);
+        const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int c = lane * 8; c < C; c += 256) store8(dst + c, z);
         return;
     }
     const float prob = top_p[src];
     const TIo* g = dy + (size_t)(src / k) * C;
     const TAct* yg = Yg + (size_t)p * C;
     float dot = 0.0f;
-    for (int c = lane; c < C; c += 32) {
-        const float gv = to_f32(g[c]);
-        dst[c] = from_f32<TAct>(__fmul_rn(gv, prob));
-        dot = fmaf(to_f32(yg[c]), gv, dot);
+    for (int c = lane * 8; c < C; c += 256) {
+        float gv[8], yv[8], o[8];
+        load8(g + c, gv);
+        load8(yg + c, yv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i] = __fmul_rn(gv[i], prob);
+            dot = fmaf(yv[i], gv[i], dot);
+        }
+        store8(dst + c, o);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);

@@ -209,7 +209,7 @@ router_dlogits_kernel(const float* __restrict__ probs, const int32_t* __restrict
 // (layers/LinearLayer.cpp:68-69, layers/MoELayer.cpp:217).
 // One CTA: DX_TOK tokens x one channel chunk (8192/E_pad channels, Wr^T of the chunk in shared
 // memory); a thread owns 8 consecutive channels and uses 16-byte accesses.
-constexpr int DX_TOK = 32;
+constexpr int DX_TOK = 64;
 constexpr int DX_WS_FLOATS = 8192;
 template <typename TAct, typename TIo>
 __global__ void __launch_bounds__(256)
@@ -217,17 +217,18 @@ router_dx_kernel(const TAct* __restrict__ dXg, const int32_t* __restrict__ pos, 
                  const float* __restrict__ Wr, int N, int C, int E, int k, int chunk, TIo* __restrict__ dx)
 {
     extern __shared__ __align__(16) float sm_dx[];
-    float* wt = sm_dx;                         // [E][chunk]  (Wr^T of this channel chunk)
-    float* dl = sm_dx + DX_WS_FLOATS;          // [DX_TOK][E]
+    const int wstride = chunk + 4;                      // padded row: transposed staging without 32-way conflicts
+    float* wt = sm_dx;                                  // [E][chunk+4]  (Wr^T of this channel chunk)
+    float* dlT = sm_dx + DX_WS_FLOATS + 4 * MAX_EXPERTS;   // [E][DX_TOK]  (dlogits^T of this token tile)
     __shared__ int spos[DX_TOK][MAX_TOPK];
     const int tok0 = blockIdx.x * DX_TOK, c_base = blockIdx.y * chunk;
     for (int i = threadIdx.x; i < chunk * E; i += blockDim.x) {
         const int c = i / E, e = i % E;
-        wt[e * chunk + c] = (c_base + c < C) ? Wr[(size_t)(c_base + c) * E + e] : 0.0f;
+        wt[e * wstride + c] = (c_base + c < C) ? Wr[(size_t)(c_base + c) * E + e] : 0.0f;
     }
     for (int i = threadIdx.x; i < DX_TOK * E; i += blockDim.x) {
-        const int t = i / E;
-        dl[i] = (tok0 + t < N) ? dlogits[(size_t)(tok0 + t) * E + (i % E)] : 0.0f;
+        const int t = i / E, e = i % E;
+        dlT[e * DX_TOK + t] = (tok0 + t < N) ? dlogits[(size_t)(tok0 + t) * E + e] : 0.0f;
     }
     if (threadIdx.x < DX_TOK) {
         const int tok = tok0 + threadIdx.x;
@@ -248,52 +249,62 @@ router_dx_kernel(const TAct* __restrict__ dXg, const int32_t* __restrict__ pos, 
     }
     __syncthreads();
     const int groups = chunk / 8;                       // 8-channel groups in the chunk
-    const int g = threadIdx.x % groups, tl = threadIdx.x / groups, tstep = blockDim.x / groups;
+    const int g = threadIdx.x % groups, ql = threadIdx.x / groups, qstep = blockDim.x / groups;
     const int c = c_base + g * 8;
     if (c >= C) return;
-    for (int t = tl; t < DX_TOK; t += tstep) {
-        const int tok = tok0 + t;
-        if (tok >= N) break;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int tq = ql; tq < DX_TOK / 4; tq += qstep) {    // a thread owns 8 channels of 4 consecutive tokens
+        if (tok0 + tq * 4 >= N) break;
+        float acc[4][8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[t][i] = 0.0f;
         for (int e = 0; e < E; ++e) {
-            const float d = dl[t * E + e];
-            const float4 w0 = *reinterpret_cast<const float4*>(&wt[e * chunk + g * 8]);
-            const float4 w1 = *reinterpret_cast<const float4*>(&wt[e * chunk + g * 8 + 4]);
-            acc[0] = fmaf(d, w0.x, acc[0]); acc[1] = fmaf(d, w0.y, acc[1]);
-            acc[2] = fmaf(d, w0.z, acc[2]); acc[3] = fmaf(d, w0.w, acc[3]);
-            acc[4] = fmaf(d, w1.x, acc[4]); acc[5] = fmaf(d, w1.y, acc[5]);
-            acc[6] = fmaf(d, w1.z, acc[6]); acc[7] = fmaf(d, w1.w, acc[7]);
-        }
-        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int j = 0; j < k; ++j) {
-            const TAct* r = dXg + (size_t)spos[t][j] * C + c;
-            if constexpr (sizeof(TAct) == 2) {
-                const uint4 u = *reinterpret_cast<const uint4*>(r);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+            const float4 d = *reinterpret_cast<const float4*>(&dlT[e * DX_TOK + tq * 4]);
+            const float4 w0 = *reinterpret_cast<const float4*>(&wt[e * wstride + g * 8]);
+            const float4 w1 = *reinterpret_cast<const float4*>(&wt[e * wstride + g * 8 + 4]);
+            const float dv[4] = {d.x, d.y, d.z, d.w};
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    s[2 * i] = __fadd_rn(s[2 * i], __uint_as_float(w[i] << 16));
-                    s[2 * i + 1] = __fadd_rn(s[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            for (int t = 0; t < 4; ++t)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[t][i] = fmaf(dv[t], wv[i], acc[t][i]);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int tl = tq * 4 + t, tok = tok0 + tl;
+            if (tok >= N) break;
+            float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int j = 0; j < k; ++j) {
+                const TAct* r = dXg + (size_t)spos[tl][j] * C + c;
+                if constexpr (sizeof(TAct) == 2) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(r);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        s[2 * i] = __fadd_rn(s[2 * i], __uint_as_float(w[i] << 16));
+                        s[2 * i + 1] = __fadd_rn(s[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+                    }
+                } else {
+                    const float4 a = *reinterpret_cast<const float4*>(r), b = *reinterpret_cast<const float4*>(r + 4);
+                    s[0] = __fadd_rn(s[0], a.x); s[1] = __fadd_rn(s[1], a.y); s[2] = __fadd_rn(s[2], a.z); s[3] = __fadd_rn(s[3], a.w);
+                    s[4] = __fadd_rn(s[4], b.x); s[5] = __fadd_rn(s[5], b.y); s[6] = __fadd_rn(s[6], b.z); s[7] = __fadd_rn(s[7], b.w);
                 }
-            } else {
-                const float4 a = *reinterpret_cast<const float4*>(r), b = *reinterpret_cast<const float4*>(r + 4);
-                s[0] = __fadd_rn(s[0], a.x); s[1] = __fadd_rn(s[1], a.y); s[2] = __fadd_rn(s[2], a.z); s[3] = __fadd_rn(s[3], a.w);
-                s[4] = __fadd_rn(s[4], b.x); s[5] = __fadd_rn(s[5], b.y); s[6] = __fadd_rn(s[6], b.z); s[7] = __fadd_rn(s[7], b.w);
             }
-        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s[i] = __fadd_rn(s[i], acc[i]);
-        TIo* o = dx + (size_t)tok * C + c;
-        if constexpr (sizeof(TIo) == 4) {
-            *reinterpret_cast<float4*>(o) = make_float4(s[0], s[1], s[2], s[3]);
-            *reinterpret_cast<float4*>(o + 4) = make_float4(s[4], s[5], s[6], s[7]);
-        } else {
-            uint4 u;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(s[0], s[1]), h1 = __floats2bfloat162_rn(s[2], s[3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(s[4], s[5]), h3 = __floats2bfloat162_rn(s[6], s[7]);
-            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
-            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(o) = u;
+            for (int i = 0; i < 8; ++i) s[i] = __fadd_rn(s[i], acc[t][i]);
+            TIo* o = dx + (size_t)tok * C + c;
+            if constexpr (sizeof(TIo) == 4) {
+                *reinterpret_cast<float4*>(o) = make_float4(s[0], s[1], s[2], s[3]);
+                *reinterpret_cast<float4*>(o + 4) = make_float4(s[4], s[5], s[6], s[7]);
+            } else {
+                uint4 u;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(s[0], s[1]), h1 = __floats2bfloat162_rn(s[2], s[3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(s[4], s[5]), h3 = __floats2bfloat162_rn(s[6], s[7]);
+                u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+                u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(o) = u;
+            }
         }
     }
 }
@@ -316,26 +327,37 @@ router_wgrad_partial_kernel(const TIo* __restrict__ x, const float* __restrict__
     const bool c_ok = c < C;
     float acc[4][4] = {};
     float bs[4] = {0, 0, 0, 0};
-    for (int tok = t0; tok < t1; ++tok) {
-        float xv[4] = {0, 0, 0, 0}, dv[4];
-        if (c_ok) {
-            if constexpr (sizeof(TIo) == 2) {
-                const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)tok * C + c);
-                xv[0] = __uint_as_float(u.x << 16); xv[1] = __uint_as_float(u.x & 0xffff0000u);
-                xv[2] = __uint_as_float(u.y << 16); xv[3] = __uint_as_float(u.y & 0xffff0000u);
-            } else {
-                const float4 f = *reinterpret_cast<const float4*>(x + (size_t)tok * C + c);
-                xv[0] = f.x; xv[1] = f.y; xv[2] = f.z; xv[3] = f.w;
+    constexpr int UN = 4;                               // tokens in flight per thread
+    for (int tb = t0; tb < t1; tb += UN) {
+        float xv[UN][4], dv[UN][4];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int tok = tb + u;
+            const bool ok = tok < t1;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[u][i] = 0.0f;
+            if (ok && c_ok) {
+                if constexpr (sizeof(TIo) == 2) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(x + (size_t)tok * C + c);
+                    xv[u][0] = __uint_as_float(w.x << 16); xv[u][1] = __uint_as_float(w.x & 0xffff0000u);
+                    xv[u][2] = __uint_as_float(w.y << 16); xv[u][3] = __uint_as_float(w.y & 0xffff0000u);
+                } else {
+                    const float4 f = *reinterpret_cast<const float4*>(x + (size_t)tok * C + c);
+                    xv[u][0] = f.x; xv[u][1] = f.y; xv[u][2] = f.z; xv[u][3] = f.w;
+                }
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dv[u][j] = (ok && e0 + j < E) ? dlogits[(size_t)tok * E + e0 + j] : 0.0f;
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) dv[j] = (e0 + j < E) ? dlogits[(size_t)tok * E + e0 + j] : 0.0f;
+        for (int u = 0; u < UN; ++u) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], dv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[u][i], dv[u][j], acc[i][j]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) bs[j] += dv[j];
+            for (int j = 0; j < 4; ++j) bs[j] += dv[u][j];
+        }
     }
     if (c_ok) {
         float* dst = part + ((size_t)blockIdx.y * C + c) * E;
@@ -427,13 +449,13 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
         while (epad < E) epad <<= 1;
         const int chunk = DX_WS_FLOATS / epad;                 // channels per CTA (multiple of 8)
         dim3 grid((N + DX_TOK - 1) / DX_TOK, (C + chunk - 1) / chunk);
-        const size_t sm = (size_t)(DX_WS_FLOATS + DX_TOK * E) * sizeof(float);
+        const size_t sm = (size_t)(DX_WS_FLOATS + 4 * MAX_EXPERTS + DX_TOK * E) * sizeof(float);
         const void* dXg = ws + w.dXg;
         static bool attr_done = false;
         if (!attr_done) {
-            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+            MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
             attr_done = true;
         }
         if (w.act_bytes == 4) {
