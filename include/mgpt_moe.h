@@ -164,6 +164,44 @@ int  mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E,
                       int32_t* row_src, int row_cap, int32_t* status,
                       void* scratch, size_t scratch_bytes, mgpt_stream_t stream);
 
+/* ---- stage level: the layer cut at its two exchange points ------------------
+ * For expert-parallel execution (the reference has no multi-GPU code; these
+ * calls split MoELayer::forward_into / backward_into, MoELayer.cpp:52-83 |
+ * 94-118 | 121-123 and 156 | 159-181 | 184-218, where rows change owner).
+ *
+ * Routing side: a layer created with all E experts and top_k = k, bound with
+ * mgpt_moe_bind_params(layer, data, grad, 2) (router tensors only).
+ * Expert side: a layer created with the E_local experts this GPU owns and
+ * top_k = 1, bound with all 2+6*E_local pointers of which data[0], data[1]
+ * (router) may be NULL.  Rows are [n, C] in the mode's activation type (BF16
+ * in BF16 mode, FP32 in FP32 mode).  Workspaces: mgpt_moe_stage_workspace_bytes
+ * (routing_side = 1 leaves out the activation buffers).                     */
+size_t mgpt_moe_stage_workspace_bytes(const mgpt_moe_layer* layer, int n, int routing_side);
+
+/* router + plan + permutation: send_rows[slot,:] = x[map[slot]/k,:], the
+ * reference's expert-major compact order (Tensor.cpp:1368-1381), so rows for
+ * experts e0..e1 are one contiguous block. Per-expert counts: workspace view
+ * "counts" or mgpt_moe_expert_counts. */
+int  mgpt_moe_route(mgpt_moe_layer* layer, const void* x, int n_tokens, int io_dtype,
+                    void* workspace, size_t workspace_bytes, void* send_rows, mgpt_stream_t stream);
+/* y[tok,:] = sum_j p[tok,j] * rows_back[slot(tok,j),:]   (Tensor.cpp:1398-1406) */
+int  mgpt_moe_combine(mgpt_moe_layer* layer, const void* rows_back, void* y, int io_dtype,
+                      void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+/* d_rows[slot,:] = p * dy[tok,:] and d_top_p (Tensor.cpp:1424-1436) */
+int  mgpt_moe_combine_backward(mgpt_moe_layer* layer, const void* rows_back, const void* dy, int io_dtype,
+                               void* d_rows, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+/* dx = gather-sum of d_rows_in + router backward; accumulates the router gradients
+ * with this GPU's own counts in the load-balance term (MoELayer.cpp:184-218). */
+int  mgpt_moe_route_backward(mgpt_moe_layer* layer, const void* x, const void* d_rows_in, void* dx, int io_dtype,
+                             void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+/* out_rows[i,:] = SwiGLU expert expert_of_row[i] applied to rows[i,:]
+ * (MoELayer.cpp:94-118); keeps what backward needs in the workspace. */
+int  mgpt_moe_experts_forward(mgpt_moe_layer* layer, const void* rows, const int32_t* expert_of_row, int n_rows,
+                              void* out_rows, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+/* d_in_rows = gradient w.r.t. rows; accumulates the expert parameter gradients (MoELayer.cpp:159-181). */
+int  mgpt_moe_experts_backward(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
+                               void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
 /* The same plan for callers that can neither pass scratch nor let the library
  * allocate: an engine whose arena already owns all device memory, or a step
  * loop that must never run into cudaMalloc (it synchronises the whole device).

@@ -18,6 +18,8 @@ SYMBOLS = [
     "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
     "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name",
     "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes", "mgpt_moe_op_plan_noalloc",
+    "mgpt_moe_stage_workspace_bytes", "mgpt_moe_route", "mgpt_moe_combine", "mgpt_moe_combine_backward",
+    "mgpt_moe_route_backward", "mgpt_moe_experts_forward", "mgpt_moe_experts_backward",
 ]
 PLAN_NOALLOC_MAX_ROWS = 1048576
 N_STAGES = 12
@@ -71,6 +73,14 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_op_plan_scratch_bytes.argtypes = [i32, i32]
     lib.mgpt_moe_op_plan_scratch_bytes.restype = sz
     lib.mgpt_moe_op_plan.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, sz, vp]
+    lib.mgpt_moe_stage_workspace_bytes.argtypes = [vp, i32, i32]
+    lib.mgpt_moe_stage_workspace_bytes.restype = sz
+    lib.mgpt_moe_route.argtypes = [vp, vp, i32, i32, vp, sz, vp, vp]
+    lib.mgpt_moe_combine.argtypes = [vp, vp, vp, i32, vp, sz, vp]
+    lib.mgpt_moe_combine_backward.argtypes = [vp, vp, vp, i32, vp, vp, sz, vp]
+    lib.mgpt_moe_route_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]
+    lib.mgpt_moe_experts_forward.argtypes = [vp, vp, vp, i32, vp, vp, sz, vp]
+    lib.mgpt_moe_experts_backward.argtypes = [vp, vp, vp, vp, sz, vp]
     lib.mgpt_moe_op_plan_noalloc.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
     _lib = lib
     return lib

@@ -26,7 +26,7 @@ void count_launch(int n) { g_launches += n; }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-Workspace make_workspace(const Dims& d, int n_tokens)
+Workspace make_workspace(const Dims& d, int n_tokens, int kind)
 {
     Workspace w = {};
     const size_t N = (size_t)n_tokens, E = d.E, k = d.k, C = d.C, H = d.H;
@@ -45,6 +45,7 @@ Workspace make_workspace(const Dims& d, int n_tokens)
         return o;
     };
     const size_t rc = (size_t)w.row_cap, ab = w.act_bytes;
+    const size_t big = kind == 0 ? 1 : 0;          // routing-side workspaces carry no activation buffers
     w.logits = take(N * E * 4);
     w.probs = take(N * E * 4);
     w.top_idx = take(N * k * 4);
@@ -59,15 +60,16 @@ Workspace make_workspace(const Dims& d, int n_tokens)
     w.pos = take(N * k * 4);
     w.row_src = take(rc * 4);
     w.blk_cnt = take((size_t)w.plan_blocks * E * 4);
-    w.Xg = take(rc * C * ab);
-    w.G = take(rc * H * ab);
-    w.U = take(rc * H * ab);
-    w.Hh = take(rc * H * ab);
-    w.Yg = take(rc * C * ab);
-    w.dYg = take(rc * C * ab);
-    w.dG = take(rc * H * ab);
-    w.dU = take(rc * H * ab);
-    w.dXg = take(rc * C * ab);
+    w.slot = take(N * k * 4);
+    w.Xg = take(big * rc * C * ab);
+    w.G = take(big * rc * H * ab);
+    w.U = take(big * rc * H * ab);
+    w.Hh = take(big * rc * H * ab);
+    w.Yg = take(big * rc * C * ab);
+    w.dYg = take(big * rc * C * ab);
+    w.dG = take(big * rc * H * ab);
+    w.dU = take(big * rc * H * ab);
+    w.dXg = take(big * rc * C * ab);
     w.d_top_p = take(N * k * 4);
     w.dlogits = take(N * E * 4);
     // router weight gradient: per-token-chunk partial sums, reduced in a second pass
@@ -188,19 +190,27 @@ int mgpt_moe_param_shape(const mgpt_moe_layer* L, int i, int* rows, int* cols)
 int mgpt_moe_bind_params(mgpt_moe_layer* L, float* const* data, float* const* grad, int n)
 {
     if (!L || !data) return fail(MGPT_MOE_EINVAL, "null argument");
-    if (n != L->n_params) return fail(MGPT_MOE_EINVAL, "expected 2+6E parameter tensors");
-    for (int i = 0; i < n; ++i) {
-        if (!data[i]) return fail(MGPT_MOE_EINVAL, "null parameter pointer");
-        if (grad && !grad[i]) return fail(MGPT_MOE_EINVAL, "null gradient pointer");
-        L->p_data[i] = data[i];
-        L->p_grad[i] = grad ? grad[i] : nullptr;
+    // n == 2: router only (the routing side of an expert-parallel layer);
+    // n == 2+6E with data[0], data[1] NULL: experts only (the expert side).
+    if (n != L->n_params && n != 2) return fail(MGPT_MOE_EINVAL, "expected 2+6E parameter tensors (or the 2 router tensors)");
+    const bool router = data[0] != nullptr && data[1] != nullptr;
+    const bool experts = n == L->n_params;
+    if (!router && !experts) return fail(MGPT_MOE_EINVAL, "null parameter pointer");
+    for (int i = 0; i < L->n_params; ++i) {
+        const bool want = i < 2 ? router : experts;
+        if (want && !data[i]) return fail(MGPT_MOE_EINVAL, "null parameter pointer");
+        if (want && grad && !grad[i]) return fail(MGPT_MOE_EINVAL, "null gradient pointer");
+        L->p_data[i] = want ? data[i] : nullptr;
+        L->p_grad[i] = (want && grad) ? grad[i] : nullptr;
     }
     L->has_grad = grad != nullptr;
+    L->router_bound = router;
+    L->experts_bound = experts;
     MGPT_CUDA(cudaSetDevice(L->device));
     const int E = L->d.E;
     const size_t CH = (size_t)L->d.C * L->d.H;
     std::vector<void*> h((size_t)15 * E, nullptr);
-    for (int e = 0; e < E; ++e) {
+    for (int e = 0; e < E && experts; ++e) {
         const int b = 2 + 6 * e;
         h[0 * E + e] = data[b + 0]; h[1 * E + e] = data[b + 2]; h[2 * E + e] = data[b + 4];
         h[3 * E + e] = data[b + 1]; h[4 * E + e] = data[b + 3]; h[5 * E + e] = data[b + 5];
@@ -213,7 +223,7 @@ int mgpt_moe_bind_params(mgpt_moe_layer* L, float* const* data, float* const* gr
         }
     }
     MGPT_CUDA(cudaMemcpy(L->d_tables, h.data(), h.size() * sizeof(void*), cudaMemcpyHostToDevice));
-    L->bound = true;
+    L->bound = router && experts;
     L->shadows_fresh = false;
     return 0;
 }
@@ -221,8 +231,12 @@ int mgpt_moe_bind_params(mgpt_moe_layer* L, float* const* data, float* const* gr
 int mgpt_moe_sync_weights(mgpt_moe_layer* L, mgpt_stream_t stream)
 {
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
-    if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
+    if (!L->router_bound && !L->experts_bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
     MGPT_CUDA(cudaSetDevice(L->device));
+    if (!L->experts_bound) {          // routing side: nothing to shadow
+        L->shadows_fresh = true;
+        return 0;
+    }
     return launch_sync_weights(L, (cudaStream_t)stream);
 }
 
@@ -243,7 +257,7 @@ int mgpt_moe_workspace_view(const mgpt_moe_layer* L, int n_tokens, const char* n
         {"top_p", w.top_p, N * k * 4}, {"counts", w.counts, E * 4}, {"offsets", w.offsets, E * 4},
         {"padded_offsets", w.padded_offsets, (E + 1) * 4}, {"tile_expert", w.tile_expert, (size_t)w.max_tiles * 4},
         {"n_tiles", w.n_tiles, 4}, {"status", w.status, 4}, {"map", w.map, N * k * 4}, {"pos", w.pos, N * k * 4},
-        {"row_src", w.row_src, rc * 4}, {"Xg", w.Xg, rc * C * ab}, {"G", w.G, rc * H * ab}, {"U", w.U, rc * H * ab},
+        {"row_src", w.row_src, rc * 4}, {"slot", w.slot, N * k * 4}, {"Xg", w.Xg, rc * C * ab}, {"G", w.G, rc * H * ab}, {"U", w.U, rc * H * ab},
         {"Hh", w.Hh, rc * H * ab}, {"Yg", w.Yg, rc * C * ab}, {"dYg", w.dYg, rc * C * ab}, {"dG", w.dG, rc * H * ab},
         {"dU", w.dU, rc * H * ab}, {"dXg", w.dXg, rc * C * ab}, {"d_top_p", w.d_top_p, N * k * 4},
         {"dlogits", w.dlogits, N * E * 4},
@@ -260,7 +274,7 @@ int mgpt_moe_workspace_view(const mgpt_moe_layer* L, int n_tokens, const char* n
 static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, size_t ws_bytes, Workspace* w)
 {
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
-    if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
+    if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first (all 2+6E tensors for the whole-layer calls)");
     if (n_tokens < 0) return fail(MGPT_MOE_EINVAL, "negative token count");
     if (io != MGPT_MOE_IO_F32 && io != MGPT_MOE_IO_BF16) return fail(MGPT_MOE_EINVAL, "unknown io dtype");
     if (L->d.mode == MGPT_MOE_FP32 && io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 tokens");

@@ -58,7 +58,7 @@ struct Workspace {
     size_t logits, probs, top_idx, top_p;
     // plan
     size_t counts, offsets, padded_offsets, tile_expert, n_tiles, status;
-    size_t map, pos, row_src, blk_cnt;
+    size_t map, pos, row_src, blk_cnt, slot;
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries
@@ -76,7 +76,8 @@ struct Dims {
     int gemm_impl;  // 0 default, 1 SIMT
 };
 
-Workspace make_workspace(const Dims& d, int n_tokens);
+// kind 0: whole layer; kind 1: routing side only (no activation buffers; rows are exchanged by the caller)
+Workspace make_workspace(const Dims& d, int n_tokens, int kind = 0);
 
 // Device-side tables of per-expert pointers (index = expert).
 struct ExpertPtrs {
@@ -93,6 +94,7 @@ struct mgpt_moe_layer {
     int n_params;
     std::vector<float*> p_data, p_grad;      // host copies of the bound pointers
     bool bound = false, has_grad = false, shadows_fresh = false;
+    bool router_bound = false, experts_bound = false;
 
     // device tables: pointers to FP32 masters / grads per expert
     void* d_tables = nullptr;                // one allocation holding all tables
@@ -141,7 +143,7 @@ namespace mgpt {
 int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, int N, int C, int E, int k,
                       float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st);
 int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
-                      void* dx, cudaStream_t st);
+                      void* dx, cudaStream_t st, const void* dXg_rows = nullptr, const int32_t* pos_rows = nullptr);
 
 // plan.cu
 int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st);
@@ -149,6 +151,16 @@ int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, 
 int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st);
 int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st);
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int gather_rows(const void* src, int src_io, const int32_t* row_src, const int32_t* n_tiles, int rows, int grid_rows,
+                int C, int k, void* dst, size_t act_bytes, cudaStream_t st);
+int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,
+                 size_t act_bytes, cudaStream_t st);
+int combine_rows_backward(const void* dy, int io, const void* rows, const int32_t* row_src, const float* top_p,
+                          const int32_t* n_tiles, int n_rows, int grid_rows, int C, int k, void* d_rows, float* d_top_p,
+                          size_t act_bytes, cudaStream_t st);
+int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
+             int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
+             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of);
 
 // gemm_simt.cu
 int simt_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);

@@ -93,7 +93,8 @@ __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
                    const int32_t* __restrict__ blk_base, const int32_t* __restrict__ offsets,
                    const int32_t* __restrict__ padded_offsets,
-                   int32_t* __restrict__ map, int32_t* __restrict__ pos, int32_t* __restrict__ row_src)
+                   int32_t* __restrict__ map, int32_t* __restrict__ pos, int32_t* __restrict__ row_src,
+                   int32_t* __restrict__ slot_of)
 {
     __shared__ int warp_cnt[PLAN_BLOCK / 32][MAX_EXPERTS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -115,6 +116,7 @@ plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
         map[slot] = i;
         pos[i] = p;
         row_src[p] = i;
+        if (slot_of) slot_of[i] = slot;
     }
 }
 
@@ -122,11 +124,12 @@ plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
 template <typename TIn, typename TAct>
 __global__ void __launch_bounds__(256)
 dispatch_rows_kernel(const TIn* __restrict__ x, const int32_t* __restrict__ row_src,
-                     const int32_t* __restrict__ n_tiles, int C, int k, TAct* __restrict__ Xg)
+                     const int32_t* __restrict__ n_tiles, int fixed_rows, int C, int k, TAct* __restrict__ Xg)
 {
     const int lane = threadIdx.x & 31;
     const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (p >= *n_tiles * ROW_TILE) return;
+    // rows in use: all tiles of the plan, or a count the host already knows
+    if (p >= (fixed_rows >= 0 ? fixed_rows : *n_tiles * ROW_TILE)) return;
     const int src = row_src[p];
     TAct* dst = Xg + (size_t)p * C;
     constexpr int VIN = 16 / sizeof(TIn), VOUT = 16 / sizeof(TAct);
@@ -226,12 +229,12 @@ combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos,
 template <typename TAct, typename TIo>
 __global__ void __launch_bounds__(256)
 combine_bwd_kernel(const TIo* __restrict__ dy, const TAct* __restrict__ Yg, const int32_t* __restrict__ row_src,
-                   const float* __restrict__ top_p, const int32_t* __restrict__ n_tiles, int C, int k,
+                   const float* __restrict__ top_p, const int32_t* __restrict__ n_tiles, int fixed_rows, int C, int k,
                    TAct* __restrict__ dYg, float* __restrict__ d_top_p)
 {
     const int lane = threadIdx.x & 31;
     const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (p >= *n_tiles * ROW_TILE) return;
+    if (p >= (fixed_rows >= 0 ? fixed_rows : *n_tiles * ROW_TILE)) return;
     const int src = row_src[p];
     TAct* dst = dYg + (size_t)p * C;
     if (src < 0) {
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(BiasGradArgs a)
 // every element is written by plan_count_kernel before it is read, so it needs no clearing.
 int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
              int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
-             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st)
+             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of)
 {
     const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
     MGPT_CUDA(cudaMemsetAsync(row_src, 0xFF, (size_t)row_cap * sizeof(int32_t), st));
@@ -329,7 +332,7 @@ int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* off
     plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, plan_blocks, E, counts, offsets, padded_offsets, tile_expert,
                                                 n_tiles, max_tiles, status);
     MGPT_LAUNCHED("plan_scan_kernel");
-    plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, offsets, padded_offsets, map, pos, row_src);
+    plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, offsets, padded_offsets, map, pos, row_src, slot_of);
     MGPT_LAUNCHED("plan_assign_kernel");
     return 0;
 }
@@ -339,61 +342,80 @@ int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st)
     return run_plan((const int32_t*)(ws + w.top_idx), w.R, d.E, (int32_t*)(ws + w.counts), (int32_t*)(ws + w.offsets),
                     (int32_t*)(ws + w.padded_offsets), (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
                     w.max_tiles, (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos), (int32_t*)(ws + w.row_src),
-                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st);
+                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st, (int32_t*)(ws + w.slot));
 }
 
-int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st)
+// dst[p,:] = src[row_src[p]/k,:] for p < rows (zero where row_src[p] < 0).  rows < 0: every tile of the plan.
+int gather_rows(const void* src, int src_io, const int32_t* row_src, const int32_t* n_tiles, int rows, int grid_rows,
+                int C, int k, void* dst, size_t act_bytes, cudaStream_t st)
 {
-    const int grid = (w.row_cap + 7) / 8;
-    const int32_t* row_src = (const int32_t*)(ws + w.row_src);
-    const int32_t* nt = (const int32_t*)(ws + w.n_tiles);
-    void* Xg = ws + w.Xg;
-    if (w.act_bytes == 4) {
-        if (io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 tokens");
-        dispatch_rows_kernel<float, float><<<grid, 256, 0, st>>>((const float*)x, row_src, nt, d.C, d.k, (float*)Xg);
-    } else if (io == MGPT_MOE_IO_F32) {
-        dispatch_rows_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)x, row_src, nt, d.C, d.k, (bf16*)Xg);
+    if (grid_rows <= 0) return 0;
+    const int grid = (grid_rows + 7) / 8;
+    if (act_bytes == 4) {
+        if (src_io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 rows");
+        dispatch_rows_kernel<float, float><<<grid, 256, 0, st>>>((const float*)src, row_src, n_tiles, rows, C, k, (float*)dst);
+    } else if (src_io == MGPT_MOE_IO_F32) {
+        dispatch_rows_kernel<float, bf16><<<grid, 256, 0, st>>>((const float*)src, row_src, n_tiles, rows, C, k, (bf16*)dst);
     } else {
-        dispatch_rows_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)x, row_src, nt, d.C, d.k, (bf16*)Xg);
+        dispatch_rows_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)src, row_src, n_tiles, rows, C, k, (bf16*)dst);
     }
     MGPT_LAUNCHED("dispatch_rows_kernel");
     return 0;
 }
 
+int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st)
+{
+    return gather_rows(x, io, (const int32_t*)(ws + w.row_src), (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, d.C, d.k,
+                       ws + w.Xg, w.act_bytes, st);
+}
+
+// y = weighted gather-sum of rows[pos[tok,j]]
+int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,
+                 size_t act_bytes, cudaStream_t st)
+{
+    if (N <= 0) return 0;
+    const int grid = (N + 7) / 8;
+    if (act_bytes == 4)
+        combine_fwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)rows, pos, top_p, N, C, k, (float*)y);
+    else if (io == MGPT_MOE_IO_F32)
+        combine_fwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (float*)y);
+    else
+        combine_fwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (bf16*)y);
+    MGPT_LAUNCHED("combine_fwd_kernel");
+    return 0;
+}
+
 int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st)
 {
-    const int N = w.n_tokens, grid = (N + 7) / 8;
-    const int32_t* pos = (const int32_t*)(ws + w.pos);
-    const float* tp = (const float*)(ws + w.top_p);
-    const void* Yg = ws + w.Yg;
-    if (w.act_bytes == 4)
-        combine_fwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)Yg, pos, tp, N, d.C, d.k, (float*)y);
+    return combine_rows(ws + w.Yg, (const int32_t*)(ws + w.pos), (const float*)(ws + w.top_p), w.n_tokens, d.C, d.k, y,
+                        io, w.act_bytes, st);
+}
+
+// d_rows[p] = top_p * dy[tok], d_top_p[flat] = <rows[p], dy[tok]> for p < rows (rows < 0: every tile of the plan)
+int combine_rows_backward(const void* dy, int io, const void* rows, const int32_t* row_src, const float* top_p,
+                          const int32_t* n_tiles, int n_rows, int grid_rows, int C, int k, void* d_rows, float* d_top_p,
+                          size_t act_bytes, cudaStream_t st)
+{
+    if (grid_rows <= 0) return 0;
+    const int grid = (grid_rows + 7) / 8;
+    if (act_bytes == 4)
+        combine_bwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)dy, (const float*)rows, row_src, top_p,
+                                                               n_tiles, n_rows, C, k, (float*)d_rows, d_top_p);
     else if (io == MGPT_MOE_IO_F32)
-        combine_fwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)Yg, pos, tp, N, d.C, d.k, (float*)y);
+        combine_bwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const float*)dy, (const bf16*)rows, row_src, top_p,
+                                                              n_tiles, n_rows, C, k, (bf16*)d_rows, d_top_p);
     else
-        combine_fwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)Yg, pos, tp, N, d.C, d.k, (bf16*)y);
-    MGPT_LAUNCHED("combine_fwd_kernel");
+        combine_bwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)rows, row_src, top_p,
+                                                             n_tiles, n_rows, C, k, (bf16*)d_rows, d_top_p);
+    MGPT_LAUNCHED("combine_bwd_kernel");
     return 0;
 }
 
 int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st)
 {
-    const int grid = (w.row_cap + 7) / 8;
-    const int32_t* row_src = (const int32_t*)(ws + w.row_src);
-    const int32_t* nt = (const int32_t*)(ws + w.n_tiles);
-    const float* tp = (const float*)(ws + w.top_p);
-    float* dtp = (float*)(ws + w.d_top_p);
-    if (w.act_bytes == 4)
-        combine_bwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)dy, (const float*)(ws + w.Yg), row_src, tp,
-                                                               nt, d.C, d.k, (float*)(ws + w.dYg), dtp);
-    else if (io == MGPT_MOE_IO_F32)
-        combine_bwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const float*)dy, (const bf16*)(ws + w.Yg), row_src, tp,
-                                                              nt, d.C, d.k, (bf16*)(ws + w.dYg), dtp);
-    else
-        combine_bwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)(ws + w.Yg), row_src, tp,
-                                                             nt, d.C, d.k, (bf16*)(ws + w.dYg), dtp);
-    MGPT_LAUNCHED("combine_bwd_kernel");
-    return 0;
+    return combine_rows_backward(dy, io, ws + w.Yg, (const int32_t*)(ws + w.row_src), (const float*)(ws + w.top_p),
+                                 (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, d.C, d.k, ws + w.dYg,
+                                 (float*)(ws + w.d_top_p), w.act_bytes, st);
 }
 
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
@@ -447,7 +469,7 @@ extern "C" int mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E, int32
     if (scratch_bytes < mgpt_moe_op_plan_scratch_bytes(n_rows, E))
         return fail(MGPT_MOE_ENOMEM, "scratch smaller than mgpt_moe_op_plan_scratch_bytes()");
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream);
+                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream, nullptr);
 }
 
 // ---- dispatch plan without any allocation ------------------------------------------
@@ -500,5 +522,5 @@ extern "C" int mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int 
     // The array still holds the previous call's block bases.  Nothing has to be cleared:
     // plan_count_kernel writes all plan_blocks*E entries this call reads before they are read.
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream);
+                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream, nullptr);
 }

@@ -424,7 +424,7 @@ int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, i
 }
 
 int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
-                      void* dx, cudaStream_t st)
+                      void* dx, cudaStream_t st, const void* dXg_rows, const int32_t* pos_rows)
 {
     const Dims& d = L->d;
     const int N = w.n_tokens, C = d.C, E = d.E, k = d.k;
@@ -433,7 +433,7 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
     const int32_t* top_idx = (const int32_t*)(ws + w.top_idx);
     const float* dtp = (const float*)(ws + w.d_top_p);
     const int32_t* counts = (const int32_t*)(ws + w.counts);
-    const int32_t* pos = (const int32_t*)(ws + w.pos);
+    const int32_t* pos = pos_rows ? pos_rows : (const int32_t*)(ws + w.pos);
     float* dl = (float*)(ws + w.dlogits);
     const float* Wr = L->p_data[0];
 
@@ -450,7 +450,7 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
         const int chunk = DX_WS_FLOATS / epad;                 // channels per CTA (multiple of 8)
         dim3 grid((N + DX_TOK - 1) / DX_TOK, (C + chunk - 1) / chunk);
         const size_t sm = (size_t)(DX_WS_FLOATS + 4 * MAX_EXPERTS + DX_TOK * E) * sizeof(float);
-        const void* dXg = ws + w.dXg;
+        const void* dXg = dXg_rows ? dXg_rows : (const void*)(ws + w.dXg);
         static bool attr_done = false;
         if (!attr_done) {
             MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));

@@ -1,0 +1,238 @@
+"""Expert-parallel MoE layer: tokens stay on their GPU, experts are sharded.
+
+One process per GPU.  Rank ``g`` of ``G`` owns experts ``[g*E/G, (g+1)*E/G)`` (weights,
+gradients) and a replica of the router.  Per step:
+
+    route (local)  ->  counts all-to-all  ->  rows all-to-all  ->  experts (local)
+                   ->  rows all-to-all back  ->  combine (local)
+
+and the mirror image for backward.  Rows leave a GPU in the reference's compact
+expert-major order, so the block for each destination is contiguous; they arrive
+ordered by (source rank, expert, source flat index) and the expert side regroups them
+by expert, stable in that order.  The load-balance term of the router gradient uses
+each GPU's own counts, which equals running the reference independently on every
+GPU's batch.  The reference itself has no multi-GPU code.
+
+torch.distributed is the transport (NCCL on GPUs; gloo works for the host logic with a
+CPU stage backend, which is how the tests exercise this file without GPUs).
+"""
+from __future__ import annotations
+
+import ctypes as ct
+
+import torch
+import torch.distributed as dist
+
+
+class CudaStages:
+    """The six stage-level entry points of libmgpt_moe.so on torch CUDA tensors."""
+
+    def __init__(self, C, H, E, k, E_local, *, mode="bf16", device=0, lb_alpha=0.01):
+        from . import _lib
+        self._lib_mod = _lib
+        self.lib = _lib.load()
+        self.C, self.H, self.E, self.k, self.E_local = C, H, E, k, E_local
+        self.device = torch.device("cuda", device)
+        self.act_dtype = torch.bfloat16 if mode == "bf16" else torch.float32
+        m = {"fp32": _lib.FP32, "bf16": _lib.BF16}[mode]
+        self.home, self.local = ct.c_void_p(), ct.c_void_p()
+        cfg = _lib.Config(C, H, E, k, lb_alpha, m, device, 0)
+        _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(self.home)))
+        cfg = _lib.Config(C, H, E_local, 1, lb_alpha, m, device, 0)
+        _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(self.local)))
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.router_params = [torch.zeros(C, E, **f32), torch.zeros(1, E, **f32)]
+        self.expert_params = []
+        for _ in range(E_local):
+            self.expert_params += [torch.zeros(C, H, **f32), torch.zeros(1, H, **f32), torch.zeros(C, H, **f32),
+                                   torch.zeros(1, H, **f32), torch.zeros(H, C, **f32), torch.zeros(1, C, **f32)]
+        for p in self.router_params + self.expert_params:
+            p.grad = torch.zeros_like(p)
+        self._bind()
+        self._home_ws = self._local_ws = None
+        self._n = self._rows = 0
+
+    def close(self):
+        for h in (self.home, self.local):
+            if h and h.value:
+                self.lib.mgpt_moe_destroy(h)
+        self.home, self.local = ct.c_void_p(), ct.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _bind(self):
+        c = self._lib_mod.check
+        rp = self.router_params
+        c(self.lib.mgpt_moe_bind_params(self.home, (ct.c_void_p * 2)(*[p.data_ptr() for p in rp]),
+                                        (ct.c_void_p * 2)(*[p.grad.data_ptr() for p in rp]), 2))
+        n = 2 + len(self.expert_params)
+        data = (ct.c_void_p * n)(None, None, *[p.data_ptr() for p in self.expert_params])
+        grad = (ct.c_void_p * n)(None, None, *[p.grad.data_ptr() for p in self.expert_params])
+        c(self.lib.mgpt_moe_bind_params(self.local, data, grad, n))
+        self.sync_weights()
+
+    def sync_weights(self):
+        c = self._lib_mod.check
+        c(self.lib.mgpt_moe_sync_weights(self.home, self._stream()))
+        c(self.lib.mgpt_moe_sync_weights(self.local, self._stream()))
+
+    @staticmethod
+    def _stream():
+        return ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _io(self, t):
+        return self._lib_mod.IO_BF16 if t.dtype == torch.bfloat16 else self._lib_mod.IO_F32
+
+    def _ws(self, handle, n, routing, cur):
+        need = int(self.lib.mgpt_moe_stage_workspace_bytes(handle, n, 1 if routing else 0))
+        if cur is None or cur.numel() < need:
+            cur = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return cur
+
+    def _view(self, handle, ws, n, name, dtype):
+        off, nb = ct.c_size_t(), ct.c_size_t()
+        self._lib_mod.check(self.lib.mgpt_moe_workspace_view(handle, n, name.encode(), ct.byref(off), ct.byref(nb)))
+        return ws[off.value: off.value + nb.value].view(dtype)
+
+    # ---- routing side
+    def route(self, x):
+        n = x.shape[0]
+        self._home_ws = self._home_ws_for(n)
+        rows = torch.empty(n * self.k, self.C, dtype=self.act_dtype, device=self.device)
+        self._lib_mod.check(self.lib.mgpt_moe_route(self.home, x.data_ptr(), n, self._io(x), self._home_ws.data_ptr(),
+                                                    self._home_ws.numel(), rows.data_ptr(), self._stream()))
+        self._n = n
+        counts = self._view(self.home, self._home_ws, n, "counts", torch.int32)
+        return rows, counts
+
+    def _home_ws_for(self, n):
+        return self._ws(self.home, n, True, self._home_ws)
+
+    def routing_view(self, name, dtype):
+        return self._view(self.home, self._home_ws, self._n, name, dtype)
+
+    def combine(self, rows_back, like):
+        y = torch.empty_like(like)
+        self._lib_mod.check(self.lib.mgpt_moe_combine(self.home, rows_back.data_ptr(), y.data_ptr(), self._io(y),
+                                                      self._home_ws.data_ptr(), self._home_ws.numel(), self._stream()))
+        return y
+
+    def combine_backward(self, rows_back, dy):
+        d_rows = torch.empty_like(rows_back)
+        self._lib_mod.check(self.lib.mgpt_moe_combine_backward(
+            self.home, rows_back.data_ptr(), dy.data_ptr(), self._io(dy), d_rows.data_ptr(),
+            self._home_ws.data_ptr(), self._home_ws.numel(), self._stream()))
+        return d_rows
+
+    def route_backward(self, x, d_rows):
+        dx = torch.empty_like(x)
+        self._lib_mod.check(self.lib.mgpt_moe_route_backward(
+            self.home, x.data_ptr(), d_rows.data_ptr(), dx.data_ptr(), self._io(x),
+            self._home_ws.data_ptr(), self._home_ws.numel(), self._stream()))
+        return dx
+
+    # ---- expert side
+    def experts_forward(self, rows, expert_of_row):
+        n = rows.shape[0]
+        self._local_ws = self._ws(self.local, n, False, self._local_ws)
+        out = torch.empty_like(rows)
+        self._lib_mod.check(self.lib.mgpt_moe_experts_forward(
+            self.local, rows.data_ptr(), expert_of_row.data_ptr(), n, out.data_ptr(),
+            self._local_ws.data_ptr(), self._local_ws.numel(), self._stream()))
+        self._rows = n
+        return out
+
+    def experts_backward(self, d_out):
+        d_in = torch.empty_like(d_out)
+        self._lib_mod.check(self.lib.mgpt_moe_experts_backward(
+            self.local, d_out.data_ptr(), d_in.data_ptr(), self._local_ws.data_ptr(), self._local_ws.numel(),
+            self._stream()))
+        return d_in
+
+
+class ExpertParallelMoE:
+    """Same role as the reference's MoELayer, with the experts sharded over a process group."""
+
+    def __init__(self, embed_dim, hidden_dim, num_experts, top_k, *, group=None, stages=None, mode="bf16",
+                 device=0, lb_alpha=0.01):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if num_experts % self.world:
+            raise ValueError(f"num_experts={num_experts} is not divisible by the group size {self.world}")
+        self.C = embed_dim
+        self.H = 4 * embed_dim if hidden_dim == -1 else hidden_dim
+        self.E, self.k = num_experts, top_k
+        self.E_local = num_experts // self.world
+        self.first_expert = self.rank * self.E_local
+        self.stages = stages if stages is not None else CudaStages(
+            self.C, self.H, self.E, self.k, self.E_local, mode=mode, device=device, lb_alpha=lb_alpha)
+        self._saved = None
+
+    # parameters: the router replica and this rank's experts, in the reference's order
+    def get_parameters(self):
+        return list(self.stages.router_params) + list(self.stages.expert_params)
+
+    def load_parameters(self, full_params):
+        """Takes the full 2+6E list (as numpy arrays or tensors) and keeps the router and this rank's experts."""
+        import numpy as np
+        mine = list(full_params[:2]) + list(full_params[2 + 6 * self.first_expert: 2 + 6 * (self.first_expert + self.E_local)])
+        for p, a in zip(self.get_parameters(), mine):
+            t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)) if not torch.is_tensor(a) else a
+            p.copy_(t.reshape(p.shape))
+        self.stages.sync_weights()
+
+    def zero_grad(self):
+        for p in self.get_parameters():
+            p.grad.zero_()
+
+    def allreduce_router_grads(self):
+        """Sum the router gradients over the group so that the replicas stay identical."""
+        if self.world > 1:
+            for p in self.stages.router_params:
+                dist.all_reduce(p.grad, group=self.group)
+
+    # ---- exchange helpers
+    def _all_to_all(self, send, send_splits, recv_splits):
+        recv = send.new_empty((int(sum(recv_splits)),) + tuple(send.shape[1:]))
+        if self.world == 1:
+            recv.copy_(send)
+        else:
+            dist.all_to_all_single(recv, send.contiguous(), list(recv_splits), list(send_splits), group=self.group)
+        return recv
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        G, El = self.world, self.E_local
+        rows, counts = self.stages.route(x)                          # [R,C] compact expert-major, counts[E]
+        counts = counts.view(G, El)
+        recv_counts = torch.empty_like(counts)                       # [source rank, local expert]
+        if G == 1:
+            recv_counts.copy_(counts)
+        else:
+            dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)
+        both = torch.stack([counts.sum(1), recv_counts.sum(1)]).cpu()   # the one host sync of the step
+        send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+        recv_rows = self._all_to_all(rows, send_splits, recv_splits)
+        expert_ids = torch.arange(El, device=recv_counts.device, dtype=torch.int32).repeat(G)
+        expert_of_row = torch.repeat_interleave(expert_ids, recv_counts.reshape(-1).to(torch.int64),
+                                                output_size=int(sum(recv_splits))).to(torch.int32)
+        out_rows = self.stages.experts_forward(recv_rows, expert_of_row)
+        rows_back = self._all_to_all(out_rows, recv_splits, send_splits)
+        y = self.stages.combine(rows_back, x)
+        self._saved = (x, rows_back, send_splits, recv_splits)
+        self.last_recv_counts = recv_counts
+        return y
+
+    def backward(self, dy: torch.Tensor) -> torch.Tensor:
+        if self._saved is None:
+            raise RuntimeError("backward before forward")
+        x, rows_back, send_splits, recv_splits = self._saved
+        d_rows = self.stages.combine_backward(rows_back, dy)
+        d_recv = self._all_to_all(d_rows, send_splits, recv_splits)
+        d_in = self.stages.experts_backward(d_recv)
+        d_back = self._all_to_all(d_in, recv_splits, send_splits)
+        return self.stages.route_backward(x, d_back)

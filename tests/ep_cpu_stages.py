@@ -1,0 +1,111 @@
+"""A CPU stand-in for the six stage-level entry points (numpy + the CPU oracle's routing).
+
+Test infrastructure: lets the host logic of mgpt_b200/ep.py (count exchange, split sizes,
+row order, regrouping) run under gloo without a GPU.
+"""
+import numpy as np
+import torch
+
+from oracle import oracle
+
+
+def _silu(g):
+    return g / (1.0 + np.exp(-g))
+
+
+class CpuStages:
+    def __init__(self, C, H, E, k, E_local, alpha=0.01):
+        self.C, self.H, self.E, self.k, self.E_local, self.alpha = C, H, E, k, E_local, alpha
+        z = lambda *s: torch.zeros(*s, dtype=torch.float32)
+        self.router_params = [z(C, E), z(1, E)]
+        self.expert_params = []
+        for _ in range(E_local):
+            self.expert_params += [z(C, H), z(1, H), z(C, H), z(1, H), z(H, C), z(1, C)]
+        for p in self.router_params + self.expert_params:
+            p.grad = torch.zeros_like(p)
+
+    def sync_weights(self):
+        pass
+
+    # ---- routing side
+    def route(self, x):
+        xn = x.numpy()
+        n = xn.shape[0]
+        dummy = [np.zeros(s, np.float32) for s in oracle.param_shapes(self.C, self.H, self.E)[2:]]
+        params = [p.numpy() for p in self.router_params] + dummy
+        r = oracle.run(oracle.Dims(n, self.C, self.H, self.E, self.k, self.alpha), xn, params, route_only=True)
+        self.r, self.n = r, n
+        rows = xn[r["map"] // self.k]
+        return torch.from_numpy(np.ascontiguousarray(rows)), torch.from_numpy(r["counts"].copy())
+
+    def combine(self, rows_back, like):
+        r, k = self.r, self.k
+        y = np.zeros((self.n, self.C), np.float32)
+        rb = rows_back.numpy()
+        for s in range(self.n * k):
+            flat = r["map"][s]
+            y[flat // k] += rb[s] * r["top_p"].reshape(-1)[flat]
+        return torch.from_numpy(y)
+
+    def combine_backward(self, rows_back, dy):
+        r, k = self.r, self.k
+        rb, g = rows_back.numpy(), dy.numpy()
+        d_rows = np.zeros_like(rb)
+        self.dtp = np.zeros(self.n * k, np.float32)
+        for s in range(self.n * k):
+            flat = r["map"][s]
+            d_rows[s] = g[flat // k] * r["top_p"].reshape(-1)[flat]
+            self.dtp[flat] = float(rb[s] @ g[flat // k])
+        return torch.from_numpy(d_rows)
+
+    def route_backward(self, x, d_rows):
+        r, k, E, n = self.r, self.k, self.E, self.n
+        xn, dr = x.numpy(), d_rows.numpy()
+        dx = np.zeros_like(xn)
+        for s in range(n * k):
+            dx[r["map"][s] // k] += dr[s]
+        dP = np.zeros((n, E), np.float32)
+        flat_e = r["top_idx"].reshape(-1)
+        dP[np.arange(n * k) // k, flat_e] = self.dtp
+        dP += (self.alpha * E * (r["counts"].astype(np.float32) / n)) / n
+        P = r["probs"]
+        dL = P * (dP - (dP * P).sum(1, keepdims=True))
+        Wr = self.router_params[0].numpy()
+        self.router_params[0].grad += torch.from_numpy(xn.T @ dL)
+        self.router_params[1].grad += torch.from_numpy(dL.sum(0, keepdims=True))
+        return torch.from_numpy(dx + dL @ Wr.T)
+
+    # ---- expert side
+    def experts_forward(self, rows, expert_of_row):
+        X, eo = rows.numpy(), expert_of_row.numpy()
+        out = np.zeros_like(X)
+        self.saved = []
+        for e in range(self.E_local):
+            idx = np.nonzero(eo == e)[0]
+            Wg, bg, Wu, bu, Wd, bd = [p.numpy() for p in self.expert_params[6 * e: 6 * e + 6]]
+            xe = X[idx]
+            G, U = xe @ Wg + bg, xe @ Wu + bu
+            Hh = _silu(G) * U
+            out[idx] = Hh @ Wd + bd
+            self.saved.append((idx, xe, G, U, Hh))
+        return torch.from_numpy(out)
+
+    def experts_backward(self, d_out):
+        D = d_out.numpy()
+        d_in = np.zeros_like(D)
+        for e, (idx, xe, G, U, Hh) in enumerate(self.saved):
+            p = self.expert_params[6 * e: 6 * e + 6]
+            Wg, Wu, Wd = p[0].numpy(), p[2].numpy(), p[4].numpy()
+            dy = D[idx]
+            p[5].grad += torch.from_numpy(dy.sum(0, keepdims=True))
+            p[4].grad += torch.from_numpy(Hh.T @ dy)
+            dH = dy @ Wd.T
+            sig = 1.0 / (1.0 + np.exp(-G))
+            dU = dH * (G * sig)
+            dG = (dH * U) * (sig * (1.0 + G * (1.0 - sig)))
+            p[1].grad += torch.from_numpy(dG.sum(0, keepdims=True))
+            p[0].grad += torch.from_numpy(xe.T @ dG)
+            p[3].grad += torch.from_numpy(dU.sum(0, keepdims=True))
+            p[2].grad += torch.from_numpy(xe.T @ dU)
+            d_in[idx] = dG @ Wg.T + dU @ Wu.T
+        return torch.from_numpy(d_in.astype(np.float32))

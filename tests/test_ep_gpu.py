@@ -1,0 +1,61 @@
+"""Expert-parallel layer on GPUs: stage-level C-ABI entry points + NCCL all-to-all."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mgpt_b200 import synth
+from mgpt_b200.ep import CudaStages
+from tests.ep_common import init_pg, run_rank
+
+pytestmark = pytest.mark.gpu
+
+
+def _stages(mode, device):
+    return lambda w, el: CudaStages(w.C, w.H, w.E, w.k, el, mode=mode, device=device, lb_alpha=w.alpha)
+
+
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-5), ("bf16", 2e-2)])
+def test_stage_entry_points_one_gpu(mode, tol):
+    """World size 1: the six stage calls compose to the whole layer."""
+    w = synth.Workload("ep1", 600, 128, 192, 8, 2, mode)
+    io = torch.bfloat16 if mode == "bf16" else torch.float32
+    run_rank(w, 0, 1, _stages(mode, 0), "cuda:0", tol, io=io)
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ["NCCL_NVLS_ENABLE"] = "0"
+        torch.cuda.set_device(rank)
+        init_pg(rank, world, "nccl", port)
+        w = synth.Workload("ep", 1500, 256, 320, 8, 2, "bf16")
+        run_rank(w, rank, world, _stages("bf16", rank), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        w = synth.Workload("epskew", 900, 128, 128, 16, 4, "bf16", skew=True)
+        run_rank(w, rank, world, _stages("bf16", rank), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_two_gpus_nccl():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
