@@ -24,6 +24,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "moe_layer_fwd_bwd_tokens_per_sec"
+# DRAM bytes (read + write) per launch from ncu captures, keyed by (workload, stage); see profiles/
+TRAFFIC = {}
 UNIT = "tokens/s"
 
 
@@ -144,36 +146,93 @@ def stage_model(w):
     return flops, byts
 
 
-def run_ours(args, w):
+def init_weights(params, w, dev, seed_of):
+    """Random-init weights of the architecture: N(0, 0.02), biases 0 (the router bias carries the skew);
+    values rounded to bf16 for bf16 workloads.  seed_of(i) seeds tensor i."""
     import torch
-    import torch.distributed as dist
-
-    from mgpt_b200 import MoELayer, launch_count, synth
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    peaks = load_peaks()
-
-    N, C = w.n_tokens, w.C
-    io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
-    layer = MoELayer(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha)
-    # random-init weights of the architecture, N(0, 0.02); biases 0 (router bias carries the skew)
-    g = torch.Generator(device=dev)
-    g.manual_seed(1234 + rank)
-    for i, p in enumerate(layer.get_parameters()):
+    for i, p in enumerate(params):
         if p.shape[0] == 1:
             p.zero_()
             if i == 1 and w.skew:
                 p.copy_((2.0 * torch.log(1.0 / (torch.arange(w.E, device=dev, dtype=torch.float64) + 1.0))).float()[None, :])
         else:
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed_of(i))
             p.normal_(0.0, 0.02, generator=g)
             if w.dtype == "bf16":
                 p.copy_(p.to(torch.bfloat16).float())
+
+
+def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms, set_profiling, barrier, N, io_bytes):
+    """Warm-up, K timed steps (CUDA events, L2 flushed between steps, max over ranks), then the host-buffer path."""
+    import torch
+    import torch.distributed as dist
+
+    from mgpt_b200 import launch_count
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    set_profiling(True)
+    barrier()
+    sampler = ClockSampler(dev.index) if rank == 0 else None
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    stage_sum = {}
+    launch_count(reset=True)
+    for s, e in ev:
+        flush.zero_()                      # L2 flush between timed iterations, outside the events
+        if world > 1:
+            dist.barrier()                 # ranks enter each timed step together
+        s.record()
+        step()
+        e.record()
+        e.synchronize()
+        for name, ms in stage_ms().items():
+            stage_sum[name] = stage_sum.get(name, 0.0) + ms
+    launches = launch_count()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    set_profiling(False)
+    total_ms = sum(s.elapsed_time(e) for s, e in ev)
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+
+    for _ in range(2):
+        step_host()
+    barrier()
+    e2e_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        step_host()
+        e2e_ms += (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.steps
+    n_dir = 2 if w.backward else 1
+    checksum = host_checksum()             # of the last step's output, computed outside the timed region
+    e2e = {"value": world * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": io_bytes * n_dir, "d2h_bytes_per_step": io_bytes * n_dir, "checksum": checksum}
+    return ms_per_step, stage_sum, int(launches), clocks, e2e
+
+
+def single_gpu_pass(args, w, rank, dev):
+    """One replica of the whole layer on this GPU (all experts local)."""
+    import torch
+
+    from mgpt_b200 import MoELayer
+
+    N, C = w.n_tokens, w.C
+    io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode=w.dtype, device=dev.index, lb_alpha=w.alpha)
+    init_weights(layer.get_parameters(), w, dev, lambda i: 1234 + i)
     layer.sync_weights()
     x_host = torch.randn(N, C, generator=torch.Generator().manual_seed(99 + rank)).to(io).pin_memory()
     dy_host = torch.randn(N, C, generator=torch.Generator().manual_seed(199 + rank)).to(io).pin_memory()
@@ -181,69 +240,100 @@ def run_ours(args, w):
     dx_host = torch.empty_like(x_host).pin_memory()
     x, dy = x_host.to(dev), dy_host.to(dev)
     y, dx = torch.empty_like(x), torch.empty_like(x)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
 
     def step():
         layer.forward_into(x, y)
         if w.backward:
             layer.backward_into(dy, dx)
 
+    def step_host():
+        layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
+
+    def host_checksum():
+        return float(y_host[:4096].float().abs().mean())
+
     def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
 
     layer.zero_grad()
-    for _ in range(max(args.warmup, 3)):
-        flush.zero_()
-        step()
-    layer.set_profiling(True)
-    barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    stage_sum = {}
-    launch_count(reset=True)
-    for s, e in ev:
-        flush.zero_()                      # L2 flush between timed iterations, outside the events
-        s.record()
-        step()
-        e.record()
-        e.synchronize()
-        for name, ms in layer.stage_ms().items():
-            stage_sum[name] = stage_sum.get(name, 0.0) + ms
-    launches = launch_count()
-    barrier()
-    clocks = sampler.stop() if sampler else None
-    layer.set_profiling(False)
-    total_ms = sum(s.elapsed_time(e) for s, e in ev)
-    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
+    res = measure(args, w, 1, 0, dev, step, step_host, host_checksum, layer.stage_ms, layer.set_profiling, barrier, N,
+                  x_host.numel() * x_host.element_size())
+    layer.close()
+    return res
+
+
+def run_ours(args, w):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    peaks = load_peaks()
+    N, C = w.n_tokens, w.C
+    reference_1gpu = None
+
+    if world == 1:
+        ms_per_step, stage_sum, launches, clocks, e2e = single_gpu_pass(args, w, rank, dev)
+        parallelism = "single GPU"
+    else:
+        from mgpt_b200.ep import ExpertParallelMoE
+
+        dist.init_process_group("nccl", device_id=dev)
+        if w.E % world:
+            raise SystemExit(f"workload {w.name}: {w.E} experts do not divide over {world} GPUs")
+        if rank == 0 and not args.no_single:
+            # the same per-GPU problem on one GPU with every expert local: the reference point of the scaling
+            r = single_gpu_pass(args, w, rank, dev)
+            reference_1gpu = {"n_gpus": 1, "value": N / (r[0] * 1e-3), "unit": UNIT, "ms_per_step": r[0],
+                              "workload": describe(w), "note": "all experts local, no exchange"}
+            torch.cuda.empty_cache()
+        dist.barrier()
+        io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+        layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha)
+        E_local = w.E // world
+        params = layer.get_parameters()
+        # router: same values on every rank; experts: seeded by their global index
+        init_weights(params, w, dev, lambda i: 1234 + (i if i < 2 else i + 6 * rank * E_local))
+        layer.stages.sync_weights()
+        x_host = torch.randn(N, C, generator=torch.Generator().manual_seed(99 + rank)).to(io).pin_memory()
+        dy_host = torch.randn(N, C, generator=torch.Generator().manual_seed(199 + rank)).to(io).pin_memory()
+        y_host = torch.empty_like(x_host).pin_memory()
+        dx_host = torch.empty_like(x_host).pin_memory()
+        x, dy = x_host.to(dev), dy_host.to(dev)
+
+        def step():
+            layer.forward(x)
+            if w.backward:
+                layer.backward(dy)
+
+        def step_host():
+            xd = x_host.to(dev, non_blocking=True)
+            y = layer.forward(xd)
+            y_host.copy_(y, non_blocking=True)
+            if w.backward:
+                dyd = dy_host.to(dev, non_blocking=True)
+                dx_host.copy_(layer.backward(dyd), non_blocking=True)
+            torch.cuda.synchronize()
+
+        def host_checksum():
+            return float(y_host[:4096].float().abs().mean())
+
+        def barrier():
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+
+        layer.zero_grad()
+        ms_per_step, stage_sum, launches, clocks, e2e = measure(
+            args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms, layer.stages.set_profiling, barrier, N,
+            x_host.numel() * x_host.element_size())
+        parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
+                       "NCCL all-to-all for dispatch and combine (4 per step)")
+
     value = world * N / (ms_per_step * 1e-3)
-
-    # end to end through the host-buffer entry point
-    for _ in range(2):
-        layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
-    barrier()
-    e2e_ms = 0.0
-    for _ in range(args.steps):
-        flush.zero_()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
-        e2e_ms += (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
-    io_bytes = x_host.numel() * x_host.element_size()
-    e2e = {"value": world * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": io_bytes * (2 if w.backward else 1),
-           "d2h_bytes_per_step": io_bytes * (2 if w.backward else 1), "checksum": float(y_host.float().abs().mean())}
-
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -259,7 +349,7 @@ def run_ours(args, w):
         ent = {"ms": round(ms, 4)}
         if name in flops:
             ent["tflops"] = round(flops[name] / (ms * 1e-3) / 1e12, 1)
-        elif name in byts:
+        elif name in byts and world == 1:
             ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
         stages[name] = ent
     launches_per = {"gateup_gemm": 1, "down_gemm": 1, "dhh_gemm": 1, "dxg_gemm": 1, "wgrad_gemm": 3}
@@ -272,7 +362,7 @@ def run_ours(args, w):
         peak = peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "unit": "TFLOP/s",
-                    "frac": round(achieved / peak, 4), "traffic": None,
+                    "frac": round(achieved / peak, 4), "traffic": TRAFFIC.get((w.name, dom)),
                     "all_gemms_tflops": round(sum(flops[k] for k in gemm) / (sum(v["ms"] for v in gemm.values()) * 1e-3) / 1e12, 1)}
 
     cpu = None
@@ -287,11 +377,13 @@ def run_ours(args, w):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": describe(w), "parallelism": "one replica per GPU, tokens sharded, no exchange" if world > 1 else "single GPU",
+        "config": {"workload": describe(w), "parallelism": parallelism,
                    "l2": "flushed between timed steps by a 256 MiB write", "hbm_peak_gbs": peaks["hbm_gbs"]},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "stages": stages,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "stages": stages,
         "cpu_baseline": cpu,
     }
+    if reference_1gpu:
+        line["same_workload_on_one_gpu"] = reference_1gpu
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -306,10 +398,13 @@ def main():
     ap.add_argument("--workload", default=None, help="c1 c2 c3 c4 c5-8 c5-64 c5-256 (default c2)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="tokens per CPU-baseline step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-single", action="store_true", help="N>1: skip the one-GPU pass of the same workload")
     args = ap.parse_args()
 
     from mgpt_b200 import synth
-    w = synth.WORKLOADS[args.workload or "c2"]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    # one GPU: the medium configuration the metric is quoted on; several GPUs: the expert-parallel one
+    w = synth.WORKLOADS[args.workload or ("c2" if world == 1 else "c4")]
     if args.impl == "reference":
         run_reference_arm(args, w)
     else:

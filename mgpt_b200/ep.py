@@ -98,6 +98,15 @@ class CudaStages:
         self._lib_mod.check(self.lib.mgpt_moe_workspace_view(handle, n, name.encode(), ct.byref(off), ct.byref(nb)))
         return ws[off.value: off.value + nb.value].view(dtype)
 
+    # ---- per-stage timing of the expert side (CUDA events inside the library)
+    def set_profiling(self, enabled: bool) -> None:
+        self._lib_mod.check(self.lib.mgpt_moe_set_profiling(self.local, 1 if enabled else 0))
+
+    def stage_ms(self) -> dict:
+        buf = (ct.c_float * self._lib_mod.N_STAGES)()
+        self._lib_mod.check(self.lib.mgpt_moe_stage_ms(self.local, buf))
+        return {self.lib.mgpt_moe_stage_name(i).decode(): float(buf[i]) for i in range(self._lib_mod.N_STAGES)}
+
     # ---- routing side
     def route(self, x):
         n = x.shape[0]
