@@ -83,6 +83,7 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
         w.rw_chunks = chunks;
     }
     w.rw_part = take((size_t)w.rw_chunks * (C * E + E) * 4);
+    w.dl16 = take(N * ((E + 7) / 8 * 8) * 2);          // dlogits in bf16 for the tensor-core router backward
     w.total = off;
     return w;
 }
@@ -140,6 +141,11 @@ int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
     L->shadow.Wg = (const void**)tab(12); L->shadow.Wu = (const void**)tab(13); L->shadow.Wd = (const void**)tab(14);
 
     if (cfg->mode == MGPT_MOE_BF16) {
+        e = cudaMalloc(&L->sWr, (size_t)C * ((E + 7) / 8 * 8) * sizeof(bf16));
+        if (e != cudaSuccess) {
+            mgpt_moe_destroy(L);
+            return cuda_fail(e, "cudaMalloc(router shadow)");
+        }
         const size_t n = (size_t)E * C * H;
         bf16** s[6] = {&L->sWg, &L->sWu, &L->sWd, &L->sWgT, &L->sWuT, &L->sWdT};
         for (auto p : s) {
@@ -162,6 +168,7 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
     cudaFree(L->d_tables);
     cudaFree(L->sWg); cudaFree(L->sWu); cudaFree(L->sWd);
     cudaFree(L->sWgT); cudaFree(L->sWuT); cudaFree(L->sWdT);
+    cudaFree(L->sWr);
     cudaFree(L->h_x); cudaFree(L->h_dy); cudaFree(L->h_y); cudaFree(L->h_dx); cudaFree(L->h_ws);
     for (int s = 0; s < ST_COUNT; ++s) {
         if (L->ev_begin[s]) cudaEventDestroy(L->ev_begin[s]);
@@ -233,10 +240,6 @@ int mgpt_moe_sync_weights(mgpt_moe_layer* L, mgpt_stream_t stream)
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
     if (!L->router_bound && !L->experts_bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
     MGPT_CUDA(cudaSetDevice(L->device));
-    if (!L->experts_bound) {          // routing side: nothing to shadow
-        L->shadows_fresh = true;
-        return 0;
-    }
     return launch_sync_weights(L, (cudaStream_t)stream);
 }
 

@@ -62,7 +62,7 @@ struct Workspace {
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries
-    size_t dYg, dG, dU, dXg, d_top_p, dlogits, rw_part;
+    size_t dYg, dG, dU, dXg, d_top_p, dlogits, rw_part, dl16;
     size_t total;
     // derived sizes
     int n_tokens, R, max_tiles, row_cap, plan_blocks, rw_chunks;
@@ -104,6 +104,7 @@ struct mgpt_moe_layer {
     // BF16 shadows, contiguous over experts (BF16 mode only)
     mgpt::bf16 *sWg = nullptr, *sWu = nullptr, *sWd = nullptr;      // [E][C][H],[E][C][H],[E][H][C]
     mgpt::bf16 *sWgT = nullptr, *sWuT = nullptr, *sWdT = nullptr;   // [E][H][C],[E][H][C],[E][C][H]
+    mgpt::bf16* sWr = nullptr;                                      // router weight [C][E8], E8 = E rounded up to 8
 
     // last forward (for backward / counts)
     int last_n = 0, last_io = 0;
@@ -142,7 +143,7 @@ namespace mgpt {
 // router.cu
 int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, int N, int C, int E, int k,
                       float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st);
-int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
+int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
                       void* dx, cudaStream_t st, const void* dXg_rows = nullptr, const int32_t* pos_rows = nullptr);
 
 // plan.cu
@@ -170,6 +171,9 @@ int simt_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaS
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 void tc_destroy(mgpt_moe_layer* L);
+int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dXg, const int32_t* pos, void* dx,
+                 cudaStream_t st);
+int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st);
 
 // weights.cu
 int launch_sync_weights(mgpt_moe_layer* L, cudaStream_t st);

@@ -281,7 +281,7 @@ __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w <<
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 // ---- token-major products ------------------------------------------------------
-enum { MODE_GATEUP = 0, MODE_DOWN = 1, MODE_DHH = 2, MODE_DXG = 3 };
+enum { MODE_GATEUP = 0, MODE_DOWN = 1, MODE_DHH = 2, MODE_DXG = 3, MODE_DX = 4 };
 
 struct RowsP {
     const int32_t* tile_expert;
@@ -294,6 +294,12 @@ struct RowsP {
     const bf16 *G, *U;      // saved pre-activations (MODE_DHH), row stride n_out
     const float* const* bias0;
     const float* const* bias1;
+    // MODE_DX only: row tiles are token tiles (no experts); the epilogue adds the expert rows of each token
+    int fixed_tiles;            // number of 128-token tiles
+    int n_valid_rows;           // tokens
+    const bf16* gather_src;     // dXg rows [*, n_out]
+    const int32_t* gather_pos;  // [tokens, gather_k] row of dXg for (token, j)
+    int gather_k;
 };
 
 // Persistent: CTA b works on items b, b+grid, ... where item = row_tile * n_col_tiles + col_tile.
@@ -307,7 +313,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                const __grid_constant__ CUtensorMap tmD2, const RowsP p)
 {
     extern __shared__ uint8_t smem_raw[];
-    const int total_items = *p.n_tiles * p.n_col_tiles;
+    const int total_items = (MODE == MODE_DX ? p.fixed_tiles : *p.n_tiles) * p.n_col_tiles;
     if ((int)blockIdx.x >= total_items) return;          // whole CTA leaves before any barrier or TMEM use
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int COLS_PER_ITEM = MODE == MODE_GATEUP ? BN / 2 : BN;
@@ -322,7 +328,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
-                const int brow = p.tile_expert[row_tile] * p.b_rows_per_expert + n0;
+                const int brow = (MODE == MODE_DX ? 0 : p.tile_expert[row_tile] * p.b_rows_per_expert) + n0;
                 const int row0 = row_tile * BM;
                 for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -383,7 +389,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++t) {
             const uint32_t buf = t & 1u;
             const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
-            const int e = p.tile_expert[row_tile];
+            const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
             const int row_w = row_tile * BM + q * 32;           // first row of this warp
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
@@ -481,6 +487,50 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         flush_stage(stage, &tmD0, n, row_w, lane);
                         stage_row_bf16(stage, lane, pu);
                         flush_stage(stage, &tmD1, n, row_w, lane);
+                    } else if (MODE == MODE_DX) {
+                        // dx = (sum of the token's expert rows, ascending row order) + dlogits * Wr^T
+                        const int tok = row_w + lane;
+                        float s0[32], s1[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) s0[j] = s1[j] = 0.0f;
+                        if (tok < p.n_valid_rows) {
+                            int ps[MAX_TOPK];
+#pragma unroll
+                            for (int j = 0; j < MAX_TOPK; ++j)
+                                ps[j] = j < p.gather_k ? p.gather_pos[(size_t)tok * p.gather_k + j] : 0x7fffffff;
+#pragma unroll
+                            for (int a = 0; a < MAX_TOPK - 1; ++a)
+#pragma unroll
+                                for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
+                                    if (ps[b] > ps[b + 1]) {
+                                        const int tmp = ps[b];
+                                        ps[b] = ps[b + 1];
+                                        ps[b + 1] = tmp;
+                                    }
+                            const int valid = min(64, p.n_out - n);
+#pragma unroll
+                            for (int j = 0; j < MAX_TOPK; ++j) {
+                                if (j < p.gather_k) {
+                                    const bf16* src = p.gather_src + (size_t)ps[j] * p.n_out + n;
+                                    float g0[32], g1[32];
+                                    load_bf16x32(src, g0, valid);
+                                    load_bf16x32(src + 32, g1, valid - 32);
+#pragma unroll
+                                    for (int i = 0; i < 32; ++i) {
+                                        s0[i] += g0[i];
+                                        s1[i] += g1[i];
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            v0[i] += s0[i];
+                            v1[i] += s1[i];
+                        }
+                        pack64(v0, v1, pk);
+                        stage_row_bf16(stage, lane, pk);
+                        flush_stage(stage, &tmD0, n, row_w, lane);
                     } else {
                         pack64(v0, v1, pk);
                         stage_row_bf16(stage, lane, pk);
@@ -500,6 +550,9 @@ struct WgradP {
     int32_t* status;
     float* const* grad;
     int M, N, n_tiles_m, n_tiles_n, E;
+    // router gradient: the "experts" are uniform chunks of uniform_rows tokens that all add into single_grad
+    int uniform_rows;
+    float* single_grad;
 };
 
 // Persistent over items (expert, m tile, n tile); experts without rows are skipped.
@@ -522,7 +575,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 const int e = item / per_expert, r = item % per_expert;
-                const int r0 = p.padded_offsets[e], nkb = (p.padded_offsets[e + 1] - r0) / BK;
+                const int r0 = p.uniform_rows ? e * p.uniform_rows : p.padded_offsets[e];
+                const int nkb = (p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - r0) / BK;
                 const int m0 = (r / p.n_tiles_n) * BM, n0 = (r % p.n_tiles_n) * BN;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -547,7 +601,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 const int e = item / per_expert;
-                const int nkb = (p.padded_offsets[e + 1] - p.padded_offsets[e]) / BK;
+                const int nkb = (p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - p.padded_offsets[e]) / BK;
                 if (nkb <= 0) continue;
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
@@ -580,7 +634,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint32_t t = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
             const int e = item / per_expert, r = item % per_expert;
-            if (p.padded_offsets[e + 1] - p.padded_offsets[e] < BK) continue;
+            if ((p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - p.padded_offsets[e]) < BK) continue;
             const uint32_t buf = t & 1u;
             const int m_w = (r / p.n_tiles_n) * BM + q * 32;             // first output row of this warp
             const int n_w = (r % p.n_tiles_n) * BN + h * 128;            // first output column of this warp
@@ -591,7 +645,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + c * 32, v[c]);
             release_acc(pipe.acc_empty(buf), lane);
-            float* g = p.grad[e];
+            float* g = p.single_grad ? p.single_grad : p.grad[e];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int n = n_w + c * 32;
@@ -666,19 +720,12 @@ struct TcState {
     CUtensorMap G_s, U_s, Hh_s, Yg_s, dG_s, dU_s, dXg_s;
 };
 
+int prepare_attrs(mgpt_moe_layer* L);
+
 int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
 {
-    if (!L->tc_state) L->tc_state = new TcState();
+    MGPT_TRY(prepare_attrs(L));
     TcState* s = (TcState*)L->tc_state;
-    if (!s->attr_set) {
-        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DHH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
-        s->attr_set = true;
-    }
     if (s->ws == ws && s->n_tokens == w.n_tokens) return 0;
     const Dims& d = L->d;
     const uint64_t rc = w.row_cap, C = d.C, H = d.H, E = d.E;
@@ -707,6 +754,23 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->dXg_s, ws + w.dXg, rc, C, 32));
     s->ws = ws;
     s->n_tokens = w.n_tokens;
+    return 0;
+}
+
+int prepare_attrs(mgpt_moe_layer* L)
+{
+    if (!L->tc_state) L->tc_state = new TcState();
+    TcState* s = (TcState*)L->tc_state;
+    if (!s->attr_set) {
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DHH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
+        s->attr_set = true;
+    }
     return 0;
 }
 
@@ -789,6 +853,55 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     tc_wgrad_kernel<<<imin(s->sms, d.E * g.n_tiles_m * g.n_tiles_n), TC_THREADS, SMEM_BYTES, st>>>(s->Hh_t, s->dYg_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wd>");
     L->stage_end(ST_WGRAD, st);
+    return 0;
+}
+
+// dx[N,C] (bf16) = gather-sum of the tokens' expert rows + dlogits * Wr^T on the tensor cores
+// (K = experts, so the product is a single k-block; the kernel is bound by the row gather).
+int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dXg, const int32_t* pos, void* dx,
+                 cudaStream_t st)
+{
+    MGPT_TRY(prepare_attrs(L));
+    TcState* s = (TcState*)L->tc_state;
+    const Dims& d = L->d;
+    const int E8 = (d.E + 7) / 8 * 8;
+    CUtensorMap mA, mB, mD;
+    MGPT_TRY(make_map(&mA, ws + w.dl16, (uint64_t)w.n_tokens, (uint64_t)E8, 128));
+    MGPT_TRY(make_map(&mB, L->sWr, (uint64_t)d.C, (uint64_t)E8, 128));
+    MGPT_TRY(make_map(&mD, dx, (uint64_t)w.n_tokens, (uint64_t)d.C, 32));
+    RowsP p = {};
+    p.n_tiles = (const int32_t*)(ws + w.n_tiles);
+    p.tile_expert = (const int32_t*)(ws + w.tile_expert);
+    p.status = (int32_t*)(ws + w.status);
+    p.kblocks = cdiv(E8, BK); p.n_out = d.C; p.b_rows_per_expert = 0; p.n_col_tiles = cdiv(d.C, BN);
+    p.fixed_tiles = cdiv(w.n_tokens, BM); p.n_valid_rows = w.n_tokens;
+    p.gather_src = (const bf16*)dXg; p.gather_pos = pos; p.gather_k = d.k;
+    tc_rows_kernel<MODE_DX><<<imin(s->sms, p.fixed_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+        mA, mA, mB, mB, mD, mD, mD, p);
+    MGPT_LAUNCHED("tc_rows_kernel<dx>");
+    return 0;
+}
+
+// gWr[C,E] += x^T * dlogits on the tensor cores, split over uniform token chunks (RED accumulation).
+int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st)
+{
+    MGPT_TRY(prepare_attrs(L));
+    TcState* s = (TcState*)L->tc_state;
+    const Dims& d = L->d;
+    const int E8 = (d.E + 7) / 8 * 8;
+    CUtensorMap mA, mB;
+    MGPT_TRY(make_map(&mA, x, (uint64_t)w.n_tokens, (uint64_t)d.C, 64));
+    MGPT_TRY(make_map(&mB, ws + w.dl16, (uint64_t)w.n_tokens, (uint64_t)E8, 64));
+    WgradP g = {};
+    g.status = (int32_t*)(ws + w.status);
+    g.M = d.C; g.N = d.E; g.n_tiles_m = cdiv(d.C, BM); g.n_tiles_n = cdiv(d.E, BN);
+    const int per_chunk = g.n_tiles_m * g.n_tiles_n;
+    int chunks = imin(64, (2 * s->sms + per_chunk - 1) / per_chunk);
+    int rows = cdiv(cdiv(w.n_tokens, chunks), BK) * BK;           // tokens per chunk, whole k-blocks
+    chunks = cdiv(w.n_tokens, rows);
+    g.E = chunks; g.uniform_rows = rows; g.single_grad = L->p_grad[0];
+    tc_wgrad_kernel<<<imin(s->sms, chunks * per_chunk), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, g);
+    MGPT_LAUNCHED("tc_wgrad_kernel<Wr>");
     return 0;
 }
 

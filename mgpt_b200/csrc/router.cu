@@ -163,44 +163,71 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 }
 
 // dlogits = P * (dP - <dP,P>),  dP = scatter(d_top_p) + alpha*E*f_e/N
-// (layers/MoELayer.cpp:189-210).  One warp per token.
+// (layers/MoELayer.cpp:189-210).  One warp per token, grid-stride over tokens.  Optionally also
+// writes a bf16 copy with rows padded to E8 columns (for the tensor-core backward) and adds
+// the column sums to gbr (layers/LinearLayer.cpp:56-57).
 template <int EPL>
 __global__ void __launch_bounds__(256)
 router_dlogits_kernel(const float* __restrict__ probs, const int32_t* __restrict__ top_idx,
                       const float* __restrict__ d_top_p, const int32_t* __restrict__ counts,
-                      int N, int E, int k, float alpha, float* __restrict__ dlogits)
+                      int N, int E, int k, float alpha, float* __restrict__ dlogits,
+                      bf16* __restrict__ dl16, int E8, float* __restrict__ gbr)
 {
-    const int lane = threadIdx.x & 31;
-    const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (tok >= N) return;
+    __shared__ float bred[8][EPL * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned full = 0xffffffffu;
-    float p[EPL], dp[EPL];
+    float lb[EPL], bsum[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
         const int e = lane + 32 * i;
-        p[i] = 0.0f;
-        dp[i] = 0.0f;
+        bsum[i] = 0.0f;
+        lb[i] = 0.0f;
         if (e < E) {
-            p[i] = probs[(size_t)tok * E + e];
             const float f = __fdiv_rn((float)counts[e], (float)N);
-            const float lb = __fdiv_rn(__fmul_rn(__fmul_rn(alpha, (float)E), f), (float)N);
-            float sel = 0.0f;
-            for (int j = 0; j < k; ++j)
-                if (top_idx[(size_t)tok * k + j] == e) sel = d_top_p[(size_t)tok * k + j];
-            dp[i] = __fadd_rn(sel, lb);
+            lb[i] = __fdiv_rn(__fmul_rn(__fmul_rn(alpha, (float)E), f), (float)N);
         }
     }
-    float dot = 0.0f;
+    for (int tok = blockIdx.x * 8 + warp; tok < N; tok += gridDim.x * 8) {
+        float p[EPL], dp[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-        const float prod = __fmul_rn(dp[i], p[i]);
-        const int lim = min(32, E - 32 * i);
-        for (int l = 0; l < lim; ++l) dot = __fadd_rn(dot, __shfl_sync(full, prod, l));
+        for (int i = 0; i < EPL; ++i) {
+            const int e = lane + 32 * i;
+            p[i] = 0.0f;
+            dp[i] = 0.0f;
+            if (e < E) {
+                p[i] = probs[(size_t)tok * E + e];
+                float sel = 0.0f;
+                for (int j = 0; j < k; ++j)
+                    if (top_idx[(size_t)tok * k + j] == e) sel = d_top_p[(size_t)tok * k + j];
+                dp[i] = __fadd_rn(sel, lb[i]);
+            }
+        }
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const float prod = __fmul_rn(dp[i], p[i]);
+            const int lim = min(32, E - 32 * i);
+            for (int l = 0; l < lim; ++l) dot = __fadd_rn(dot, __shfl_sync(full, prod, l));
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int e = lane + 32 * i;
+            const float v = e < E ? __fmul_rn(p[i], __fsub_rn(dp[i], dot)) : 0.0f;
+            if (e < E) dlogits[(size_t)tok * E + e] = v;
+            if (dl16 && e < E8) dl16[(size_t)tok * E8 + e] = __float2bfloat16(v);
+            bsum[i] += v;
+        }
     }
+    if (gbr) {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-        const int e = lane + 32 * i;
-        if (e < E) dlogits[(size_t)tok * E + e] = __fmul_rn(p[i], __fsub_rn(dp[i], dot));
+        for (int i = 0; i < EPL; ++i) bred[warp][lane + 32 * i] = bsum[i];
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            float t = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < 8; ++wv) t += bred[wv][e];
+            atomicAdd(&gbr[e], t);
+        }
     }
 }
 
@@ -423,7 +450,7 @@ int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, i
     return router_fwd_dispatch((const bf16*)x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
 }
 
-int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
+int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
                       void* dx, cudaStream_t st, const void* dXg_rows, const int32_t* pos_rows)
 {
     const Dims& d = L->d;
@@ -434,23 +461,30 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
     const float* dtp = (const float*)(ws + w.d_top_p);
     const int32_t* counts = (const int32_t*)(ws + w.counts);
     const int32_t* pos = pos_rows ? pos_rows : (const int32_t*)(ws + w.pos);
+    const void* dXg = dXg_rows ? dXg_rows : (const void*)(ws + w.dXg);
     float* dl = (float*)(ws + w.dlogits);
     const float* Wr = L->p_data[0];
-
+    // Tensor-core path: BF16 mode with BF16 tokens (x, dx are TMA operands); gWr rows need 16-byte pieces.
+    const bool tc = d.mode == MGPT_MOE_BF16 && d.gemm_impl == 0 && io == MGPT_MOE_IO_BF16;
+    const bool tc_wgrad = tc && L->has_grad && E % 4 == 0;
+    const int E8 = (E + 7) / 8 * 8;
     {
-        const int grid = (N + 7) / 8;
-        if (E <= 32) router_dlogits_kernel<1><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl);
-        else if (E <= 64) router_dlogits_kernel<2><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl);
-        else router_dlogits_kernel<4><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl);
+        const int grid = min((N + 7) / 8, 1184);
+        bf16* dl16 = tc ? (bf16*)(ws + w.dl16) : nullptr;
+        float* gbr = tc_wgrad ? L->p_grad[1] : nullptr;
+        if (E <= 32) router_dlogits_kernel<1><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl, dl16, E8, gbr);
+        else if (E <= 64) router_dlogits_kernel<2><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl, dl16, E8, gbr);
+        else router_dlogits_kernel<4><<<grid, 256, 0, st>>>(probs, top_idx, dtp, counts, N, E, k, d.alpha, dl, dl16, E8, gbr);
         MGPT_LAUNCHED("router_dlogits_kernel");
     }
-    {
+    if (tc) {
+        MGPT_TRY(tc_router_dx(L, w, ws, dXg, pos, dx, st));
+    } else {
         int epad = 8;
         while (epad < E) epad <<= 1;
         const int chunk = DX_WS_FLOATS / epad;                 // channels per CTA (multiple of 8)
         dim3 grid((N + DX_TOK - 1) / DX_TOK, (C + chunk - 1) / chunk);
         const size_t sm = (size_t)(DX_WS_FLOATS + 4 * MAX_EXPERTS + DX_TOK * E) * sizeof(float);
-        const void* dXg = dXg_rows ? dXg_rows : (const void*)(ws + w.dXg);
         static bool attr_done = false;
         if (!attr_done) {
             MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
@@ -467,7 +501,9 @@ int launch_router_bwd(const mgpt_moe_layer* L, const Workspace& w, char* ws, con
         }
         MGPT_LAUNCHED("router_dx_kernel");
     }
-    if (L->has_grad) {
+    if (tc_wgrad) {
+        MGPT_TRY(tc_router_wgrad(L, w, ws, x, st));
+    } else if (L->has_grad) {
         const int E4 = (E + 3) / 4, ch_per_cta = (256 / E4) * 4;
         const int cblocks = (C + ch_per_cta - 1) / ch_per_cta;
         float* part = (float*)(ws + w.rw_part);

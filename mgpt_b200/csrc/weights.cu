@@ -39,12 +39,31 @@ shadow_kernel(const void* const* __restrict__ src_ptrs, int rows, int cols,
     }
 }
 
+// Wr [C,E] fp32 -> [C,E8] bf16, zero in the padding columns
+__global__ void __launch_bounds__(256)
+router_shadow_kernel(const float* __restrict__ Wr, int C, int E, int E8, bf16* __restrict__ out)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= C * E8) return;
+    const int c = i / E8, e = i % E8;
+    out[i] = __float2bfloat16(e < E ? Wr[(size_t)c * E + e] : 0.0f);
+}
+
 }  // namespace
 
 int launch_sync_weights(mgpt_moe_layer* L, cudaStream_t st)
 {
     const Dims& d = L->d;
     if (d.mode != MGPT_MOE_BF16) return 0;
+    if (L->router_bound) {
+        const int E8 = (d.E + 7) / 8 * 8;
+        router_shadow_kernel<<<(d.C * E8 + 255) / 256, 256, 0, st>>>(L->p_data[0], d.C, d.E, E8, L->sWr);
+        MGPT_LAUNCHED("router_shadow_kernel");
+    }
+    if (!L->experts_bound) {
+        L->shadows_fresh = true;
+        return 0;
+    }
     dim3 gCH((d.H + 31) / 32, (d.C + 31) / 32, d.E), gHC((d.C + 31) / 32, (d.H + 31) / 32, d.E);
     shadow_kernel<<<gCH, 256, 0, st>>>(L->master.Wg, d.C, d.H, L->sWg, L->sWgT);
     MGPT_LAUNCHED("shadow_kernel<Wg>");

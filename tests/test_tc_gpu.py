@@ -44,16 +44,18 @@ def test_tc_matches_oracle_small(name):
     (700, 192, 200, 5, 2, False),      # ragged k (200 = 3*64+8) and column tails
     (3000, 128, 96, 16, 4, True),      # skewed: empty and one-row experts next to large ones
 ])
-def test_tc_against_simt_and_oracle(shape):
+@pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
+def test_tc_against_simt_and_oracle(shape, io):
     n, C, H, E, k, skew = shape
     w = synth.Workload("tc", n, C, H, E, k, "bf16", skew=skew)
     x, params, dy = synth.make_inputs(w, seed=11, bias_std=0.02)
     if skew:
         params[0] = synth.bf16_round(params[0] * np.float32(10.0))
     ref = oracle.run(dims_of(w), x, params, dy, threads=16)
-    tc = run_layer(w, x, params, dy, mode="bf16")
+    # BF16 tokens also take the tensor-core router backward (dx and gWr); FP32 tokens the CUDA-core one
+    tc = run_layer(w, x, params, dy, mode="bf16", io=io)
     assert tc["status"] == 0
-    simt = run_layer(w, x, params, dy, mode="bf16", gemm_impl=1)
+    simt = run_layer(w, x, params, dy, mode="bf16", gemm_impl=1, io=io)
     assert_routing_exact(tc, ref)
     a, b = _buffers(tc, w), _buffers(simt, w)
     for name in ACT:
