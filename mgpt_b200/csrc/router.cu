@@ -27,7 +27,10 @@ __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 // EL lanes share one token (lane % EL owns experts el, el+32, ...: EPL of them, EPL > 1 only
 // with EL = 32); a warp therefore works on 32/EL tokens at once and on TPW such groups in
 // sequence, which gives every lane TPW*EPL independent accumulation chains.
-template <typename TIn, int EL, int EPL, int TPW>
+// FAST: C is a multiple of 32 and E fills the staged columns exactly, so both tiles are copied
+// with 16-byte loads into registers one chunk ahead of the arithmetic (double-buffered tiles,
+// one barrier per chunk); otherwise a plain staged loop handles ragged shapes.
+template <typename TIn, int EL, int EPL, int TPW, bool FAST>
 __global__ void __launch_bounds__(R_WARPS * 32)
 router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ br,
                   int N, int C, int E, int k,
@@ -38,8 +41,10 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
     constexpr int TOK_W = TPW * SUB;                // tokens per warp
     constexpr int TOK = R_WARPS * TOK_W;            // tokens per CTA
     constexpr int WCOLS = EPL * EL;                 // staged expert columns
-    __shared__ __align__(16) float xs[TOK][R_XPAD];
-    __shared__ float wsm[R_CK][WCOLS];
+    constexpr int NBUF = FAST ? 2 : 1;
+    constexpr int THREADS = R_WARPS * 32;
+    __shared__ __align__(16) float xs[NBUF][TOK][R_XPAD];
+    __shared__ __align__(16) float wsm[NBUF][R_CK][WCOLS];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = lane / EL, el = lane % EL;
@@ -51,30 +56,19 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 #pragma unroll
         for (int i = 0; i < EPL; ++i) acc[t][i] = 0.0f;
 
-    for (int c0 = 0; c0 < C; c0 += R_CK) {
-        // stage x[tok0.., c0..c0+31] and Wr[c0..c0+31, :] (zero padded: adding 0*w is exact)
-        for (int i = tid; i < TOK * R_CK; i += R_WARPS * 32) {
-            const int t = i / R_CK, j = i % R_CK;
-            const int tok = tok0 + t, c = c0 + j;
-            xs[t][j] = (tok < N && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
-        }
-        for (int i = tid; i < R_CK * WCOLS; i += R_WARPS * 32) {
-            const int j = i / WCOLS, e = i % WCOLS;
-            const int c = c0 + j;
-            wsm[j][e] = (c < C && e < E) ? Wr[(size_t)c * E + e] : 0.0f;
-        }
-        __syncthreads();
+    // sequential over the 32 staged channels: acc = fadd(acc, fmul(x, w)), the reference's order
+    auto compute = [&](int buf) {
 #pragma unroll 2
         for (int j = 0; j < R_CK; j += 4) {
             float4 xv[TPW];
 #pragma unroll
             for (int t = 0; t < TPW; ++t)
-                xv[t] = *reinterpret_cast<const float4*>(&xs[warp * TOK_W + t * SUB + sub][j]);
+                xv[t] = *reinterpret_cast<const float4*>(&xs[buf][warp * TOK_W + t * SUB + sub][j]);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
                 float w[EPL];
 #pragma unroll
-                for (int i = 0; i < EPL; ++i) w[i] = wsm[j + jj][el + 32 * i];
+                for (int i = 0; i < EPL; ++i) w[i] = wsm[buf][j + jj][el + 32 * i];
 #pragma unroll
                 for (int t = 0; t < TPW; ++t) {
                     const float xe = jj == 0 ? xv[t].x : jj == 1 ? xv[t].y : jj == 2 ? xv[t].z : xv[t].w;
@@ -83,7 +77,86 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
                 }
             }
         }
+    };
+
+    if constexpr (FAST) {
+        constexpr int XV = 16 / sizeof(TIn);            // elements per 16-byte piece
+        constexpr int XPT = R_CK / XV;                  // pieces per token per chunk
+        constexpr int X_VECS = TOK * XPT, X_PER = (X_VECS + THREADS - 1) / THREADS;
+        constexpr int W_VECS = R_CK * WCOLS / 4, W_PER = (W_VECS + THREADS - 1) / THREADS;
+        uint4 xr[X_PER];
+        float4 wr[W_PER];
+        auto gload = [&](int c0) {
+#pragma unroll
+            for (int u = 0; u < X_PER; ++u) {
+                const int v = tid + u * THREADS;
+                xr[u] = make_uint4(0, 0, 0, 0);
+                if (v < X_VECS) {
+                    const int tok = tok0 + v / XPT;
+                    if (tok < N) xr[u] = *reinterpret_cast<const uint4*>(x + (size_t)tok * C + c0 + (v % XPT) * XV);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < W_PER; ++u) {
+                const int v = tid + u * THREADS;
+                if (v < W_VECS) wr[u] = *reinterpret_cast<const float4*>(Wr + (size_t)c0 * E + v * 4);
+            }
+        };
+        auto sstore = [&](int buf) {
+#pragma unroll
+            for (int u = 0; u < X_PER; ++u) {
+                const int v = tid + u * THREADS;
+                if (v < X_VECS) {
+                    float* dst = &xs[buf][v / XPT][(v % XPT) * XV];
+                    if constexpr (sizeof(TIn) == 2) {
+                        const uint32_t w4[4] = {xr[u].x, xr[u].y, xr[u].z, xr[u].w};
+                        *reinterpret_cast<float4*>(dst) = make_float4(
+                            __uint_as_float(w4[0] << 16), __uint_as_float(w4[0] & 0xffff0000u),
+                            __uint_as_float(w4[1] << 16), __uint_as_float(w4[1] & 0xffff0000u));
+                        *reinterpret_cast<float4*>(dst + 4) = make_float4(
+                            __uint_as_float(w4[2] << 16), __uint_as_float(w4[2] & 0xffff0000u),
+                            __uint_as_float(w4[3] << 16), __uint_as_float(w4[3] & 0xffff0000u));
+                    } else {
+                        *reinterpret_cast<uint4*>(dst) = xr[u];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < W_PER; ++u) {
+                const int v = tid + u * THREADS;
+                if (v < W_VECS) *reinterpret_cast<float4*>(&wsm[buf][0][0] + v * 4) = wr[u];
+            }
+        };
+        const int nchunks = C / R_CK;
+        gload(0);
+        sstore(0);
         __syncthreads();
+        for (int ci = 0; ci < nchunks; ++ci) {
+            const bool more = ci + 1 < nchunks;
+            if (more) gload((ci + 1) * R_CK);          // next chunk's loads fly during this chunk's arithmetic
+            compute(ci & 1);
+            if (more) sstore((ci + 1) & 1);
+            __syncthreads();
+        }
+    } else {
+        for (int c0 = 0; c0 < C; c0 += R_CK) {
+            // stage x[tok0.., c0..c0+31] and Wr[c0..c0+31, :] (zero padded: adding 0*w is exact)
+#pragma unroll 4
+            for (int i = tid; i < TOK * R_CK; i += THREADS) {
+                const int t = i / R_CK, j = i % R_CK;
+                const int tok = tok0 + t, c = c0 + j;
+                xs[0][t][j] = (tok < N && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
+            }
+#pragma unroll 4
+            for (int i = tid; i < R_CK * WCOLS; i += THREADS) {
+                const int j = i / WCOLS, e = i % WCOLS;
+                const int c = c0 + j;
+                wsm[0][j][e] = (c < C && e < E) ? Wr[(size_t)c * E + e] : 0.0f;
+            }
+            __syncthreads();
+            compute(0);
+            __syncthreads();
+        }
     }
 
     float bias[EPL];
@@ -422,8 +495,12 @@ int router_fwd_launch(const TIn* x, const float* Wr, const float* br, int N, int
                       float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
 {
     constexpr int TOK = R_WARPS * TPW * (32 / EL);
-    router_fwd_kernel<TIn, EL, EPL, TPW><<<(N + TOK - 1) / TOK, R_WARPS * 32, 0, st>>>(
-        x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
+    const int grid = (N + TOK - 1) / TOK;
+    const bool fast = C % R_CK == 0 && E == EPL * EL && ((uintptr_t)x & 15) == 0 && ((uintptr_t)Wr & 15) == 0;
+    if (fast)
+        router_fwd_kernel<TIn, EL, EPL, TPW, true><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
+    else
+        router_fwd_kernel<TIn, EL, EPL, TPW, false><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
     MGPT_LAUNCHED("router_fwd_kernel");
     return 0;
 }
