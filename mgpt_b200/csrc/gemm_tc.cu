@@ -116,7 +116,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// 32 lanes x 32 consecutive 32-bit columns: thread = TMEM lane (row), v[j] = column j
+// 32 lanes x 32 consecutive 32-bit columns: thread = TMEM lane (row), v[j] = column j.
+// Asynchronous: pair with tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
 {
     uint32_t r[32];
@@ -129,10 +130,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The registers written by tmem_ld32 may be read only after this (several loads can be in flight).
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version bits.
 //   K-major  operand: rows of 64 bf16 (128 B), 8-row groups SBO apart (LBO unused)
@@ -155,7 +157,24 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn_major, 
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+// v[j] += bias[n + j] for 32 consecutive columns; 16-byte loads when the whole piece is inside the row
+__device__ __forceinline__ void add_bias32(float (&v)[32], const float* __restrict__ bias, int n, int n_out)
+{
+    if (n + 32 <= n_out) {
+        const float4* b4 = reinterpret_cast<const float4*>(bias + n);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 b = __ldg(b4 + q);
+            v[4 * q] += b.x; v[4 * q + 1] += b.y; v[4 * q + 2] += b.z; v[4 * q + 3] += b.w;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (n + j < n_out) v[j] += bias[n + j];
+    }
+}
 
 __device__ __forceinline__ void load_bf16x32(const bf16* src, float (&v)[32], int valid)
 {
@@ -247,6 +266,9 @@ __device__ __forceinline__ void release_acc(uint32_t bar, int lane)
 // 128-byte swizzle a TMA store with SWIZZLE_128B expects (16-byte chunk j of row r at j ^ (r & 7)).
 __device__ __forceinline__ void stage_row_bf16(uint8_t* stage, int lane, const uint32_t (&packed)[32])
 {
+    // the previous TMA store out of this tile must have finished reading it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
     const uint32_t row = smem_u32(stage) + lane * 128;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -263,9 +285,7 @@ __device__ __forceinline__ void flush_stage(uint8_t* stage, const CUtensorMap* m
     if (lane == 0) {
         tma_store_2d(map, x, y, smem_u32(stage));
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging tile may be rewritten
     }
-    __syncwarp();
 }
 __device__ __forceinline__ void pack64(const float (&a)[32], const float (&b)[32], uint32_t (&out)[32])
 {
@@ -402,25 +422,21 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 uint32_t gp[32], up[32];
                 tmem_ld32(t_lane + h * 64, a);
                 tmem_ld32(t_lane + h * 64 + 32, b);
+                tmem_ld_wait();
                 if (live) {
                     const float* bg = p.bias0[e];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        a[j] += (n + j < p.n_out) ? bg[n + j] : 0.0f;
-                        b[j] += (n + 32 + j < p.n_out) ? bg[n + 32 + j] : 0.0f;
-                    }
+                    add_bias32(a, bg, n, p.n_out);
+                    add_bias32(b, bg, n + 32, p.n_out);
                 }
                 pack64(a, b, gp);
                 tmem_ld32(t_lane + BN / 2 + h * 64, a);
                 tmem_ld32(t_lane + BN / 2 + h * 64 + 32, b);
+                tmem_ld_wait();
                 release_acc(pipe.acc_empty(buf), lane);
                 if (live) {
                     const float* bu = p.bias1[e];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        a[j] += (n + j < p.n_out) ? bu[n + j] : 0.0f;
-                        b[j] += (n + 32 + j < p.n_out) ? bu[n + 32 + j] : 0.0f;
-                    }
+                    add_bias32(a, bu, n, p.n_out);
+                    add_bias32(b, bu, n + 32, p.n_out);
                     pack64(a, b, up);
                     stage_row_bf16(stage, lane, gp);
                     flush_stage(stage, &tmD0, n, row_w, lane);
@@ -445,16 +461,14 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     float v0[32], v1[32];
                     tmem_ld32(t_lane + h * 128 + cc * 64, v0);
                     tmem_ld32(t_lane + h * 128 + cc * 64 + 32, v1);
+                    tmem_ld_wait();
                     if (cc == 1) release_acc(pipe.acc_empty(buf), lane);
                     if (n >= p.n_out) continue;                      // warp-uniform
                     uint32_t pk[32];
                     if (MODE == MODE_DOWN) {
                         const float* bias = p.bias0[e];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            v0[j] += (n + j < p.n_out) ? bias[n + j] : 0.0f;
-                            v1[j] += (n + 32 + j < p.n_out) ? bias[n + 32 + j] : 0.0f;
-                        }
+                        add_bias32(v0, bias, n, p.n_out);
+                        add_bias32(v1, bias, n + 32, p.n_out);
                         pack64(v0, v1, pk);
                         stage_row_bf16(stage, lane, pk);
                         flush_stage(stage, &tmD0, n, row_w, lane);
@@ -644,6 +658,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             float v[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + c * 32, v[c]);
+            tmem_ld_wait();
             release_acc(pipe.acc_empty(buf), lane);
             float* g = p.single_grad ? p.single_grad : p.grad[e];
 #pragma unroll
