@@ -35,12 +35,12 @@ constexpr uint32_t A_BYTES = BM * BK * 2;            // 16 KiB
 constexpr uint32_t B_BYTES = BN * BK * 2;            // 32 KiB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB
 constexpr uint32_t HALF_B = B_BYTES / 2;
-constexpr int EPI_WARPS = 8;
-constexpr uint32_t STAGING_BYTES = 4096;             // per epilogue warp: 32 rows x 128 B
+constexpr int EPI_WARPS = 16;                        // four per TMEM lane quarter
+constexpr uint32_t STAGING_BYTES = 2048;             // per epilogue warp: 32 rows x 64 B
 constexpr uint32_t TMEM_COLS = 2 * BN;               // two accumulators
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-9 epilogue
+constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-17 epilogue
 
 enum { ERR_FULL_WAIT = 2, ERR_EMPTY_WAIT = 4, ERR_ACC_WAIT = 8 };
 
@@ -262,17 +262,18 @@ __device__ __forceinline__ void release_acc(uint32_t bar, int lane)
     if (lane == 0) mbar_arrive(bar);
 }
 
-// Writes this thread's row of a [32 rows x 64 bf16] tile into the warp's staging tile in the
-// 128-byte swizzle a TMA store with SWIZZLE_128B expects (16-byte chunk j of row r at j ^ (r & 7)).
-__device__ __forceinline__ void stage_row_bf16(uint8_t* stage, int lane, const uint32_t (&packed)[32])
+// Writes this thread's row of a [32 rows x 32 bf16] tile into the warp's staging tile in the
+// 64-byte swizzle a TMA store with SWIZZLE_64B expects (16-byte chunk j of row r at j ^ ((r >> 1) & 3)).
+__device__ __forceinline__ void stage_row_bf16(uint8_t* stage, int lane, const uint32_t (&packed)[16])
 {
     // the previous TMA store out of this tile must have finished reading it
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
-    const uint32_t row = smem_u32(stage) + lane * 128;
+    const uint32_t row = smem_u32(stage) + lane * 64;
+    const uint32_t sw = ((uint32_t)lane >> 1) & 3u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t a = row + (((uint32_t)j ^ ((uint32_t)lane & 7u)) << 4);
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t a = row + (((uint32_t)j ^ sw) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(packed[4 * j]), "r"(packed[4 * j + 1]),
                      "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3]) : "memory");
     }
@@ -287,14 +288,12 @@ __device__ __forceinline__ void flush_stage(uint8_t* stage, const CUtensorMap* m
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
 }
-__device__ __forceinline__ void pack64(const float (&a)[32], const float (&b)[32], uint32_t (&out)[32])
+__device__ __forceinline__ void pack32(const float (&a)[32], uint32_t (&out)[16])
 {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
         out[i] = *reinterpret_cast<uint32_t*>(&h);
-        __nv_bfloat162 g = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
-        out[16 + i] = *reinterpret_cast<uint32_t*>(&g);
     }
 }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -402,7 +401,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             }
         }
     } else {
-        // 8 epilogue warps: TMEM lane quarter q = warp % 4 (rows q*32..+31), column half h
+        // 16 epilogue warps: TMEM lane quarter q = warp % 4 (rows q*32..+31), column group h = 0..3
         const int q = warp & 3, h = (warp - 2) >> 2;
         uint8_t* stage = pipe.staging + (warp - 2) * STAGING_BYTES;
         uint32_t t = 0;
@@ -415,38 +414,27 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             tc_fence_after();
             const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
             if (MODE == MODE_GATEUP) {
-                // this warp: hidden units n0 + h*64 .. +63  (gate columns h*64.., up columns 128 + h*64..)
-                const int n = n0 + h * 64;
-                const bool live = n < p.n_out;
+                // this warp: hidden units n0 + h*32 .. +31  (gate columns h*32.., up columns 128 + h*32..)
+                const int n = n0 + h * 32;
                 float a[32], b[32];
-                uint32_t gp[32], up[32];
-                tmem_ld32(t_lane + h * 64, a);
-                tmem_ld32(t_lane + h * 64 + 32, b);
-                tmem_ld_wait();
-                if (live) {
-                    const float* bg = p.bias0[e];
-                    add_bias32(a, bg, n, p.n_out);
-                    add_bias32(b, bg, n + 32, p.n_out);
-                }
-                pack64(a, b, gp);
-                tmem_ld32(t_lane + BN / 2 + h * 64, a);
-                tmem_ld32(t_lane + BN / 2 + h * 64 + 32, b);
+                tmem_ld32(t_lane + h * 32, a);
+                tmem_ld32(t_lane + BN / 2 + h * 32, b);
                 tmem_ld_wait();
                 release_acc(pipe.acc_empty(buf), lane);
-                if (live) {
-                    const float* bu = p.bias1[e];
-                    add_bias32(a, bu, n, p.n_out);
-                    add_bias32(b, bu, n + 32, p.n_out);
-                    pack64(a, b, up);
+                if (n < p.n_out) {
+                    uint32_t gp[16], up[16];
+                    add_bias32(a, p.bias0[e], n, p.n_out);
+                    add_bias32(b, p.bias1[e], n, p.n_out);
+                    pack32(a, gp);
+                    pack32(b, up);
                     stage_row_bf16(stage, lane, gp);
                     flush_stage(stage, &tmD0, n, row_w, lane);
                     stage_row_bf16(stage, lane, up);
                     flush_stage(stage, &tmD1, n, row_w, lane);
                     // Hh from the rounded G and U (backward reads the stored values)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g0 = bf_lo(gp[i]), g1 = bf_hi(gp[i]);
-                        const float h0 = silu(g0) * bf_lo(up[i]), h1 = silu(g1) * bf_hi(up[i]);
+                    for (int i = 0; i < 16; ++i) {
+                        const float h0 = silu(bf_lo(gp[i])) * bf_lo(up[i]), h1 = silu(bf_hi(gp[i])) * bf_hi(up[i]);
                         __nv_bfloat162 hh = __floats2bfloat162_rn(h0, h1);
                         gp[i] = *reinterpret_cast<uint32_t*>(&hh);
                     }
@@ -454,59 +442,39 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     flush_stage(stage, &tmD2, n, row_w, lane);
                 }
             } else {
-                // this warp: columns n0 + h*128 .. +127, two chunks of 64
+                // this warp: columns n0 + h*64 .. +63, two units of 32
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int n = n0 + h * 128 + cc * 64;
-                    float v0[32], v1[32];
-                    tmem_ld32(t_lane + h * 128 + cc * 64, v0);
-                    tmem_ld32(t_lane + h * 128 + cc * 64 + 32, v1);
+                for (int un = 0; un < 2; ++un) {
+                    const int n = n0 + h * 64 + un * 32;
+                    float v[32];
+                    tmem_ld32(t_lane + h * 64 + un * 32, v);
                     tmem_ld_wait();
-                    if (cc == 1) release_acc(pipe.acc_empty(buf), lane);
+                    if (un == 1) release_acc(pipe.acc_empty(buf), lane);
                     if (n >= p.n_out) continue;                      // warp-uniform
-                    uint32_t pk[32];
+                    uint32_t pk[16];
                     if (MODE == MODE_DOWN) {
-                        const float* bias = p.bias0[e];
-                        add_bias32(v0, bias, n, p.n_out);
-                        add_bias32(v1, bias, n + 32, p.n_out);
-                        pack64(v0, v1, pk);
-                        stage_row_bf16(stage, lane, pk);
-                        flush_stage(stage, &tmD0, n, row_w, lane);
+                        add_bias32(v, p.bias0[e], n, p.n_out);
                     } else if (MODE == MODE_DHH) {
-                        // utils/Tensor.cpp:2020-2027 with dd = dHh; G, U are this thread's row, 128 B each
+                        // utils/Tensor.cpp:2020-2027 with dd = dHh; G, U: this thread's row, 64 B each
                         const size_t o = (size_t)(row_w + lane) * p.n_out + n;
-                        const int valid = min(64, p.n_out - n);
-                        uint32_t pu[32];
+                        const int valid = min(32, p.n_out - n);
+                        float g[32], u[32];
+                        uint32_t pu[16];
+                        load_bf16x32(p.G + o, g, valid);
+                        load_bf16x32(p.U + o, u, valid);
 #pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            float (&v)[32] = half == 0 ? v0 : v1;
-                            float g[32], u[32];
-                            load_bf16x32(p.G + o + half * 32, g, valid - half * 32);
-                            load_bf16x32(p.U + o + half * 32, u, valid - half * 32);
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const float sig = __fdividef(1.0f, 1.0f + __expf(-g[j]));
-                                const float dd = v[j];
-                                v[j] = (dd * u[j]) * (sig * (1.0f + g[j] * (1.0f - sig)));   // dG
-                                u[j] = dd * (g[j] * sig);                                     // dU
-                            }
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                __nv_bfloat162 x = __floats2bfloat162_rn(u[2 * i], u[2 * i + 1]);
-                                pu[half * 16 + i] = *reinterpret_cast<uint32_t*>(&x);
-                            }
+                        for (int j = 0; j < 32; ++j) {
+                            const float sig = __fdividef(1.0f, 1.0f + __expf(-g[j]));
+                            const float dd = v[j];
+                            v[j] = (dd * u[j]) * (sig * (1.0f + g[j] * (1.0f - sig)));   // dG
+                            u[j] = dd * (g[j] * sig);                                     // dU
                         }
-                        pack64(v0, v1, pk);
-                        stage_row_bf16(stage, lane, pk);
-                        flush_stage(stage, &tmD0, n, row_w, lane);
+                        pack32(u, pu);
                         stage_row_bf16(stage, lane, pu);
                         flush_stage(stage, &tmD1, n, row_w, lane);
                     } else if (MODE == MODE_DX) {
                         // dx = (sum of the token's expert rows, ascending row order) + dlogits * Wr^T
                         const int tok = row_w + lane;
-                        float s0[32], s1[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) s0[j] = s1[j] = 0.0f;
                         if (tok < p.n_valid_rows) {
                             int ps[MAX_TOPK];
 #pragma unroll
@@ -521,35 +489,21 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                                         ps[b] = ps[b + 1];
                                         ps[b + 1] = tmp;
                                     }
-                            const int valid = min(64, p.n_out - n);
+                            const int valid = min(32, p.n_out - n);
 #pragma unroll
                             for (int j = 0; j < MAX_TOPK; ++j) {
                                 if (j < p.gather_k) {
-                                    const bf16* src = p.gather_src + (size_t)ps[j] * p.n_out + n;
-                                    float g0[32], g1[32];
-                                    load_bf16x32(src, g0, valid);
-                                    load_bf16x32(src + 32, g1, valid - 32);
+                                    float g[32];
+                                    load_bf16x32(p.gather_src + (size_t)ps[j] * p.n_out + n, g, valid);
 #pragma unroll
-                                    for (int i = 0; i < 32; ++i) {
-                                        s0[i] += g0[i];
-                                        s1[i] += g1[i];
-                                    }
+                                    for (int i = 0; i < 32; ++i) v[i] += g[i];
                                 }
                             }
                         }
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            v0[i] += s0[i];
-                            v1[i] += s1[i];
-                        }
-                        pack64(v0, v1, pk);
-                        stage_row_bf16(stage, lane, pk);
-                        flush_stage(stage, &tmD0, n, row_w, lane);
-                    } else {
-                        pack64(v0, v1, pk);
-                        stage_row_bf16(stage, lane, pk);
-                        flush_stage(stage, &tmD0, n, row_w, lane);
                     }
+                    pack32(v, pk);
+                    stage_row_bf16(stage, lane, pk);
+                    flush_stage(stage, &tmD0, n, row_w, lane);
                 }
             }
         }
@@ -644,40 +598,44 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else {
         const int q = warp & 3, h = (warp - 2) >> 2;
-        float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32][32] floats
+        float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32 rows][16 floats]
         uint32_t t = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
             const int e = item / per_expert, r = item % per_expert;
             if ((p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - p.padded_offsets[e]) < BK) continue;
             const uint32_t buf = t & 1u;
             const int m_w = (r / p.n_tiles_n) * BM + q * 32;             // first output row of this warp
-            const int n_w = (r % p.n_tiles_n) * BN + h * 128;            // first output column of this warp
+            const int n_w = (r % p.n_tiles_n) * BN + h * 64;             // first output column of this warp
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
-            const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + h * 128;
-            float v[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + c * 32, v[c]);
+            const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + h * 64;
+            float v[2][32];
+            tmem_ld32(t_lane, v[0]);
+            tmem_ld32(t_lane + 32, v[1]);
             tmem_ld_wait();
             release_acc(pipe.acc_empty(buf), lane);
             float* g = p.single_grad ? p.single_grad : p.grad[e];
+            const uint32_t sw_w = ((uint32_t)lane >> 1) & 3u;            // writer: row = lane
+            const int sub = lane >> 2, piece = lane & 3;                 // reader: 8 rows x 4 pieces per pass
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int n = n_w + c * 32;
+            for (int c = 0; c < 4; ++c) {                                // four groups of 16 columns
+                const int n = n_w + c * 16;
                 if (n >= p.N) break;
-                // transpose through shared memory (16-byte pieces, XOR-swizzled by row) so that one
-                // vector RED instruction covers four full 128-byte row segments
+                // transpose through shared memory (16-byte pieces, XOR-swizzled by row) so that one vector
+                // RED instruction covers eight full 64-byte row segments
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<float4*>(&stage[lane * 32 + ((j ^ (lane & 7)) << 2)]) =
-                        make_float4(v[c][4 * j], v[c][4 * j + 1], v[c][4 * j + 2], v[c][4 * j + 3]);
+                for (int j = 0; j < 4; ++j) {
+                    const int s0 = (c & 1) * 16 + 4 * j;
+                    *reinterpret_cast<float4*>(&stage[lane * 16 + (((uint32_t)j ^ sw_w) << 2)]) =
+                        make_float4(v[c >> 1][s0], v[c >> 1][s0 + 1], v[c >> 1][s0 + 2], v[c >> 1][s0 + 3]);
+                }
                 __syncwarp();
-                const int sub = lane >> 3, piece = lane & 7;
                 const int col = n + piece * 4;
 #pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    const int r = rr * 4 + sub, m = m_w + r;
-                    const float4 x = *reinterpret_cast<const float4*>(&stage[r * 32 + ((piece ^ (r & 7)) << 2)]);
+                for (int rr = 0; rr < 4; ++rr) {
+                    const int row = rr * 8 + sub, m = m_w + row;
+                    const float4 x = *reinterpret_cast<const float4*>(
+                        &stage[row * 16 + (((uint32_t)piece ^ (((uint32_t)row >> 1) & 3u)) << 2)]);
                     if (m < p.M && col < p.N) red_add_v4(g + (size_t)m * p.N + col, x);
                 }
                 __syncwarp();
@@ -706,17 +664,20 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-// 2-D row-major bf16 tensor [rows, cols]; box = {64 columns (128 B), box_rows}; 128-byte swizzle; OOB reads 0.
+// 2-D row-major bf16 tensor [rows, cols].  Loads: box = {64 columns (128 B), box_rows}, 128-byte swizzle,
+// OOB reads 0.  Stores (box_rows == 32): box = {32 columns (64 B), 32 rows}, 64-byte swizzle.
 int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows)
 {
+    const bool store = box_rows == 32;
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(MGPT_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * sizeof(bf16)};
-    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t box[2] = {store ? 32u : 64u, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, store ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(MGPT_MOE_ECUDA, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
     return 0;
@@ -731,7 +692,7 @@ struct TcState {
     CUtensorMap Xg, Hh, dYg, dG, dU, WgT, WuT, WdT, Wg, Wu, Wd;
     // reduction-over-rows operand loads (box 64 x 64 rows)
     CUtensorMap Xg_t, Hh_t, dYg_t, dG_t, dU_t;
-    // epilogue stores (box 64 x 32 rows)
+    // epilogue stores (box 32 x 32 rows, 64-byte swizzle)
     CUtensorMap G_s, U_s, Hh_s, Yg_s, dG_s, dU_s, dXg_s;
 };
 
