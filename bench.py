@@ -352,7 +352,7 @@ def run_ours(args, w):
         elif name in byts and world == 1:
             ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
         stages[name] = ent
-    launches_per = {"gateup_gemm": 1, "down_gemm": 1, "dhh_gemm": 1, "dxg_gemm": 1, "wgrad_gemm": 3}
+    launches_per = {"gateup_gemm": 1, "down_gemm": 1, "dhh_gemm": 1, "dxg_gemm": 1, "wgrad_gemm": 1}
     gemm = {k: v for k, v in stages.items() if k in flops}
     roofline = None
     if gemm:

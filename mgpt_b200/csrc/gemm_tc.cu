@@ -410,6 +410,18 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
             const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
             const int row_w = row_tile * BM + q * 32;           // first row of this warp
+            if (MODE == MODE_DHH) {
+                // G and U of this item come from HBM: start pulling this thread's two 128-byte rows into L2
+                // while the tensor core is still working on the item
+                const int n = n0 + h * 64;
+                if (n < p.n_out) {
+                    const size_t o = (size_t)(row_w + lane) * p.n_out + n;
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.G + o));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.G + o + 32));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.U + o));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.U + o + 32));
+                }
+            }
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
             const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
@@ -513,24 +525,53 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 }
 
 // ---- weight gradients: grad[e][M,N] += A_e^T * B_e over the expert's rows ---------
+// One weight-gradient problem: grad[e][M,N] += A_e^T * B_e over the rows of "expert" e.
+struct WgradProb {
+    float* const* grad;     // per-expert output [M,N]
+    float* single_grad;     // or one output all chunks add into (router gradient)
+    int M, N, n_tiles_m, n_tiles_n;
+    int n_groups;           // experts, or uniform token chunks
+    int uniform_rows;       // > 0: group g covers rows [g*uniform_rows, +uniform_rows) instead of an expert's rows
+    int item_begin;         // first item index of this problem
+};
 struct WgradP {
     const int32_t* padded_offsets;
     int32_t* status;
-    float* const* grad;
-    int M, N, n_tiles_m, n_tiles_n, E;
-    // router gradient: the "experts" are uniform chunks of uniform_rows tokens that all add into single_grad
-    int uniform_rows;
-    float* single_grad;
+    WgradProb prob[3];
+    int n_probs, total_items;
 };
+struct WgradItem {
+    int pr, e, m0, n0, r0, nkb;
+};
+__device__ __forceinline__ WgradItem wgrad_item(const WgradP& p, int item)
+{
+    WgradItem w;
+    w.pr = (p.n_probs > 2 && item >= p.prob[2].item_begin) ? 2 : (p.n_probs > 1 && item >= p.prob[1].item_begin) ? 1 : 0;
+    const WgradProb& q = p.prob[w.pr];
+    const int local = item - q.item_begin, per = q.n_tiles_m * q.n_tiles_n;
+    w.e = local / per;
+    const int r = local % per;
+    w.m0 = (r / q.n_tiles_n) * BM;
+    w.n0 = (r % q.n_tiles_n) * BN;
+    if (q.uniform_rows) {
+        w.r0 = w.e * q.uniform_rows;
+        w.nkb = q.uniform_rows / BK;
+    } else {
+        w.r0 = p.padded_offsets[w.e];
+        w.nkb = (p.padded_offsets[w.e + 1] - w.r0) / BK;
+    }
+    return w;
+}
 
-// Persistent over items (expert, m tile, n tile); experts without rows are skipped.
+// Persistent over items (problem, expert, m tile, n tile); experts without rows are skipped.
 __global__ void __launch_bounds__(TC_THREADS, 1)
-tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const WgradP p)
+tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const WgradP p)
 {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_expert = p.n_tiles_m * p.n_tiles_n;
-    const int total_items = p.E * per_expert;
+    const int total_items = p.total_items;
     if ((int)blockIdx.x >= total_items) return;
 
     const Pipe pipe = carve(smem_raw);
@@ -542,11 +583,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t it = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-                const int e = item / per_expert, r = item % per_expert;
-                const int r0 = p.uniform_rows ? e * p.uniform_rows : p.padded_offsets[e];
-                const int nkb = (p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - r0) / BK;
-                const int m0 = (r / p.n_tiles_n) * BM, n0 = (r % p.n_tiles_n) * BN;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const WgradItem w = wgrad_item(p, item);
+                const CUtensorMap* mA = w.pr == 0 ? &tmA0 : w.pr == 1 ? &tmA1 : &tmA2;
+                const CUtensorMap* mB = w.pr == 0 ? &tmB0 : w.pr == 1 ? &tmB1 : &tmB2;
+                for (int kb = 0; kb < w.nkb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
                         ok = false;
@@ -554,11 +594,11 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(pipe.full(s), STAGE_BYTES);
-                    const int row = r0 + kb * BK;
+                    const int row = w.r0 + kb * BK;
 #pragma unroll
-                    for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, &tmA, m0 + 64 * i, row, pipe.full(s));
+                    for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
 #pragma unroll
-                    for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, &tmB, n0 + 64 * i, row, pipe.full(s));
+                    for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
                 }
             }
         }
@@ -568,14 +608,13 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-                const int e = item / per_expert;
-                const int nkb = (p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - p.padded_offsets[e]) / BK;
-                if (nkb <= 0) continue;
+                const WgradItem w = wgrad_item(p, item);
+                if (w.nkb <= 0) continue;
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                for (int kb = 0; kb < w.nkb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(pipe.full(s), (it / STAGES) & 1, p.status, ERR_FULL_WAIT)) {
                         ok = false;
@@ -601,11 +640,12 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32 rows][16 floats]
         uint32_t t = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-            const int e = item / per_expert, r = item % per_expert;
-            if ((p.uniform_rows ? p.uniform_rows : p.padded_offsets[e + 1] - p.padded_offsets[e]) < BK) continue;
+            const WgradItem w = wgrad_item(p, item);
+            if (w.nkb <= 0) continue;
+            const WgradProb& pb = p.prob[w.pr];
             const uint32_t buf = t & 1u;
-            const int m_w = (r / p.n_tiles_n) * BM + q * 32;             // first output row of this warp
-            const int n_w = (r % p.n_tiles_n) * BN + h * 64;             // first output column of this warp
+            const int m_w = w.m0 + q * 32;             // first output row of this warp
+            const int n_w = w.n0 + h * 64;             // first output column of this warp
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
             const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + h * 64;
@@ -614,13 +654,14 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld32(t_lane + 32, v[1]);
             tmem_ld_wait();
             release_acc(pipe.acc_empty(buf), lane);
-            float* g = p.single_grad ? p.single_grad : p.grad[e];
+            float* g = pb.single_grad ? pb.single_grad : pb.grad[w.e];
+            const int M = pb.M, N = pb.N;
             const uint32_t sw_w = ((uint32_t)lane >> 1) & 3u;            // writer: row = lane
             const int sub = lane >> 2, piece = lane & 3;                 // reader: 8 rows x 4 pieces per pass
 #pragma unroll
             for (int c = 0; c < 4; ++c) {                                // four groups of 16 columns
                 const int n = n_w + c * 16;
-                if (n >= p.N) break;
+                if (n >= N) break;
                 // transpose through shared memory (16-byte pieces, XOR-swizzled by row) so that one vector
                 // RED instruction covers eight full 64-byte row segments
 #pragma unroll
@@ -636,7 +677,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int row = rr * 8 + sub, m = m_w + row;
                     const float4 x = *reinterpret_cast<const float4*>(
                         &stage[row * 16 + (((uint32_t)piece ^ (((uint32_t)row >> 1) & 3u)) << 2)]);
-                    if (m < p.M && col < p.N) red_add_v4(g + (size_t)m * p.N + col, x);
+                    if (m < M && col < N) red_add_v4(g + (size_t)m * N + col, x);
                 }
                 __syncwarp();
             }
@@ -809,25 +850,30 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     L->stage_end(ST_DXG, st);
     if (!L->has_grad) return 0;
 
+    // all three weight gradients in one launch:
+    //   gWg += Xg^T dG, gWu += Xg^T dU   [C,H];   gWd += Hh^T dYg   [H,C]
     WgradP g = {};
     g.padded_offsets = (const int32_t*)(ws + w.padded_offsets);
     g.status = (int32_t*)(ws + w.status);
-    g.E = d.E;
+    g.n_probs = 3;
+    float* const* grads[3] = {L->master.gWg, L->master.gWu, L->master.gWd};
+    int items = 0;
+    for (int i = 0; i < 3; ++i) {
+        WgradProb& q = g.prob[i];
+        q.grad = grads[i];
+        q.M = i < 2 ? d.C : d.H;
+        q.N = i < 2 ? d.H : d.C;
+        q.n_tiles_m = cdiv(q.M, BM);
+        q.n_tiles_n = cdiv(q.N, BN);
+        q.n_groups = d.E;
+        q.item_begin = items;
+        items += d.E * q.n_tiles_m * q.n_tiles_n;
+    }
+    g.total_items = items;
     L->stage_begin(ST_WGRAD, st);
-    // gWg += Xg^T dG, gWu += Xg^T dU   [C,H]
-    g.M = d.C; g.N = d.H; g.n_tiles_m = cdiv(d.C, BM); g.n_tiles_n = cdiv(d.H, BN);
-    const int items_ch = d.E * g.n_tiles_m * g.n_tiles_n;
-    g.grad = L->master.gWg;
-    tc_wgrad_kernel<<<imin(s->sms, items_ch), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, g);
-    MGPT_LAUNCHED("tc_wgrad_kernel<Wg>");
-    g.grad = L->master.gWu;
-    tc_wgrad_kernel<<<imin(s->sms, items_ch), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dU_t, g);
-    MGPT_LAUNCHED("tc_wgrad_kernel<Wu>");
-    // gWd += Hh^T dYg   [H,C]
-    g.M = d.H; g.N = d.C; g.n_tiles_m = cdiv(d.H, BM); g.n_tiles_n = cdiv(d.C, BN);
-    g.grad = L->master.gWd;
-    tc_wgrad_kernel<<<imin(s->sms, d.E * g.n_tiles_m * g.n_tiles_n), TC_THREADS, SMEM_BYTES, st>>>(s->Hh_t, s->dYg_t, g);
-    MGPT_LAUNCHED("tc_wgrad_kernel<Wd>");
+    tc_wgrad_kernel<<<imin(s->sms, items), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, s->Xg_t, s->dU_t, s->Hh_t,
+                                                                       s->dYg_t, g);
+    MGPT_LAUNCHED("tc_wgrad_kernel");
     L->stage_end(ST_WGRAD, st);
     return 0;
 }
@@ -870,13 +916,16 @@ int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void*
     MGPT_TRY(make_map(&mB, ws + w.dl16, (uint64_t)w.n_tokens, (uint64_t)E8, 64));
     WgradP g = {};
     g.status = (int32_t*)(ws + w.status);
-    g.M = d.C; g.N = d.E; g.n_tiles_m = cdiv(d.C, BM); g.n_tiles_n = cdiv(d.E, BN);
-    const int per_chunk = g.n_tiles_m * g.n_tiles_n;
+    g.n_probs = 1;
+    WgradProb& q = g.prob[0];
+    q.M = d.C; q.N = d.E; q.n_tiles_m = cdiv(d.C, BM); q.n_tiles_n = cdiv(d.E, BN);
+    const int per_chunk = q.n_tiles_m * q.n_tiles_n;
     int chunks = imin(64, (2 * s->sms + per_chunk - 1) / per_chunk);
     int rows = cdiv(cdiv(w.n_tokens, chunks), BK) * BK;           // tokens per chunk, whole k-blocks
     chunks = cdiv(w.n_tokens, rows);
-    g.E = chunks; g.uniform_rows = rows; g.single_grad = L->p_grad[0];
-    tc_wgrad_kernel<<<imin(s->sms, chunks * per_chunk), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, g);
+    q.n_groups = chunks; q.uniform_rows = rows; q.single_grad = L->p_grad[0]; q.item_begin = 0;
+    g.total_items = chunks * per_chunk;
+    tc_wgrad_kernel<<<imin(s->sms, g.total_items), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, mA, mB, mA, mB, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wr>");
     return 0;
 }
