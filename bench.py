@@ -25,7 +25,10 @@ if ROOT not in sys.path:
 
 METRIC = "moe_layer_fwd_bwd_tokens_per_sec"
 # DRAM bytes (read + write) per launch from ncu captures, keyed by (workload, stage); see profiles/
-TRAFFIC = {}
+TRAFFIC = {
+    ("c2", "wgrad_gemm"): 415.8e6, ("c2", "gateup_gemm"): 154.8e6, ("c2", "dhh_gemm"): 204.2e6,
+    ("c2", "down_gemm"): 73.9e6, ("c2", "dxg_gemm"): 149.5e6,
+}
 UNIT = "tokens/s"
 
 
