@@ -73,3 +73,14 @@ def test_tc_c2_reduced_tokens():
     got = run_layer(w, x, params, dy, mode="bf16", io=torch.bfloat16)
     assert_routing_exact(got, ref)
     assert_values(got, ref, TOL_BF16, w)
+
+
+@pytest.mark.parametrize("n", [8, 64])
+def test_tc_decode_shapes_forward_only(n):
+    """Config-5 dimensions (C=1024, H=2816, E=32, k=2), one new token per sequence, forward only."""
+    w = synth.WORKLOADS["c5-64"].scaled(n)
+    x, params, dy = synth.make_inputs(w)
+    ref = oracle.run(dims_of(w), x, params, None, threads=32)
+    got = run_layer(w, x, params, None, mode="bf16", io=torch.bfloat16)
+    assert_routing_exact(got, ref)
+    assert rel_l2(got["y"], ref["y"]) <= TOL_BF16
