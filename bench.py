@@ -175,7 +175,6 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
     sampler = ClockSampler(dev.index) if rank == 0 else None           # samples every 100 ms from here on
-    t_sampler = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         flush.zero_()
         step()
@@ -196,17 +195,19 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
             stage_sum[name] = stage_sum.get(name, 0.0) + ms
     launches = launch_count()
     barrier()
-    # a short run can end before nvidia-smi has printed a sample: keep the same load up (untimed) until it has
-    while world == 1 and sampler and time.perf_counter() - t_sampler < 0.7:
-        step()
-        torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler else None
     set_profiling(False)
     total_ms = sum(s.elapsed_time(e) for s, e in ev)
     t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / args.steps
+    # a short run can end before nvidia-smi has printed a sample: keep the same load up (untimed) for
+    # about 0.7 s in total; the count is derived from the all-reduced step time, so every rank runs the same
+    extra = min(2000, max(0, int(700.0 / max(ms_per_step, 1e-3)) - args.steps - max(args.warmup, 3)))
+    for _ in range(extra):
+        step()
+    barrier()
+    clocks = sampler.stop() if sampler else None
 
     for _ in range(2):
         step_host()
