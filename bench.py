@@ -285,6 +285,7 @@ def run_ours(args, w):
     peaks = load_peaks()
     N, C = w.n_tokens, w.C
     reference_1gpu = None
+    ep_phases = None
 
     if world == 1:
         ms_per_step, stage_sum, launches, clocks, e2e = single_gpu_pass(args, w, rank, dev)
@@ -341,6 +342,13 @@ def run_ours(args, w):
         ms_per_step, stage_sum, launches, clocks, e2e = measure(
             args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms, layer.stages.set_profiling, barrier, N,
             x_host.numel() * x_host.element_size())
+        # one more step with CUDA events around every phase (exchange vs compute), outside the timed region
+        layer.phase_events = {}
+        step()
+        torch.cuda.synchronize()
+        ep_phases = {k: round(v, 3) for k, v in layer.phase_ms().items()}
+        layer.phase_events = None
+        dist.barrier()
         parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
                        "NCCL all-to-all for dispatch and combine (4 per step)")
 
@@ -405,6 +413,8 @@ def run_ours(args, w):
     }
     if reference_1gpu:
         line["same_workload_on_one_gpu"] = reference_1gpu
+    if world > 1:
+        line["ep_phases_ms"] = ep_phases
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

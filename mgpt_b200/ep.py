@@ -181,6 +181,21 @@ class ExpertParallelMoE:
         self.stages = stages if stages is not None else CudaStages(
             self.C, self.H, self.E, self.k, self.E_local, mode=mode, device=device, lb_alpha=lb_alpha)
         self._saved = None
+        self.phase_events = None        # set to {} to record CUDA events around every phase of a step
+
+    def _mark(self, name):
+        if self.phase_events is not None and torch.cuda.is_available():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_events.setdefault("order", []).append((name, ev))
+
+    def phase_ms(self):
+        """Milliseconds between consecutive marks of the last recorded step (after a synchronize)."""
+        marks = (self.phase_events or {}).get("order", [])
+        out = {}
+        for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
 
     # parameters: the router replica and this rank's experts, in the reference's order
     def get_parameters(self):
@@ -216,7 +231,11 @@ class ExpertParallelMoE:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         G, El = self.world, self.E_local
+        if self.phase_events is not None:
+            self.phase_events["order"] = []
+        self._mark("start")
         rows, counts = self.stages.route(x)                          # [R,C] compact expert-major, counts[E]
+        self._mark("route")
         counts = counts.view(G, El)
         recv_counts = torch.empty_like(counts)                       # [source rank, local expert]
         if G == 1:
@@ -225,13 +244,18 @@ class ExpertParallelMoE:
             dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)
         both = torch.stack([counts.sum(1), recv_counts.sum(1)]).cpu()   # the one host sync of the step
         send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+        self._mark("counts_exchange_and_host_sync")
         recv_rows = self._all_to_all(rows, send_splits, recv_splits)
+        self._mark("rows_all_to_all")
         expert_ids = torch.arange(El, device=recv_counts.device, dtype=torch.int32).repeat(G)
         expert_of_row = torch.repeat_interleave(expert_ids, recv_counts.reshape(-1).to(torch.int64),
                                                 output_size=int(sum(recv_splits))).to(torch.int32)
         out_rows = self.stages.experts_forward(recv_rows, expert_of_row)
+        self._mark("experts_forward")
         rows_back = self._all_to_all(out_rows, recv_splits, send_splits)
+        self._mark("rows_back_all_to_all")
         y = self.stages.combine(rows_back, x)
+        self._mark("combine")
         self._saved = (x, rows_back, send_splits, recv_splits)
         self.last_recv_counts = recv_counts
         return y
@@ -241,7 +265,13 @@ class ExpertParallelMoE:
             raise RuntimeError("backward before forward")
         x, rows_back, send_splits, recv_splits = self._saved
         d_rows = self.stages.combine_backward(rows_back, dy)
+        self._mark("combine_backward")
         d_recv = self._all_to_all(d_rows, send_splits, recv_splits)
+        self._mark("grad_rows_all_to_all")
         d_in = self.stages.experts_backward(d_recv)
+        self._mark("experts_backward")
         d_back = self._all_to_all(d_in, recv_splits, send_splits)
-        return self.stages.route_backward(x, d_back)
+        self._mark("grad_rows_back_all_to_all")
+        dx = self.stages.route_backward(x, d_back)
+        self._mark("route_backward")
+        return dx
