@@ -174,31 +174,39 @@ int  mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E,
  * Expert side: a layer created with the E_local experts this GPU owns and
  * top_k = 1, bound with all 2+6*E_local pointers of which data[0], data[1]
  * (router) may be NULL.  Rows are [n, C] in the mode's activation type (BF16
- * in BF16 mode, FP32 in FP32 mode).  Workspaces: mgpt_moe_stage_workspace_bytes
- * (routing_side = 1 leaves out the activation buffers).                     */
+ * in BF16 mode, FP32 in FP32 mode) and travel TILE-ALIGNED: expert-major, each
+ * expert's segment padded with zero rows to a multiple of 128 rows, so the
+ * rows of experts e0..e1 are the contiguous range
+ * [padded_offsets[e0], padded_offsets[e1+1]) (workspace view "padded_offsets";
+ * real counts: view "counts").  Workspaces: mgpt_moe_stage_workspace_bytes.  */
 size_t mgpt_moe_stage_workspace_bytes(const mgpt_moe_layer* layer, int n, int routing_side);
 
-/* router + plan + permutation: send_rows[slot,:] = x[map[slot]/k,:], the
- * reference's expert-major compact order (Tensor.cpp:1368-1381), so rows for
- * experts e0..e1 are one contiguous block. Per-expert counts: workspace view
- * "counts" or mgpt_moe_expert_counts. */
+/* router + plan + permutation into send_rows[row_cap, C] (row_cap = rows of the
+ * workspace view "row_src"): the layout above, stable within an expert like the
+ * reference's slot order (Tensor.cpp:1368-1381). */
 int  mgpt_moe_route(mgpt_moe_layer* layer, const void* x, int n_tokens, int io_dtype,
                     void* workspace, size_t workspace_bytes, void* send_rows, mgpt_stream_t stream);
-/* y[tok,:] = sum_j p[tok,j] * rows_back[slot(tok,j),:]   (Tensor.cpp:1398-1406) */
+/* y[tok,:] = sum_j p[tok,j] * rows_back[row(tok,j),:]   (Tensor.cpp:1398-1406); rows_back in the send layout */
 int  mgpt_moe_combine(mgpt_moe_layer* layer, const void* rows_back, void* y, int io_dtype,
                       void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
-/* d_rows[slot,:] = p * dy[tok,:] and d_top_p (Tensor.cpp:1424-1436) */
+/* d_rows[row,:] = p * dy[tok,:] (zero in padding rows) and d_top_p (Tensor.cpp:1424-1436) */
 int  mgpt_moe_combine_backward(mgpt_moe_layer* layer, const void* rows_back, const void* dy, int io_dtype,
                                void* d_rows, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
 /* dx = gather-sum of d_rows_in + router backward; accumulates the router gradients
  * with this GPU's own counts in the load-balance term (MoELayer.cpp:184-218). */
 int  mgpt_moe_route_backward(mgpt_moe_layer* layer, const void* x, const void* d_rows_in, void* dx, int io_dtype,
                              void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
-/* out_rows[i,:] = SwiGLU expert expert_of_row[i] applied to rows[i,:]
- * (MoELayer.cpp:94-118); keeps what backward needs in the workspace. */
-int  mgpt_moe_experts_forward(mgpt_moe_layer* layer, const void* rows, const int32_t* expert_of_row, int n_rows,
-                              void* out_rows, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
-/* d_in_rows = gradient w.r.t. rows; accumulates the expert parameter gradients (MoELayer.cpp:159-181). */
+/* The SwiGLU experts on received rows (MoELayer.cpp:94-118). rows[n_rows, C] is n_src
+ * blocks (one per source rank, in rank order), each holding one padded segment per
+ * local expert; seg_counts[n_src * E_local] (device, source-major) are the REAL row
+ * counts. n_rows = sum of the padded segment lengths. The kernels read rows and write
+ * out_rows (same layout) in place: no copy, no regrouping. Keeps what backward needs
+ * in the workspace; rows must stay valid until backward. */
+int  mgpt_moe_experts_forward(mgpt_moe_layer* layer, const void* rows, const int32_t* seg_counts, int n_src,
+                              int n_rows, void* out_rows, void* workspace, size_t workspace_bytes,
+                              mgpt_stream_t stream);
+/* d_in_rows = gradient w.r.t. rows (same layout; d_out_rows must be zero in padding rows, as
+ * mgpt_moe_combine_backward writes it); accumulates the expert parameter gradients (MoELayer.cpp:159-181). */
 int  mgpt_moe_experts_backward(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
                                void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
 

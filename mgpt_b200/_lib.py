@@ -79,7 +79,7 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_combine.argtypes = [vp, vp, vp, i32, vp, sz, vp]
     lib.mgpt_moe_combine_backward.argtypes = [vp, vp, vp, i32, vp, vp, sz, vp]
     lib.mgpt_moe_route_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]
-    lib.mgpt_moe_experts_forward.argtypes = [vp, vp, vp, i32, vp, vp, sz, vp]
+    lib.mgpt_moe_experts_forward.argtypes = [vp, vp, vp, i32, i32, vp, vp, sz, vp]
     lib.mgpt_moe_experts_backward.argtypes = [vp, vp, vp, vp, sz, vp]
     lib.mgpt_moe_op_plan_noalloc.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
     _lib = lib

@@ -45,7 +45,8 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
         return o;
     };
     const size_t rc = (size_t)w.row_cap, ab = w.act_bytes;
-    const size_t big = kind == 0 ? 1 : 0;          // routing-side workspaces carry no activation buffers
+    const size_t big = kind == 1 ? 0 : 1;          // routing-side workspaces carry no activation buffers
+    const size_t rowbuf = kind == 0 ? 1 : 0;       // expert-side row buffers belong to the caller
     w.logits = take(N * E * 4);
     w.probs = take(N * E * 4);
     w.top_idx = take(N * k * 4);
@@ -61,15 +62,16 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     w.row_src = take(rc * 4);
     w.blk_cnt = take((size_t)w.plan_blocks * E * 4);
     w.slot = take(N * k * 4);
-    w.Xg = take(big * rc * C * ab);
+    w.seg = take(E * MAX_SOURCES * 2 * 4);
+    w.Xg = take(rowbuf * rc * C * ab);
     w.G = take(big * rc * H * ab);
     w.U = take(big * rc * H * ab);
     w.Hh = take(big * rc * H * ab);
-    w.Yg = take(big * rc * C * ab);
-    w.dYg = take(big * rc * C * ab);
+    w.Yg = take(rowbuf * rc * C * ab);
+    w.dYg = take(rowbuf * rc * C * ab);
     w.dG = take(big * rc * H * ab);
     w.dU = take(big * rc * H * ab);
-    w.dXg = take(big * rc * C * ab);
+    w.dXg = take(rowbuf * rc * C * ab);
     w.d_top_p = take(N * k * 4);
     w.dlogits = take(N * E * 4);
     // router weight gradient: per-token-chunk partial sums, reduced in a second pass
@@ -301,6 +303,8 @@ int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, in
     char* ws = (char*)workspace;
     const Dims& d = L->d;
     L->fwd_done = false;
+    L->ext_Xg = L->ext_Yg = L->ext_dYg = L->ext_dXg = nullptr;      // whole-layer calls keep every buffer in the workspace
+    L->n_seg = 0;
     for (int s = 0; s < ST_COUNT; ++s) L->ev_used[s] = false;
     if (n_tokens > 0) {
         L->stage_begin(ST_ROUTER, st);

@@ -18,6 +18,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int ROW_TILE = 128;   // rows of one expert segment are padded to this
 constexpr int MAX_EXPERTS = 128;
 constexpr int MAX_TOPK = 8;
+constexpr int MAX_SOURCES = 64;  // source ranks an expert-side layer can receive row segments from
 
 enum Stage {
     ST_ROUTER = 0, ST_PLAN, ST_DISPATCH, ST_GATEUP, ST_DOWN, ST_COMBINE,
@@ -58,7 +59,7 @@ struct Workspace {
     size_t logits, probs, top_idx, top_p;
     // plan
     size_t counts, offsets, padded_offsets, tile_expert, n_tiles, status;
-    size_t map, pos, row_src, blk_cnt, slot;
+    size_t map, pos, row_src, blk_cnt, slot, seg;
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries
@@ -76,7 +77,8 @@ struct Dims {
     int gemm_impl;  // 0 default, 1 SIMT
 };
 
-// kind 0: whole layer; kind 1: routing side only (no activation buffers; rows are exchanged by the caller)
+// kind 0: whole layer; kind 1: routing side only (no activation buffers; rows are exchanged by the caller);
+// kind 2: expert side (the four [rows, C] buffers belong to the caller)
 Workspace make_workspace(const Dims& d, int n_tokens, int kind = 0);
 
 // Device-side tables of per-expert pointers (index = expert).
@@ -119,6 +121,11 @@ struct mgpt_moe_layer {
     // TMA descriptors (opaque, built per workspace pointer)
     void* tc_state = nullptr;
 
+    // expert side of an expert-parallel layer: row buffers owned by the caller (the exchange buffers) and the
+    // number of row segments per expert (one per source rank); 0 = one contiguous padded range per expert
+    void *ext_Xg = nullptr, *ext_Yg = nullptr, *ext_dYg = nullptr, *ext_dXg = nullptr;
+    int n_seg = 0;
+
     // optional per-stage timing
     bool profiling = false;
     cudaEvent_t ev_begin[mgpt::ST_COUNT] = {}, ev_end[mgpt::ST_COUNT] = {};
@@ -138,6 +145,12 @@ struct mgpt_moe_layer {
 
 namespace mgpt {
 
+// the four [rows, C] buffers: in the workspace, or caller-owned on the expert side of an expert-parallel layer
+inline char* buf_Xg(const mgpt_moe_layer* L, const Workspace& w, char* ws) { return L->ext_Xg ? (char*)L->ext_Xg : ws + w.Xg; }
+inline char* buf_Yg(const mgpt_moe_layer* L, const Workspace& w, char* ws) { return L->ext_Yg ? (char*)L->ext_Yg : ws + w.Yg; }
+inline char* buf_dYg(const mgpt_moe_layer* L, const Workspace& w, char* ws) { return L->ext_dYg ? (char*)L->ext_dYg : ws + w.dYg; }
+inline char* buf_dXg(const mgpt_moe_layer* L, const Workspace& w, char* ws) { return L->ext_dXg ? (char*)L->ext_dXg : ws + w.dXg; }
+
 // ---- stage launchers (each enqueues on `st`, returns 0 or an error code) ---
 
 // router.cu
@@ -152,6 +165,7 @@ int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, 
 int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st);
 int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st);
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st);
 int gather_rows(const void* src, int src_io, const int32_t* row_src, const int32_t* n_tiles, int rows, int grid_rows,
                 int C, int k, void* dst, size_t act_bytes, cudaStream_t st);
 int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,

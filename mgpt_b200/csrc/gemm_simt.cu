@@ -135,6 +135,8 @@ struct WgradArgs {
     float* const* grad;          // per expert [M, N]
     const int32_t* padded_offsets;
     int M, N;
+    const int32_t* seg;          // [E][n_seg][2] {first row, rows} when an expert's rows come in several segments
+    int n_seg;
 };
 
 template <typename TAct>
@@ -143,13 +145,20 @@ __global__ void __launch_bounds__(256) simt_wgrad_kernel(WgradArgs a)
     __shared__ __align__(16) float As[TK][TM + 4];
     __shared__ __align__(16) float Bs[TK][TN + 4];
     const int e = blockIdx.z;
-    const int r0 = a.padded_offsets[e], r1 = a.padded_offsets[e + 1];
-    if (r0 >= r1) return;
     const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
     float acc[4][4] = {};
-    const TAct* A = (const TAct*)a.A + (size_t)r0 * a.lda;
-    const TAct* B = (const TAct*)a.B + (size_t)r0 * a.ldb;
-    tile_mac(A, 1L, (long)a.lda, m0, a.M, B, (long)a.ldb, 1L, n0, a.N, r1 - r0, acc, As, Bs);
+    const int nseg = a.n_seg > 0 ? a.n_seg : 1;
+    int total = 0;
+    for (int sgi = 0; sgi < nseg; ++sgi) {
+        const int r0 = a.n_seg > 0 ? a.seg[(e * a.n_seg + sgi) * 2] : a.padded_offsets[e];
+        const int len = a.n_seg > 0 ? a.seg[(e * a.n_seg + sgi) * 2 + 1] : a.padded_offsets[e + 1] - r0;
+        if (len <= 0) continue;               // uniform over the CTA
+        total += len;
+        const TAct* A = (const TAct*)a.A + (size_t)r0 * a.lda;
+        const TAct* B = (const TAct*)a.B + (size_t)r0 * a.ldb;
+        tile_mac(A, 1L, (long)a.lda, m0, a.M, B, (long)a.ldb, 1L, n0, a.N, len, acc, As, Bs);
+    }
+    if (total == 0) return;
     float* g = a.grad[e];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
 #pragma unroll
@@ -172,14 +181,14 @@ int experts_forward_t(mgpt_moe_layer* L, const ExpertPtrs& P, const Workspace& w
     a.tile_expert = (const int32_t*)(ws + w.tile_expert);
     a.n_tiles = (const int32_t*)(ws + w.n_tiles);
     // gate/up + SwiGLU
-    a.A = ws + w.Xg; a.B = P.Wg; a.B2 = P.Wu; a.bias = P.bg; a.bias2 = P.bu;
+    a.A = buf_Xg(L, w, ws); a.B = P.Wg; a.B2 = P.Wu; a.bias = P.bg; a.bias2 = P.bu;
     a.D = ws + w.G; a.D2 = ws + w.U; a.D3 = ws + w.Hh; a.K = d.C; a.Nout = d.H;
     L->stage_begin(ST_GATEUP, st);
     simt_rows_kernel<TAct, TW, EPI_GATEUP><<<dim3(w.row_cap / TM, (d.H + TN - 1) / TN), 256, 0, st>>>(a);
     MGPT_LAUNCHED("simt_rows_kernel<gateup>");
     L->stage_end(ST_GATEUP, st);
     // down
-    a.A = ws + w.Hh; a.B = P.Wd; a.bias = P.bd; a.D = ws + w.Yg; a.K = d.H; a.Nout = d.C;
+    a.A = ws + w.Hh; a.B = P.Wd; a.bias = P.bd; a.D = buf_Yg(L, w, ws); a.K = d.H; a.Nout = d.C;
     L->stage_begin(ST_DOWN, st);
     simt_rows_kernel<TAct, TW, EPI_DOWN><<<dim3(w.row_cap / TM, (d.C + TN - 1) / TN), 256, 0, st>>>(a);
     MGPT_LAUNCHED("simt_rows_kernel<down>");
@@ -195,14 +204,14 @@ int experts_backward_t(mgpt_moe_layer* L, const ExpertPtrs& P, const Workspace& 
     a.tile_expert = (const int32_t*)(ws + w.tile_expert);
     a.n_tiles = (const int32_t*)(ws + w.n_tiles);
     // dHh = dYg * Wd^T, fused SwiGLU backward -> dG, dU
-    a.A = ws + w.dYg; a.B = P.Wd; a.G = ws + w.G; a.U = ws + w.U; a.D = ws + w.dG; a.D2 = ws + w.dU;
+    a.A = buf_dYg(L, w, ws); a.B = P.Wd; a.G = ws + w.G; a.U = ws + w.U; a.D = ws + w.dG; a.D2 = ws + w.dU;
     a.K = d.C; a.Nout = d.H;
     L->stage_begin(ST_DHH, st);
     simt_rows_kernel<TAct, TW, EPI_DHH><<<dim3(w.row_cap / TM, (d.H + TN - 1) / TN), 256, 0, st>>>(a);
     MGPT_LAUNCHED("simt_rows_kernel<dhh>");
     L->stage_end(ST_DHH, st);
     // dXg = dG * Wg^T + dU * Wu^T
-    a.A = ws + w.dG; a.A2 = ws + w.dU; a.B = P.Wg; a.B2 = P.Wu; a.D = ws + w.dXg; a.K = d.H; a.Nout = d.C;
+    a.A = ws + w.dG; a.A2 = ws + w.dU; a.B = P.Wg; a.B2 = P.Wu; a.D = buf_dXg(L, w, ws); a.K = d.H; a.Nout = d.C;
     L->stage_begin(ST_DXG, st);
     simt_rows_kernel<TAct, TW, EPI_DXG><<<dim3(w.row_cap / TM, (d.C + TN - 1) / TN), 256, 0, st>>>(a);
     MGPT_LAUNCHED("simt_rows_kernel<dxg>");
@@ -212,8 +221,9 @@ int experts_backward_t(mgpt_moe_layer* L, const ExpertPtrs& P, const Workspace& 
     const int32_t* poff = (const int32_t*)(ws + w.padded_offsets);
     WgradArgs g = {};
     g.padded_offsets = poff;
+    g.seg = (const int32_t*)(ws + w.seg); g.n_seg = L->n_seg;
     // dWg += Xg^T dG ; dWu += Xg^T dU   [C,H]
-    g.A = ws + w.Xg; g.lda = d.C; g.M = d.C; g.N = d.H; g.ldb = d.H;
+    g.A = buf_Xg(L, w, ws); g.lda = d.C; g.M = d.C; g.N = d.H; g.ldb = d.H;
     dim3 gCH((d.C + TM - 1) / TM, (d.H + TN - 1) / TN, d.E);
     g.B = ws + w.dG; g.grad = L->master.gWg;
     simt_wgrad_kernel<TAct><<<gCH, 256, 0, st>>>(g);
@@ -222,7 +232,7 @@ int experts_backward_t(mgpt_moe_layer* L, const ExpertPtrs& P, const Workspace& 
     simt_wgrad_kernel<TAct><<<gCH, 256, 0, st>>>(g);
     MGPT_LAUNCHED("simt_wgrad_kernel<Wu>");
     // dWd += Hh^T dYg   [H,C]
-    g.A = ws + w.Hh; g.lda = d.H; g.M = d.H; g.B = ws + w.dYg; g.ldb = d.C; g.N = d.C; g.grad = L->master.gWd;
+    g.A = ws + w.Hh; g.lda = d.H; g.M = d.H; g.B = buf_dYg(L, w, ws); g.ldb = d.C; g.N = d.C; g.grad = L->master.gWd;
     dim3 gHC((d.H + TM - 1) / TM, (d.C + TN - 1) / TN, d.E);
     simt_wgrad_kernel<TAct><<<gHC, 256, 0, st>>>(g);
     MGPT_LAUNCHED("simt_wgrad_kernel<Wd>");

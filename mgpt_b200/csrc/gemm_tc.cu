@@ -536,6 +536,8 @@ struct WgradProb {
 };
 struct WgradP {
     const int32_t* padded_offsets;
+    const int32_t* seg;     // [E][n_seg][2] {first row, rows}: an expert's rows in n_seg segments (0 = one padded range)
+    int n_seg;
     int32_t* status;
     WgradProb prob[3];
     int n_probs, total_items;
@@ -556,6 +558,10 @@ __device__ __forceinline__ WgradItem wgrad_item(const WgradP& p, int item)
     if (q.uniform_rows) {
         w.r0 = w.e * q.uniform_rows;
         w.nkb = q.uniform_rows / BK;
+    } else if (p.n_seg > 0) {
+        w.r0 = 0;
+        w.nkb = 0;
+        for (int sg = 0; sg < p.n_seg; ++sg) w.nkb += p.seg[(w.e * p.n_seg + sg) * 2 + 1] / BK;
     } else {
         w.r0 = p.padded_offsets[w.e];
         w.nkb = (p.padded_offsets[w.e + 1] - w.r0) / BK;
@@ -586,19 +592,25 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                 const WgradItem w = wgrad_item(p, item);
                 const CUtensorMap* mA = w.pr == 0 ? &tmA0 : w.pr == 1 ? &tmA1 : &tmA2;
                 const CUtensorMap* mB = w.pr == 0 ? &tmB0 : w.pr == 1 ? &tmB1 : &tmB2;
-                for (int kb = 0; kb < w.nkb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
-                        ok = false;
-                        break;
+                const bool segmented = p.n_seg > 0 && !p.prob[w.pr].uniform_rows;
+                const int nseg = segmented ? p.n_seg : 1;
+                for (int sg = 0; sg < nseg && ok; ++sg) {
+                    const int seg_r0 = segmented ? p.seg[(w.e * p.n_seg + sg) * 2] : w.r0;
+                    const int seg_kb = segmented ? p.seg[(w.e * p.n_seg + sg) * 2 + 1] / BK : w.nkb;
+                    for (int kb = 0; kb < seg_kb; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                        mbar_expect_tx(pipe.full(s), STAGE_BYTES);
+                        const int row = seg_r0 + kb * BK;
+#pragma unroll
+                        for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
+#pragma unroll
+                        for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
                     }
-                    const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                    mbar_expect_tx(pipe.full(s), STAGE_BYTES);
-                    const int row = w.r0 + kb * BK;
-#pragma unroll
-                    for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
-#pragma unroll
-                    for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
                 }
             }
         }
@@ -726,6 +738,7 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 struct TcState {
     const void* ws = nullptr;
+    const void *xg = nullptr, *yg = nullptr, *dyg = nullptr, *dxg = nullptr;
     int n_tokens = -1;
     bool attr_set = false;
     int sms = 0;
@@ -743,12 +756,13 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
 {
     MGPT_TRY(prepare_attrs(L));
     TcState* s = (TcState*)L->tc_state;
-    if (s->ws == ws && s->n_tokens == w.n_tokens) return 0;
+    const void *xg = buf_Xg(L, w, ws), *yg = buf_Yg(L, w, ws), *dyg = buf_dYg(L, w, ws), *dxg = buf_dXg(L, w, ws);
+    if (s->ws == ws && s->n_tokens == w.n_tokens && s->xg == xg && s->yg == yg && s->dyg == dyg && s->dxg == dxg) return 0;
     const Dims& d = L->d;
     const uint64_t rc = w.row_cap, C = d.C, H = d.H, E = d.E;
-    MGPT_TRY(make_map(&s->Xg, ws + w.Xg, rc, C, 128));
+    MGPT_TRY(make_map(&s->Xg, xg, rc, C, 128));
     MGPT_TRY(make_map(&s->Hh, ws + w.Hh, rc, H, 128));
-    MGPT_TRY(make_map(&s->dYg, ws + w.dYg, rc, C, 128));
+    MGPT_TRY(make_map(&s->dYg, dyg, rc, C, 128));
     MGPT_TRY(make_map(&s->dG, ws + w.dG, rc, H, 128));
     MGPT_TRY(make_map(&s->dU, ws + w.dU, rc, H, 128));
     MGPT_TRY(make_map(&s->WgT, L->sWgT, E * H, C, 128));
@@ -757,20 +771,21 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->Wg, L->sWg, E * C, H, 128));
     MGPT_TRY(make_map(&s->Wu, L->sWu, E * C, H, 128));
     MGPT_TRY(make_map(&s->Wd, L->sWd, E * H, C, 128));
-    MGPT_TRY(make_map(&s->Xg_t, ws + w.Xg, rc, C, 64));
+    MGPT_TRY(make_map(&s->Xg_t, xg, rc, C, 64));
     MGPT_TRY(make_map(&s->Hh_t, ws + w.Hh, rc, H, 64));
-    MGPT_TRY(make_map(&s->dYg_t, ws + w.dYg, rc, C, 64));
+    MGPT_TRY(make_map(&s->dYg_t, dyg, rc, C, 64));
     MGPT_TRY(make_map(&s->dG_t, ws + w.dG, rc, H, 64));
     MGPT_TRY(make_map(&s->dU_t, ws + w.dU, rc, H, 64));
     MGPT_TRY(make_map(&s->G_s, ws + w.G, rc, H, 32));
     MGPT_TRY(make_map(&s->U_s, ws + w.U, rc, H, 32));
     MGPT_TRY(make_map(&s->Hh_s, ws + w.Hh, rc, H, 32));
-    MGPT_TRY(make_map(&s->Yg_s, ws + w.Yg, rc, C, 32));
+    MGPT_TRY(make_map(&s->Yg_s, yg, rc, C, 32));
     MGPT_TRY(make_map(&s->dG_s, ws + w.dG, rc, H, 32));
     MGPT_TRY(make_map(&s->dU_s, ws + w.dU, rc, H, 32));
-    MGPT_TRY(make_map(&s->dXg_s, ws + w.dXg, rc, C, 32));
+    MGPT_TRY(make_map(&s->dXg_s, dxg, rc, C, 32));
     s->ws = ws;
     s->n_tokens = w.n_tokens;
+    s->xg = xg; s->yg = yg; s->dyg = dyg; s->dxg = dxg;
     return 0;
 }
 
@@ -854,6 +869,8 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     //   gWg += Xg^T dG, gWu += Xg^T dU   [C,H];   gWd += Hh^T dYg   [H,C]
     WgradP g = {};
     g.padded_offsets = (const int32_t*)(ws + w.padded_offsets);
+    g.seg = (const int32_t*)(ws + w.seg);
+    g.n_seg = L->n_seg;
     g.status = (int32_t*)(ws + w.status);
     g.n_probs = 3;
     float* const* grads[3] = {L->master.gWg, L->master.gWu, L->master.gWd};

@@ -422,7 +422,7 @@ int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cud
 {
     const Dims& d = L->d;
     BiasGradArgs a;
-    a.M[0] = ws + w.dYg; a.M[1] = ws + w.dG; a.M[2] = ws + w.dU;
+    a.M[0] = buf_dYg(L, w, ws); a.M[1] = ws + w.dG; a.M[2] = ws + w.dU;
     a.gb[0] = L->master.gbd; a.gb[1] = L->master.gbg; a.gb[2] = L->master.gbu;
     a.cols[0] = d.C; a.cols[1] = d.H; a.cols[2] = d.H;
     a.tile_expert = (const int32_t*)(ws + w.tile_expert);
@@ -432,6 +432,50 @@ int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cud
     if (w.act_bytes == 4) bias_grad_kernel<float><<<grid, 256, 0, st>>>(a);
     else bias_grad_kernel<bf16><<<grid, 256, 0, st>>>(a);
     MGPT_LAUNCHED("bias_grad_kernel");
+    return 0;
+}
+
+// Expert side of an expert-parallel layer: rows arrive as one block per source rank, inside it one
+// 128-row-padded segment per local expert.  From the [n_src][E] real row counts this builds the tile ->
+// expert table in arrival order, the per-expert segment list {first row, padded rows} and the totals.
+__global__ void __launch_bounds__(256)
+segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, int32_t* __restrict__ counts,
+                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ n_tiles, int max_tiles,
+                     int32_t* __restrict__ seg, int32_t* __restrict__ status)
+{
+    __shared__ int first_tile[MAX_SOURCES * MAX_EXPERTS + 1];
+    const int n = n_src * E;
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int i = 0; i < n; ++i) {            // i = s*E + e, arrival order
+            first_tile[i] = t;
+            t += (seg_counts[i] + ROW_TILE - 1) / ROW_TILE;
+        }
+        first_tile[n] = t;
+        *n_tiles = t;
+        *status = t > max_tiles ? 1 : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int s_ = i / E, e = i % E;
+        const int t0 = first_tile[i], t1 = first_tile[i + 1];
+        seg[(e * n_src + s_) * 2] = t0 * ROW_TILE;
+        seg[(e * n_src + s_) * 2 + 1] = (t1 - t0) * ROW_TILE;
+        for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int s_ = 0; s_ < n_src; ++s_) c += seg_counts[s_ * E + e];
+        counts[e] = c;
+    }
+}
+
+int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st)
+{
+    segment_tiles_kernel<<<1, 256, 0, st>>>(seg_counts, n_src, d.E, (int32_t*)(ws + w.counts),
+                                            (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles), w.max_tiles,
+                                            (int32_t*)(ws + w.seg), (int32_t*)(ws + w.status));
+    MGPT_LAUNCHED("segment_tiles_kernel");
     return 0;
 }
 

@@ -6,10 +6,12 @@ gradients) and a replica of the router.  Per step:
     route (local)  ->  counts all-to-all  ->  rows all-to-all  ->  experts (local)
                    ->  rows all-to-all back  ->  combine (local)
 
-and the mirror image for backward.  Rows leave a GPU in the reference's compact
-expert-major order, so the block for each destination is contiguous; they arrive
-ordered by (source rank, expert, source flat index) and the expert side regroups them
-by expert, stable in that order.  The load-balance term of the router gradient uses
+and the mirror image for backward.  Rows travel tile-aligned: expert-major with every
+expert's segment padded by zero rows to a multiple of 128, the layout the single-GPU
+layer uses internally.  The block for each destination is then one contiguous range and
+what arrives (one block per source rank, inside it one padded segment per local expert)
+is fed to the tensor-core kernels where it lands; the expert side moves no rows.
+The load-balance term of the router gradient uses
 each GPU's own counts, which equals running the reference independently on every
 GPU's batch.  The reference itself has no multi-GPU code.
 
@@ -109,12 +111,14 @@ class CudaStages:
 
     # ---- routing side
     def route(self, x):
+        """Returns (rows [row_cap, C] in the padded expert-major layout, counts[E] real rows per expert)."""
         n = x.shape[0]
         self._home_ws = self._home_ws_for(n)
-        rows = torch.empty(n * self.k, self.C, dtype=self.act_dtype, device=self.device)
+        self._n = n
+        row_cap = self._view(self.home, self._home_ws, n, "row_src", torch.int32).numel()
+        rows = torch.empty(row_cap, self.C, dtype=self.act_dtype, device=self.device)
         self._lib_mod.check(self.lib.mgpt_moe_route(self.home, x.data_ptr(), n, self._io(x), self._home_ws.data_ptr(),
                                                     self._home_ws.numel(), rows.data_ptr(), self._stream()))
-        self._n = n
         counts = self._view(self.home, self._home_ws, n, "counts", torch.int32)
         return rows, counts
 
@@ -145,14 +149,16 @@ class CudaStages:
         return dx
 
     # ---- expert side
-    def experts_forward(self, rows, expert_of_row):
+    def experts_forward(self, rows, seg_counts, n_src):
+        """rows: n_src blocks of padded per-expert segments; seg_counts: int32 [n_src, E_local] real counts."""
         n = rows.shape[0]
         self._local_ws = self._ws(self.local, n, False, self._local_ws)
         out = torch.empty_like(rows)
+        self._seg_counts = seg_counts.contiguous()
         self._lib_mod.check(self.lib.mgpt_moe_experts_forward(
-            self.local, rows.data_ptr(), expert_of_row.data_ptr(), n, out.data_ptr(),
+            self.local, rows.data_ptr(), self._seg_counts.data_ptr(), n_src, n, out.data_ptr(),
             self._local_ws.data_ptr(), self._local_ws.numel(), self._stream()))
-        self._rows = n
+        self._rows = rows          # read again by the weight gradients
         return out
 
     def experts_backward(self, d_out):
@@ -229,12 +235,16 @@ class ExpertParallelMoE:
             dist.all_to_all_single(recv, send.contiguous(), list(recv_splits), list(send_splits), group=self.group)
         return recv
 
+    @staticmethod
+    def _pad128(t):
+        return (t + 127) // 128 * 128
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         G, El = self.world, self.E_local
         if self.phase_events is not None:
             self.phase_events["order"] = []
         self._mark("start")
-        rows, counts = self.stages.route(x)                          # [R,C] compact expert-major, counts[E]
+        rows, counts = self.stages.route(x)                          # padded expert-major rows, counts[E]
         self._mark("route")
         counts = counts.view(G, El)
         recv_counts = torch.empty_like(counts)                       # [source rank, local expert]
@@ -242,15 +252,13 @@ class ExpertParallelMoE:
             recv_counts.copy_(counts)
         else:
             dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)
-        both = torch.stack([counts.sum(1), recv_counts.sum(1)]).cpu()   # the one host sync of the step
+        both = torch.stack([self._pad128(counts).sum(1), self._pad128(recv_counts).sum(1)]).cpu()   # the one host sync
         send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+        n_send = int(sum(send_splits))
         self._mark("counts_exchange_and_host_sync")
-        recv_rows = self._all_to_all(rows, send_splits, recv_splits)
+        recv_rows = self._all_to_all(rows[:n_send], send_splits, recv_splits)
         self._mark("rows_all_to_all")
-        expert_ids = torch.arange(El, device=recv_counts.device, dtype=torch.int32).repeat(G)
-        expert_of_row = torch.repeat_interleave(expert_ids, recv_counts.reshape(-1).to(torch.int64),
-                                                output_size=int(sum(recv_splits))).to(torch.int32)
-        out_rows = self.stages.experts_forward(recv_rows, expert_of_row)
+        out_rows = self.stages.experts_forward(recv_rows, recv_counts, G)
         self._mark("experts_forward")
         rows_back = self._all_to_all(out_rows, recv_splits, send_splits)
         self._mark("rows_back_all_to_all")
@@ -264,9 +272,10 @@ class ExpertParallelMoE:
         if self._saved is None:
             raise RuntimeError("backward before forward")
         x, rows_back, send_splits, recv_splits = self._saved
+        n_send = int(sum(send_splits))            # = every tile of the local plan
         d_rows = self.stages.combine_backward(rows_back, dy)
         self._mark("combine_backward")
-        d_recv = self._all_to_all(d_rows, send_splits, recv_splits)
+        d_recv = self._all_to_all(d_rows[:n_send], send_splits, recv_splits)
         self._mark("grad_rows_all_to_all")
         d_in = self.stages.experts_backward(d_recv)
         self._mark("experts_backward")

@@ -27,7 +27,17 @@ class CpuStages:
     def sync_weights(self):
         pass
 
-    # ---- routing side
+    # ---- routing side (rows in the padded expert-major layout of the CUDA stages)
+    def _layout(self):
+        r, k = self.r, self.k
+        cnt, off = r["counts"].astype(np.int64), r["offsets"].astype(np.int64)
+        poff = np.concatenate([[0], np.cumsum((cnt + 127) // 128 * 128)])
+        flat_e = r["top_idx"].reshape(-1).astype(np.int64)
+        slot_of = np.empty(self.n * k, np.int64)
+        slot_of[r["map"]] = np.arange(self.n * k)
+        self.pos = poff[flat_e] + slot_of - off[flat_e]          # flat index -> padded row
+        self.n_rows = int(poff[-1])
+
     def route(self, x):
         xn = x.numpy()
         n = xn.shape[0]
@@ -35,35 +45,36 @@ class CpuStages:
         params = [p.numpy() for p in self.router_params] + dummy
         r = oracle.run(oracle.Dims(n, self.C, self.H, self.E, self.k, self.alpha), xn, params, route_only=True)
         self.r, self.n = r, n
-        rows = xn[r["map"] // self.k]
-        return torch.from_numpy(np.ascontiguousarray(rows)), torch.from_numpy(r["counts"].copy())
+        self._layout()
+        rows = np.zeros((self.n_rows + 128, self.C), np.float32)      # a little spare capacity, like row_cap
+        rows[self.pos] = xn[np.arange(n * self.k) // self.k]
+        return torch.from_numpy(rows), torch.from_numpy(r["counts"].copy())
 
     def combine(self, rows_back, like):
-        r, k = self.r, self.k
+        k = self.k
         y = np.zeros((self.n, self.C), np.float32)
-        rb = rows_back.numpy()
-        for s in range(self.n * k):
-            flat = r["map"][s]
-            y[flat // k] += rb[s] * r["top_p"].reshape(-1)[flat]
+        rb, tp = rows_back.numpy(), self.r["top_p"].reshape(-1)
+        for flat in np.argsort(self.pos):                 # ascending row order, like the reference's slot order
+            y[flat // k] += rb[self.pos[flat]] * tp[flat]
         return torch.from_numpy(y)
 
     def combine_backward(self, rows_back, dy):
-        r, k = self.r, self.k
-        rb, g = rows_back.numpy(), dy.numpy()
+        k = self.k
+        rb, g, tp = rows_back.numpy(), dy.numpy(), self.r["top_p"].reshape(-1)
         d_rows = np.zeros_like(rb)
         self.dtp = np.zeros(self.n * k, np.float32)
-        for s in range(self.n * k):
-            flat = r["map"][s]
-            d_rows[s] = g[flat // k] * r["top_p"].reshape(-1)[flat]
-            self.dtp[flat] = float(rb[s] @ g[flat // k])
+        for flat in range(self.n * k):
+            p = self.pos[flat]
+            d_rows[p] = g[flat // k] * tp[flat]
+            self.dtp[flat] = float(rb[p] @ g[flat // k])
         return torch.from_numpy(d_rows)
 
     def route_backward(self, x, d_rows):
         r, k, E, n = self.r, self.k, self.E, self.n
         xn, dr = x.numpy(), d_rows.numpy()
         dx = np.zeros_like(xn)
-        for s in range(n * k):
-            dx[r["map"][s] // k] += dr[s]
+        for flat in range(n * k):
+            dx[flat // k] += dr[self.pos[flat]]
         dP = np.zeros((n, E), np.float32)
         flat_e = r["top_idx"].reshape(-1)
         dP[np.arange(n * k) // k, flat_e] = self.dtp
@@ -75,13 +86,22 @@ class CpuStages:
         self.router_params[1].grad += torch.from_numpy(dL.sum(0, keepdims=True))
         return torch.from_numpy(dx + dL @ Wr.T)
 
-    # ---- expert side
-    def experts_forward(self, rows, expert_of_row):
-        X, eo = rows.numpy(), expert_of_row.numpy()
+    # ---- expert side: n_src blocks, each one padded segment per local expert
+    def experts_forward(self, rows, seg_counts, n_src):
+        X, sc = rows.numpy(), seg_counts.numpy().reshape(n_src, self.E_local)
+        index = [[] for _ in range(self.E_local)]
+        r0 = 0
+        for s in range(n_src):
+            for e in range(self.E_local):
+                c = int(sc[s, e])
+                index[e] += list(range(r0, r0 + c))
+                assert not X[r0 + c: r0 + (c + 127) // 128 * 128].any(), "padding rows must arrive as zeros"
+                r0 += (c + 127) // 128 * 128
+        assert r0 == X.shape[0]
         out = np.zeros_like(X)
         self.saved = []
         for e in range(self.E_local):
-            idx = np.nonzero(eo == e)[0]
+            idx = np.array(index[e], dtype=np.int64)
             Wg, bg, Wu, bu, Wd, bd = [p.numpy() for p in self.expert_params[6 * e: 6 * e + 6]]
             xe = X[idx]
             G, U = xe @ Wg + bg, xe @ Wu + bu
