@@ -63,6 +63,7 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     w.blk_cnt = take((size_t)w.plan_blocks * E * 4);
     w.slot = take(N * k * 4);
     w.seg = take(E * MAX_SOURCES * 2 * 4);
+    w.tile_order = take((size_t)w.max_tiles * 4);
     w.Xg = take(rowbuf * rc * C * ab);
     w.G = take(big * rc * H * ab);
     w.U = take(big * rc * H * ab);

@@ -19,6 +19,7 @@ constexpr int ROW_TILE = 128;   // rows of one expert segment are padded to this
 constexpr int MAX_EXPERTS = 128;
 constexpr int MAX_TOPK = 8;
 constexpr int MAX_SOURCES = 64;  // source ranks an expert-side layer can receive row segments from
+constexpr int MAX_SEGMENTS = 4096;  // sources x local experts
 
 enum Stage {
     ST_ROUTER = 0, ST_PLAN, ST_DISPATCH, ST_GATEUP, ST_DOWN, ST_COMBINE,
@@ -59,7 +60,7 @@ struct Workspace {
     size_t logits, probs, top_idx, top_p;
     // plan
     size_t counts, offsets, padded_offsets, tile_expert, n_tiles, status;
-    size_t map, pos, row_src, blk_cnt, slot, seg;
+    size_t map, pos, row_src, blk_cnt, slot, seg, tile_order;
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries

@@ -304,6 +304,7 @@ enum { MODE_GATEUP = 0, MODE_DOWN = 1, MODE_DHH = 2, MODE_DXG = 3, MODE_DX = 4 }
 
 struct RowsP {
     const int32_t* tile_expert;
+    const int32_t* tile_order;  // optional: i-th row tile to work on (expert-major order over scattered tiles)
     const int32_t* n_tiles;
     int32_t* status;
     int kblocks;            // k-blocks (of 64) per operand pair
@@ -346,7 +347,8 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             uint32_t it = 0;
             bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-                const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+                const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+                const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
                 const int brow = (MODE == MODE_DX ? 0 : p.tile_expert[row_tile] * p.b_rows_per_expert) + n0;
                 const int row0 = row_tile * BM;
                 for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
@@ -407,7 +409,8 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         uint32_t t = 0;
         for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++t) {
             const uint32_t buf = t & 1u;
-            const int row_tile = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+            const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+                const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
             const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
             const int row_w = row_tile * BM + q * 32;           // first row of this warp
             if (MODE == MODE_DHH) {
@@ -818,6 +821,7 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     const Dims& d = L->d;
     RowsP p = {};
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
+    p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
     p.status = (int32_t*)(ws + w.status);
     // gate/up + SwiGLU: K = C, 128 hidden units per item
@@ -846,6 +850,7 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     const Dims& d = L->d;
     RowsP p = {};
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
+    p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
     p.status = (int32_t*)(ws + w.status);
     // dHh = dYg * Wd^T  (K = C), SwiGLU backward in the epilogue

@@ -440,10 +440,12 @@ int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cud
 // expert table in arrival order, the per-expert segment list {first row, padded rows} and the totals.
 __global__ void __launch_bounds__(256)
 segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, int32_t* __restrict__ counts,
-                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ n_tiles, int max_tiles,
-                     int32_t* __restrict__ seg, int32_t* __restrict__ status)
+                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_order,
+                     int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ seg,
+                     int32_t* __restrict__ status)
 {
-    __shared__ int first_tile[MAX_SOURCES * MAX_EXPERTS + 1];
+    __shared__ int first_tile[MAX_SEGMENTS + 1];     // in arrival order (s, e)
+    __shared__ int first_item[MAX_SEGMENTS];         // in processing order (e, s)
     const int n = n_src * E;
     if (threadIdx.x == 0) {
         int t = 0;
@@ -454,6 +456,12 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
         first_tile[n] = t;
         *n_tiles = t;
         *status = t > max_tiles ? 1 : 0;
+        int it = 0;
+        for (int e = 0; e < E; ++e)
+            for (int s_ = 0; s_ < n_src; ++s_) {
+                first_item[e * n_src + s_] = it;
+                it += (seg_counts[s_ * E + e] + ROW_TILE - 1) / ROW_TILE;
+            }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -461,7 +469,12 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
         const int t0 = first_tile[i], t1 = first_tile[i + 1];
         seg[(e * n_src + s_) * 2] = t0 * ROW_TILE;
         seg[(e * n_src + s_) * 2 + 1] = (t1 - t0) * ROW_TILE;
-        for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+        const int o0 = first_item[e * n_src + s_];
+        for (int t = t0; t < t1 && t < max_tiles; ++t) {
+            tile_expert[t] = e;
+            // tiles are worked on expert after expert (one expert's weights stay in L2), wherever they landed
+            if (o0 + (t - t0) < max_tiles) tile_order[o0 + (t - t0)] = t;
+        }
     }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int c = 0;
@@ -472,9 +485,11 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
 
 int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st)
 {
+    if (n_src * d.E > MAX_SEGMENTS) return fail(MGPT_MOE_EINVAL, "sources x local experts must not exceed 4096");
     segment_tiles_kernel<<<1, 256, 0, st>>>(seg_counts, n_src, d.E, (int32_t*)(ws + w.counts),
-                                            (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles), w.max_tiles,
-                                            (int32_t*)(ws + w.seg), (int32_t*)(ws + w.status));
+                                            (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.tile_order),
+                                            (int32_t*)(ws + w.n_tiles), w.max_tiles, (int32_t*)(ws + w.seg),
+                                            (int32_t*)(ws + w.status));
     MGPT_LAUNCHED("segment_tiles_kernel");
     return 0;
 }
