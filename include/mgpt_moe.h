@@ -154,7 +154,7 @@ int  mgpt_moe_op_router(const void* x, int io_dtype, const float* Wr, const floa
  * segment rounded up to 128 rows), tile_expert[row_cap/128], n_tiles[1],
  * map[n_rows] (compact slot -> flat index, the reference's sorted_token_ids),
  * pos[n_rows] (flat index -> padded row), row_src[row_cap] (padded row -> flat
- * index, -1 for padding), status[1] (0 = ok).
+ * index, -1 for padding; written for the n_tiles*128 rows in use), status[1] (0 = ok).
  * row_cap: a multiple of 128, at least (n_rows + E*127) rounded down to 128.
  * scratch: device memory of mgpt_moe_op_plan_scratch_bytes(n_rows, E) bytes. */
 size_t mgpt_moe_op_plan_scratch_bytes(int n_rows, int E);

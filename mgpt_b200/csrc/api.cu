@@ -177,6 +177,10 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
         if (L->ev_begin[s]) cudaEventDestroy(L->ev_begin[s]);
         if (L->ev_end[s]) cudaEventDestroy(L->ev_end[s]);
     }
+    if (L->copy_stream) {
+        cudaStreamDestroy(L->copy_stream);
+        for (auto& e : L->copy_ev) cudaEventDestroy(e);
+    }
     delete L;
 }
 
@@ -406,13 +410,32 @@ int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_hos
         MGPT_CUDA(cudaMalloc(&L->h_ws, ws_bytes));
         L->h_ws_bytes = ws_bytes;
     }
+    // Copies that nothing is waiting for yet run on a second stream: dy goes up while forward computes and
+    // y comes down (the other PCIe direction) while backward computes.
+    if (!L->copy_stream) {
+        MGPT_CUDA(cudaStreamCreateWithFlags(&L->copy_stream, cudaStreamNonBlocking));
+        for (auto& e : L->copy_ev) MGPT_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    cudaStream_t cs = L->copy_stream;
     MGPT_CUDA(cudaMemcpyAsync(L->h_x, x_host, io_bytes, cudaMemcpyHostToDevice, st));
-    if (dy_host) MGPT_CUDA(cudaMemcpyAsync(L->h_dy, dy_host, io_bytes, cudaMemcpyHostToDevice, st));
-    MGPT_TRY(mgpt_moe_forward(L, L->h_x, L->h_y, n_tokens, io, L->h_ws, L->h_ws_bytes, stream));
-    MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, st));
     if (dy_host) {
+        MGPT_CUDA(cudaEventRecord(L->copy_ev[0], st));              // after x: keep the upload order x, dy
+        MGPT_CUDA(cudaStreamWaitEvent(cs, L->copy_ev[0], 0));
+        MGPT_CUDA(cudaMemcpyAsync(L->h_dy, dy_host, io_bytes, cudaMemcpyHostToDevice, cs));
+        MGPT_CUDA(cudaEventRecord(L->copy_ev[1], cs));              // dy is on the device
+    }
+    MGPT_TRY(mgpt_moe_forward(L, L->h_x, L->h_y, n_tokens, io, L->h_ws, L->h_ws_bytes, stream));
+    if (dy_host) {
+        MGPT_CUDA(cudaEventRecord(L->copy_ev[2], st));              // y is complete
+        MGPT_CUDA(cudaStreamWaitEvent(cs, L->copy_ev[2], 0));
+        MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, cs));
+        MGPT_CUDA(cudaEventRecord(L->copy_ev[3], cs));
+        MGPT_CUDA(cudaStreamWaitEvent(st, L->copy_ev[1], 0));       // backward needs dy
         MGPT_TRY(mgpt_moe_backward(L, L->h_x, L->h_dy, L->h_dx, io, L->h_ws, L->h_ws_bytes, stream));
         MGPT_CUDA(cudaMemcpyAsync(dx_host, L->h_dx, io_bytes, cudaMemcpyDeviceToHost, st));
+        MGPT_CUDA(cudaStreamWaitEvent(st, L->copy_ev[3], 0));       // the caller's stream also covers the y copy
+    } else {
+        MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, st));
     }
     MGPT_CUDA(cudaStreamSynchronize(st));
     return 0;

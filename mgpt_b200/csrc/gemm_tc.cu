@@ -296,6 +296,16 @@ __device__ __forceinline__ void pack32(const float (&a)[32], uint32_t (&out)[16]
         out[i] = *reinterpret_cast<uint32_t*>(&h);
     }
 }
+// 32 bf16 of this thread's row as 16 packed words (zero beyond `valid` columns); stays packed to save registers
+__device__ __forceinline__ void load_packed32(const bf16* src, uint32_t (&w)[16], int valid)
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 u = make_uint4(0, 0, 0, 0);
+        if (q * 8 < valid) u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+        w[4 * q] = u.x; w[4 * q + 1] = u.y; w[4 * q + 2] = u.z; w[4 * q + 3] = u.w;
+    }
+}
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
@@ -413,17 +423,14 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
             const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
             const int row_w = row_tile * BM + q * 32;           // first row of this warp
+            // MODE_DHH: the saved G and U of this item come from HBM.  Unit 0's pieces are requested before the wait
+            // for the accumulator, unit 1's while unit 0 is worked on, so their latency hides behind other work.
+            uint32_t gq[2][16], uq[2][16];
             if (MODE == MODE_DHH) {
-                // G and U of this item come from HBM: start pulling this thread's two 128-byte rows into L2
-                // while the tensor core is still working on the item
                 const int n = n0 + h * 64;
-                if (n < p.n_out) {
-                    const size_t o = (size_t)(row_w + lane) * p.n_out + n;
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.G + o));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.G + o + 32));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.U + o));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.U + o + 32));
-                }
+                const size_t o = (size_t)(row_w + lane) * p.n_out + n;
+                load_packed32(p.G + o, gq[0], p.n_out - n);
+                load_packed32(p.U + o, uq[0], p.n_out - n);
             }
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
@@ -470,23 +477,37 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     if (MODE == MODE_DOWN) {
                         add_bias32(v, p.bias0[e], n, p.n_out);
                     } else if (MODE == MODE_DHH) {
-                        // utils/Tensor.cpp:2020-2027 with dd = dHh; G, U: this thread's row, 64 B each
-                        const size_t o = (size_t)(row_w + lane) * p.n_out + n;
-                        const int valid = min(32, p.n_out - n);
-                        float g[32], u[32];
-                        uint32_t pu[16];
-                        load_bf16x32(p.G + o, g, valid);
-                        load_bf16x32(p.U + o, u, valid);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float sig = __fdividef(1.0f, 1.0f + __expf(-g[j]));
-                            const float dd = v[j];
-                            v[j] = (dd * u[j]) * (sig * (1.0f + g[j] * (1.0f - sig)));   // dG
-                            u[j] = dd * (g[j] * sig);                                     // dU
+                        // utils/Tensor.cpp:2020-2027 with dd = dHh
+                        if (un == 0) {
+                            const int n1 = n + 32;
+                            const size_t o1 = (size_t)(row_w + lane) * p.n_out + n1;
+                            load_packed32(p.G + o1, gq[1], p.n_out - n1);
+                            load_packed32(p.U + o1, uq[1], p.n_out - n1);
                         }
-                        pack32(u, pu);
-                        stage_row_bf16(stage, lane, pu);
+                        uint32_t (&gw)[16] = gq[un];
+                        uint32_t (&uw)[16] = uq[un];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float dgv[2], duv[2];
+#pragma unroll
+                            for (int hh = 0; hh < 2; ++hh) {
+                                const float g = hh ? bf_hi(gw[i]) : bf_lo(gw[i]);
+                                const float u = hh ? bf_hi(uw[i]) : bf_lo(uw[i]);
+                                const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+                                const float dd = v[2 * i + hh];
+                                dgv[hh] = (dd * u) * (sig * (1.0f + g * (1.0f - sig)));
+                                duv[hh] = dd * (g * sig);
+                            }
+                            __nv_bfloat162 a2 = __floats2bfloat162_rn(dgv[0], dgv[1]);
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(duv[0], duv[1]);
+                            gw[i] = *reinterpret_cast<uint32_t*>(&a2);      // dG, packed in place
+                            uw[i] = *reinterpret_cast<uint32_t*>(&b2);      // dU, packed in place
+                        }
+                        stage_row_bf16(stage, lane, uw);
                         flush_stage(stage, &tmD1, n, row_w, lane);
+                        stage_row_bf16(stage, lane, gw);
+                        flush_stage(stage, &tmD0, n, row_w, lane);
+                        continue;
                     } else if (MODE == MODE_DX) {
                         // dx = (sum of the token's expert rows, ascending row order) + dlogits * Wr^T
                         const int tok = row_w + lane;

@@ -79,7 +79,7 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
         padded_offsets[E] = p;
         const int nt = p / ROW_TILE;
         *n_tiles = nt;
-        if (nt > max_tiles) atomicOr(status, 1);   // cannot happen: max_tiles bounds sum(ceil)
+        *status = nt > max_tiles ? 1 : 0;          // cannot happen: max_tiles bounds sum(ceil); also clears the word
     }
     __syncthreads();
     if (e < E) {
@@ -117,6 +117,13 @@ plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
         pos[i] = p;
         row_src[p] = i;
         if (slot_of) slot_of[i] = slot;
+    }
+    // padding rows of every expert's segment carry no source (block 0, one thread per expert)
+    if (blockIdx.x == 0 && threadIdx.x < E) {
+        const int e2 = threadIdx.x;
+        const int cnt = offsets[e2 + 1 < E ? e2 + 1 : e2] - offsets[e2];      // compact count (last expert: below)
+        const int real = e2 + 1 < E ? cnt : R - offsets[e2];
+        for (int q = padded_offsets[e2] + real; q < padded_offsets[e2 + 1]; ++q) row_src[q] = -1;
     }
 }
 
@@ -325,8 +332,7 @@ int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* off
              int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of)
 {
     const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
-    MGPT_CUDA(cudaMemsetAsync(row_src, 0xFF, (size_t)row_cap * sizeof(int32_t), st));
-    MGPT_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+    (void)row_cap;      // rows beyond the plan's tiles are never read; padding rows are marked by plan_assign_kernel
     plan_count_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
     MGPT_LAUNCHED("plan_count_kernel");
     plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, plan_blocks, E, counts, offsets, padded_offsets, tile_expert,

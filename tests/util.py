@@ -115,4 +115,6 @@ def assert_plan_equal(bufs: dict, ref: dict, n_rows: int) -> None:
             got = got[:nt]
         elif key in ("map", "pos"):
             got = got[:n_rows]
+        elif key == "row_src":            # defined for the rows of the plan's tiles; beyond them nothing is written
+            got, want = got[:nt * 128], want[:nt * 128]
         assert np.array_equal(got, want), key
