@@ -109,7 +109,10 @@ int  mgpt_moe_expert_counts(mgpt_moe_layer* layer, int32_t* host_counts);
 /* Offset and size of a named buffer inside the workspace for n_tokens, for
  * tests and for callers that read routing results in place. Names:
  * logits probs top_idx top_p counts offsets padded_offsets map pos row_src
- * tile_expert n_tiles Xg G U Hh Yg dYg dG dU dXg d_top_p dlogits status. */
+ * tile_expert n_tiles Xg G U Hh Yg dYg dG dU dXg d_top_p dlogits status.
+ * Activation buffers are row-major [padded rows, width], except G and U on
+ * the tensor-core path (mode BF16, gemm_impl 0), which only its own epilogues
+ * read: [row tile][8-column chunk][128 rows][8 values]. */
 int  mgpt_moe_workspace_view(const mgpt_moe_layer* layer, int n_tokens, const char* name,
                              size_t* offset, size_t* bytes);
 

@@ -296,15 +296,29 @@ __device__ __forceinline__ void pack32(const float (&a)[32], uint32_t (&out)[16]
         out[i] = *reinterpret_cast<uint32_t*>(&h);
     }
 }
-// 32 bf16 of this thread's row as 16 packed words (zero beyond `valid` columns); stays packed to save registers
-__device__ __forceinline__ void load_packed32(const bf16* src, uint32_t (&w)[16], int valid)
+// The saved pre-activations G and U are private to the gate/up and dHh epilogues, so they are kept in the layout
+// both epilogues touch with full-width accesses: [row tile][8-column chunk][128 rows][8 bf16].  A thread owns one
+// row (its TMEM lane); the 32 lanes of a warp then read or write 512 contiguous bytes per instruction.
+// `chunk0` points at this thread's row in the first chunk of its 32 columns; `valid` = columns left in the tensor.
+__device__ __forceinline__ void load_blocked32(const uint4* chunk0, uint32_t (&w)[16], int valid)
 {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         uint4 u = make_uint4(0, 0, 0, 0);
-        if (q * 8 < valid) u = __ldg(reinterpret_cast<const uint4*>(src) + q);
+        if (q * 8 < valid) u = __ldg(chunk0 + q * BM);
         w[4 * q] = u.x; w[4 * q + 1] = u.y; w[4 * q + 2] = u.z; w[4 * q + 3] = u.w;
     }
+}
+__device__ __forceinline__ void store_blocked32(uint4* chunk0, const uint32_t (&w)[16], int valid)
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        if (q * 8 < valid) chunk0[q * BM] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+}
+// this thread's row in chunk n/8 of row tile `row_tile` (n_out columns, a multiple of 8)
+__device__ __forceinline__ size_t blocked_index(int row_tile, int n_out, int n, int row_in_tile)
+{
+    return ((size_t)row_tile * (n_out >> 3) + (n >> 3)) * BM + row_in_tile;
 }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
@@ -321,7 +335,7 @@ struct RowsP {
     int n_out;              // output columns (H or C)
     int n_col_tiles;        // column tiles per row tile
     int b_rows_per_expert;  // rows of one expert in the B tensor map (= n_out)
-    const bf16 *G, *U;      // saved pre-activations (MODE_DHH), row stride n_out
+    bf16 *G, *U;            // saved pre-activations in the blocked layout (written by MODE_GATEUP, read by MODE_DHH)
     const float* const* bias0;
     const float* const* bias1;
     // MODE_DX only: row tiles are token tiles (no experts); the epilogue adds the expert rows of each token
@@ -428,9 +442,9 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             uint32_t gq[2][16], uq[2][16];
             if (MODE == MODE_DHH) {
                 const int n = n0 + h * 64;
-                const size_t o = (size_t)(row_w + lane) * p.n_out + n;
-                load_packed32(p.G + o, gq[0], p.n_out - n);
-                load_packed32(p.U + o, uq[0], p.n_out - n);
+                const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
+                load_blocked32(reinterpret_cast<const uint4*>(p.G) + o, gq[0], p.n_out - n);
+                load_blocked32(reinterpret_cast<const uint4*>(p.U) + o, uq[0], p.n_out - n);
             }
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
@@ -449,10 +463,9 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     add_bias32(b, p.bias1[e], n, p.n_out);
                     pack32(a, gp);
                     pack32(b, up);
-                    stage_row_bf16(stage, lane, gp);
-                    flush_stage(stage, &tmD0, n, row_w, lane);
-                    stage_row_bf16(stage, lane, up);
-                    flush_stage(stage, &tmD1, n, row_w, lane);
+                    const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
+                    store_blocked32(reinterpret_cast<uint4*>(p.G) + o, gp, p.n_out - n);
+                    store_blocked32(reinterpret_cast<uint4*>(p.U) + o, up, p.n_out - n);
                     // Hh from the rounded G and U (backward reads the stored values)
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -480,9 +493,9 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         // utils/Tensor.cpp:2020-2027 with dd = dHh
                         if (un == 0) {
                             const int n1 = n + 32;
-                            const size_t o1 = (size_t)(row_w + lane) * p.n_out + n1;
-                            load_packed32(p.G + o1, gq[1], p.n_out - n1);
-                            load_packed32(p.U + o1, uq[1], p.n_out - n1);
+                            const size_t o1 = blocked_index(row_tile, p.n_out, n1, q * 32 + lane);
+                            load_blocked32(reinterpret_cast<const uint4*>(p.G) + o1, gq[1], p.n_out - n1);
+                            load_blocked32(reinterpret_cast<const uint4*>(p.U) + o1, uq[1], p.n_out - n1);
                         }
                         uint32_t (&gw)[16] = gq[un];
                         uint32_t (&uw)[16] = uq[un];
@@ -771,7 +784,7 @@ struct TcState {
     // reduction-over-rows operand loads (box 64 x 64 rows)
     CUtensorMap Xg_t, Hh_t, dYg_t, dG_t, dU_t;
     // epilogue stores (box 32 x 32 rows, 64-byte swizzle)
-    CUtensorMap G_s, U_s, Hh_s, Yg_s, dG_s, dU_s, dXg_s;
+    CUtensorMap Hh_s, Yg_s, dG_s, dU_s, dXg_s;
 };
 
 int prepare_attrs(mgpt_moe_layer* L);
@@ -800,8 +813,6 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->dYg_t, dyg, rc, C, 64));
     MGPT_TRY(make_map(&s->dG_t, ws + w.dG, rc, H, 64));
     MGPT_TRY(make_map(&s->dU_t, ws + w.dU, rc, H, 64));
-    MGPT_TRY(make_map(&s->G_s, ws + w.G, rc, H, 32));
-    MGPT_TRY(make_map(&s->U_s, ws + w.U, rc, H, 32));
     MGPT_TRY(make_map(&s->Hh_s, ws + w.Hh, rc, H, 32));
     MGPT_TRY(make_map(&s->Yg_s, yg, rc, C, 32));
     MGPT_TRY(make_map(&s->dG_s, ws + w.dG, rc, H, 32));
@@ -848,9 +859,10 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     // gate/up + SwiGLU: K = C, 128 hidden units per item
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN / 2);
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
+    p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
     L->stage_begin(ST_GATEUP, st);
     tc_rows_kernel<MODE_GATEUP><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->Xg, s->Xg, s->WgT, s->WuT, s->G_s, s->U_s, s->Hh_s, p);
+        s->Xg, s->Xg, s->WgT, s->WuT, s->Hh_s, s->Hh_s, s->Hh_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<gateup>");
     L->stage_end(ST_GATEUP, st);
     // down: K = H
@@ -876,7 +888,7 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     p.status = (int32_t*)(ws + w.status);
     // dHh = dYg * Wd^T  (K = C), SwiGLU backward in the epilogue
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN);
-    p.G = (const bf16*)(ws + w.G); p.U = (const bf16*)(ws + w.U);
+    p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
     L->stage_begin(ST_DHH, st);
     tc_rows_kernel<MODE_DHH><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         s->dYg, s->dYg, s->Wd, s->Wd, s->dG_s, s->dU_s, s->dU_s, p);

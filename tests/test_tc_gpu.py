@@ -19,13 +19,20 @@ def _bf16_inputs(w, x, params, dy):
     return synth.bf16_round(x), [synth.bf16_round(p) for p in params], synth.bf16_round(dy)
 
 
-def _buffers(got, w):
+def _buffers(got, w, blocked_gu=False):
+    """Activation buffers as [rows, width].  The tcgen05 path keeps G and U as
+    [row tile][8-column chunk][128 rows][8] (include/mgpt_moe.h); ``blocked_gu`` undoes that."""
     layer = got["layer"]
     rows = int(got["padded_offsets"][-1])
     out = {}
     for name in ACT:
         width = w.C if name in ("Xg", "Yg", "dYg", "dXg") else w.H
-        out[name] = layer.workspace_view(name, torch.bfloat16).view(-1, width)[:rows].float().cpu().numpy()
+        t = layer.workspace_view(name, torch.bfloat16)
+        if blocked_gu and name in ("G", "U"):
+            t = t.view(-1, width // 8, 128, 8).permute(0, 2, 1, 3).reshape(-1, width)
+        else:
+            t = t.view(-1, width)
+        out[name] = t[:rows].float().cpu().numpy()
     return out
 
 
@@ -57,7 +64,7 @@ def test_tc_against_simt_and_oracle(shape, io):
     assert tc["status"] == 0
     simt = run_layer(w, x, params, dy, mode="bf16", gemm_impl=1, io=io)
     assert_routing_exact(tc, ref)
-    a, b = _buffers(tc, w), _buffers(simt, w)
+    a, b = _buffers(tc, w, blocked_gu=True), _buffers(simt, w)
     for name in ACT:
         assert rel_l2(a[name], b[name]) < 6e-3, (name, rel_l2(a[name], b[name]))
     for i, (ga, gb) in enumerate(zip(tc["grads"], simt["grads"])):
