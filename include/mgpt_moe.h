@@ -136,6 +136,12 @@ int  mgpt_moe_set_profiling(mgpt_moe_layer* layer, int enabled);
 int  mgpt_moe_stage_ms(mgpt_moe_layer* layer, float* ms);
 const char* mgpt_moe_stage_name(int stage);
 
+/* Upper bound on the CTAs of the persistent tensor-core kernels of this layer
+ * (one CTA per SM; 0 = every SM, the default). A caller that overlaps these
+ * kernels with communication kernels on another stream leaves SMs free for
+ * them this way; results do not depend on the value. No reference counterpart. */
+int  mgpt_moe_set_sm_budget(mgpt_moe_layer* layer, int n_sms);
+
 /* Number of kernels the library launched since the counter was last reset
  * (host-side count of its own launches; for benchmark bookkeeping). */
 long mgpt_moe_launch_count(int reset);

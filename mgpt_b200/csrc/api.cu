@@ -450,6 +450,14 @@ const char* mgpt_moe_stage_name(int stage)
     return (stage >= 0 && stage < ST_COUNT) ? kStageNames[stage] : "";
 }
 
+int mgpt_moe_set_sm_budget(mgpt_moe_layer* L, int n_sms)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (n_sms < 0) return fail(MGPT_MOE_EINVAL, "n_sms must be >= 0 (0 = every SM)");
+    L->sm_budget = n_sms;
+    return 0;
+}
+
 int mgpt_moe_set_profiling(mgpt_moe_layer* L, int enabled)
 {
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");

@@ -123,6 +123,7 @@ struct mgpt_moe_layer {
 
     // TMA descriptors (opaque, built per workspace pointer)
     void* tc_state = nullptr;
+    int sm_budget = 0;                       // > 0: persistent kernels launch at most this many CTAs
 
     // expert side of an expert-parallel layer: row buffers owned by the caller (the exchange buffers) and the
     // number of row segments per expert (one per source rank); 0 = one contiguous padded range per expert

@@ -38,11 +38,12 @@ constexpr uint32_t HALF_B = B_BYTES / 2;
 constexpr int EPI_WARPS = 16;                        // four per TMEM lane quarter
 constexpr uint32_t STAGING_BYTES = 2048;             // per epilogue warp: 32 rows x 64 B
 constexpr uint32_t TMEM_COLS = 2 * BN;               // two accumulators
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024 /*align slack*/ + 512 /*barriers, work queue*/;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-17 epilogue
 
-enum { ERR_FULL_WAIT = 2, ERR_EMPTY_WAIT = 4, ERR_ACC_WAIT = 8 };
+enum { ERR_FULL_WAIT = 2, ERR_EMPTY_WAIT = 4, ERR_ACC_WAIT = 8, ERR_SCHED_WAIT = 16 };
+constexpr int SCHED_Q = 8;                           // queue entries: the producer runs up to ~4 items ahead of the slowest epilogue warp
 
 // ---- PTX wrappers ------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -205,6 +206,10 @@ struct Pipe {
     __device__ __forceinline__ uint32_t empty(int s) const { return bars + 8u * (STAGES + s); }
     __device__ __forceinline__ uint32_t acc_full(int b) const { return bars + 8u * (2 * STAGES + b); }
     __device__ __forceinline__ uint32_t acc_empty(int b) const { return bars + 8u * (2 * STAGES + 2 + b); }
+    // work-item queue: slot i is full once the producer has written item(i), empty once every consumer has read it
+    __device__ __forceinline__ uint32_t sched_full(int i) const { return bars + 8u * (2 * STAGES + 5 + i); }
+    __device__ __forceinline__ uint32_t sched_empty(int i) const { return bars + 8u * (2 * STAGES + 5 + SCHED_Q + i); }
+    __device__ __forceinline__ uint32_t sched_item(int i) const { return bars + 8u * (2 * STAGES + 5 + 2 * SCHED_Q) + 4u * i; }
 };
 
 __device__ __forceinline__ Pipe carve(uint8_t* raw)
@@ -233,6 +238,11 @@ __device__ __forceinline__ uint32_t cta_setup(const Pipe& pipe, int warp)
             mbar_init(pipe.acc_full(b), 1);
             mbar_init(pipe.acc_empty(b), EPI_WARPS);
         }
+#pragma unroll
+        for (int i = 0; i < SCHED_Q; ++i) {
+            mbar_init(pipe.sched_full(i), 1);
+            mbar_init(pipe.sched_empty(i), 1 + EPI_WARPS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(pipe.tmem_slot, TMEM_COLS);
@@ -251,6 +261,46 @@ __device__ __forceinline__ void cta_teardown(uint32_t tmem_base, int warp)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- work distribution ---------------------------------------------------------
+// Items are handed out by a device-wide counter instead of a fixed stride, so a CTA that starts late (its SM
+// was busy with another stream's kernel) or meets longer items simply takes fewer of them.  The producer thread
+// fetches the CTA's n-th item and passes it to the MMA thread and the epilogue warps through a small queue in
+// shared memory.  counter[0] = next item, counter[1] = CTAs that have finished; the last CTA to finish clears
+// both, so the pair is ready for the next launch on the stream without a memset.
+// The value returned by the counter is first looked at in sched_publish (item >= total: no work left, published
+// as -1 so that the other roles stop at this entry too); between request and use lie an item's loads.
+__device__ __forceinline__ int sched_fetch(int32_t* counter) { return atomicAdd(counter, 1); }
+// Hands the CTA's n-th item to the other roles.  False: the wait for a free queue slot ran out.
+__device__ __forceinline__ bool sched_publish(const Pipe& pipe, uint32_t n, int& item, int total, int32_t* status)
+{
+    const int slot = n % SCHED_Q;
+    if (item >= total) item = -1;
+    if (n >= SCHED_Q && !mbar_wait(pipe.sched_empty(slot), ((n / SCHED_Q) - 1) & 1, status, ERR_SCHED_WAIT)) return false;
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(pipe.sched_item(slot)), "r"(item) : "memory");
+    mbar_arrive(pipe.sched_full(slot));
+    return true;
+}
+// The caller reads with every thread that needs the item, then one thread per consumer calls sched_release.
+__device__ __forceinline__ int sched_consume(const Pipe& pipe, uint32_t n, int32_t* status)
+{
+    const int slot = n % SCHED_Q;
+    if (!mbar_wait(pipe.sched_full(slot), (n / SCHED_Q) & 1, status, ERR_SCHED_WAIT)) return -1;
+    int item;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(item) : "r"(pipe.sched_item(slot)) : "memory");
+    return item;
+}
+__device__ __forceinline__ void sched_release(const Pipe& pipe, uint32_t n) { mbar_arrive(pipe.sched_empty(n % SCHED_Q)); }
+// Thread 0 of every CTA of the grid, after its last fetch (also CTAs that leave without fetching).
+__device__ __forceinline__ void sched_finish(int32_t* counter)
+{
+    __threadfence();
+    if (atomicAdd(counter + 1, 1) == (int)gridDim.x - 1) {
+        counter[0] = 0;
+        counter[1] = 0;
+        __threadfence();
     }
 }
 
@@ -331,6 +381,7 @@ struct RowsP {
     const int32_t* tile_order;  // optional: i-th row tile to work on (expert-major order over scattered tiles)
     const int32_t* n_tiles;
     int32_t* status;
+    int32_t* sched;         // {next item, finished CTAs}, both zero between launches
     int kblocks;            // k-blocks (of 64) per operand pair
     int n_out;              // output columns (H or C)
     int n_col_tiles;        // column tiles per row tile
@@ -358,7 +409,10 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 {
     extern __shared__ uint8_t smem_raw[];
     const int total_items = (MODE == MODE_DX ? p.fixed_tiles : *p.n_tiles) * p.n_col_tiles;
-    if ((int)blockIdx.x >= total_items) return;          // whole CTA leaves before any barrier or TMEM use
+    if ((int)blockIdx.x >= total_items) {                // whole CTA leaves before any barrier or TMEM use
+        if (threadIdx.x == 0) sched_finish(p.sched);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int COLS_PER_ITEM = MODE == MODE_GATEUP ? BN / 2 : BN;
     const int kb_per_item = (MODE == MODE_DXG ? 2 : 1) * p.kblocks;
@@ -370,11 +424,18 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            int item = sched_fetch(p.sched);
+            ok = sched_publish(pipe, 0, item, total_items, p.status);
+            for (uint32_t nf = 1; ok && item >= 0; ++nf) {
+                // the next item is requested now and handed on after this item's loads are under way,
+                // so the round trip to the counter stays off the critical path
+                int next = sched_fetch(p.sched);
                 const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
                 const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
                 const int brow = (MODE == MODE_DX ? 0 : p.tile_expert[row_tile] * p.b_rows_per_expert) + n0;
                 const int row0 = row_tile * BM;
+                // a last column tile with at most 128 valid columns takes half of B and a 128-wide MMA
+                const bool narrow = MODE != MODE_GATEUP && p.n_out - n0 <= BN / 2;
                 for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
@@ -382,7 +443,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         break;
                     }
                     const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                    mbar_expect_tx(pipe.full(s), STAGE_BYTES);
+                    mbar_expect_tx(pipe.full(s), narrow ? A_BYTES + HALF_B : STAGE_BYTES);
                     const bool second = MODE == MODE_DXG && kb >= p.kblocks;
                     const int kx = (second ? kb - p.kblocks : kb) * BK;
                     tma_load_2d(a_dst, second ? &tmA1 : &tmA0, kx, row0, pipe.full(s));
@@ -392,17 +453,24 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     } else {
                         const CUtensorMap* mb = second ? &tmB1 : &tmB0;
                         tma_load_2d(b_dst, mb, kx, brow, pipe.full(s));
-                        tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
+                        if (!narrow) tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
                     }
                 }
+                if (ok) ok = sched_publish(pipe, nf, next, total_items, p.status);
+                item = next;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0);
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++t) {
+            for (; ok; ++t) {
+                const int item = sched_consume(pipe, t, p.status);
+                if (item >= 0) sched_release(pipe, t);
+                if (item < 0) break;
+                const int n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
+                const bool narrow = MODE != MODE_GATEUP && p.n_out - n0 <= BN / 2;
+                const uint32_t idesc = narrow ? make_idesc(BM, BN / 2, 0, 0) : make_idesc(BM, BN, 0, 0);
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
@@ -431,10 +499,13 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const int q = warp & 3, h = (warp - 2) >> 2;
         uint8_t* stage = pipe.staging + (warp - 2) * STAGING_BYTES;
         uint32_t t = 0;
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++t) {
+        for (;; ++t) {
+            const int item = __shfl_sync(0xffffffffu, sched_consume(pipe, t, p.status), 0);   // warp-uniform
+            if (item < 0) break;
+            if (lane == 0) sched_release(pipe, t);
             const uint32_t buf = t & 1u;
             const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
-                const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
+            const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
             const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
             const int row_w = row_tile * BM + q * 32;           // first row of this warp
             // MODE_DHH: the saved G and U of this item come from HBM.  Unit 0's pieces are requested before the wait
@@ -559,6 +630,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores landed before exit
     }
     cta_teardown(tmem_base, warp);
+    if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 // ---- weight gradients: grad[e][M,N] += A_e^T * B_e over the expert's rows ---------
@@ -576,6 +648,7 @@ struct WgradP {
     const int32_t* seg;     // [E][n_seg][2] {first row, rows}: an expert's rows in n_seg segments (0 = one padded range)
     int n_seg;
     int32_t* status;
+    int32_t* sched;         // {next item, finished CTAs}, both zero between launches
     WgradProb prob[3];
     int n_probs, total_items;
 };
@@ -615,7 +688,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_items = p.total_items;
-    if ((int)blockIdx.x >= total_items) return;
+    if ((int)blockIdx.x >= total_items) {
+        if (threadIdx.x == 0) sched_finish(p.sched);
+        return;
+    }
 
     const Pipe pipe = carve(smem_raw);
     const uint32_t tmem_base = cta_setup(pipe, warp);
@@ -625,8 +701,12 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            int item = sched_fetch(p.sched);
+            ok = sched_publish(pipe, 0, item, total_items, p.status);
+            for (uint32_t nf = 1; ok && item >= 0; ++nf) {
+                int next = sched_fetch(p.sched);      // handed on after this item's loads
                 const WgradItem w = wgrad_item(p, item);
+                const int nb = (min(BN, p.prob[w.pr].N - w.n0) + 63) / 64;   // 64-column boxes of B with valid columns
                 const CUtensorMap* mA = w.pr == 0 ? &tmA0 : w.pr == 1 ? &tmA1 : &tmA2;
                 const CUtensorMap* mB = w.pr == 0 ? &tmB0 : w.pr == 1 ? &tmB1 : &tmB2;
                 const bool segmented = p.n_seg > 0 && !p.prob[w.pr].uniform_rows;
@@ -641,24 +721,31 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                             break;
                         }
                         const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                        mbar_expect_tx(pipe.full(s), STAGE_BYTES);
+                        mbar_expect_tx(pipe.full(s), A_BYTES + nb * BOX);
                         const int row = seg_r0 + kb * BK;
 #pragma unroll
                         for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
 #pragma unroll
-                        for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
+                        for (int i = 0; i < BN / 64; ++i)
+                            if (i < nb) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
                     }
                 }
+                if (ok) ok = sched_publish(pipe, nf, next, total_items, p.status);
+                item = next;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            for (uint32_t nf = 0; ok; ++nf) {
+                const int item = sched_consume(pipe, nf, p.status);
+                if (item < 0) break;
+                sched_release(pipe, nf);
                 const WgradItem w = wgrad_item(p, item);
                 if (w.nkb <= 0) continue;
+                // a last column tile is as wide as its valid 64-column boxes
+                const uint32_t idesc = make_idesc(BM, 64 * ((min(BN, p.prob[w.pr].N - w.n0) + 63) / 64), 1, 1);
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
@@ -688,7 +775,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         const int q = warp & 3, h = (warp - 2) >> 2;
         float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32 rows][16 floats]
         uint32_t t = 0;
-        for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        for (uint32_t nf = 0;; ++nf) {
+            const int item = __shfl_sync(0xffffffffu, sched_consume(pipe, nf, p.status), 0);  // warp-uniform
+            if (item < 0) break;
+            if (lane == 0) sched_release(pipe, nf);
             const WgradItem w = wgrad_item(p, item);
             if (w.nkb <= 0) continue;
             const WgradProb& pb = p.prob[w.pr];
@@ -734,6 +824,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         }
     }
     cta_teardown(tmem_base, warp);
+    if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------
@@ -779,6 +870,7 @@ struct TcState {
     int n_tokens = -1;
     bool attr_set = false;
     int sms = 0;
+    int32_t* sched = nullptr;    // device: one {next item, finished CTAs} pair per kind of launch, zero between launches
     // K-major operand loads (box 64 x 128 rows)
     CUtensorMap Xg, Hh, dYg, dG, dU, WgT, WuT, WdT, Wg, Wu, Wd;
     // reduction-over-rows operand loads (box 64 x 64 rows)
@@ -836,6 +928,8 @@ int prepare_attrs(mgpt_moe_layer* L)
         MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
+        MGPT_CUDA(cudaMalloc(&s->sched, 64 * sizeof(int32_t)));
+        MGPT_CUDA(cudaMemset(s->sched, 0, 64 * sizeof(int32_t)));
         s->attr_set = true;
     }
     return 0;
@@ -843,6 +937,8 @@ int prepare_attrs(mgpt_moe_layer* L)
 
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 int imin(int a, int b) { return a < b ? a : b; }
+// persistent CTAs to launch: every SM, or the caller's budget when other kernels must stay resident beside these
+int grid_sms(const mgpt_moe_layer* L, const TcState* s) { return L->sm_budget > 0 ? imin(L->sm_budget, s->sms) : s->sms; }
 
 }  // namespace
 
@@ -861,7 +957,8 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
     p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
     L->stage_begin(ST_GATEUP, st);
-    tc_rows_kernel<MODE_GATEUP><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+    p.sched = s->sched + 0;
+    tc_rows_kernel<MODE_GATEUP><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         s->Xg, s->Xg, s->WgT, s->WuT, s->Hh_s, s->Hh_s, s->Hh_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<gateup>");
     L->stage_end(ST_GATEUP, st);
@@ -869,7 +966,8 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
     p.bias0 = L->master.bd; p.bias1 = nullptr;
     L->stage_begin(ST_DOWN, st);
-    tc_rows_kernel<MODE_DOWN><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+    p.sched = s->sched + 2;
+    tc_rows_kernel<MODE_DOWN><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         s->Hh, s->Hh, s->WdT, s->WdT, s->Yg_s, s->Yg_s, s->Yg_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<down>");
     L->stage_end(ST_DOWN, st);
@@ -890,14 +988,16 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN);
     p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
     L->stage_begin(ST_DHH, st);
-    tc_rows_kernel<MODE_DHH><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+    p.sched = s->sched + 4;
+    tc_rows_kernel<MODE_DHH><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         s->dYg, s->dYg, s->Wd, s->Wd, s->dG_s, s->dU_s, s->dU_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<dhh>");
     L->stage_end(ST_DHH, st);
     // dXg = dG * Wg^T + dU * Wu^T  (K = 2H)
     p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
     L->stage_begin(ST_DXG, st);
-    tc_rows_kernel<MODE_DXG><<<imin(s->sms, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+    p.sched = s->sched + 6;
+    tc_rows_kernel<MODE_DXG><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         s->dG, s->dU, s->Wg, s->Wu, s->dXg_s, s->dXg_s, s->dXg_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<dxg>");
     L->stage_end(ST_DXG, st);
@@ -926,7 +1026,8 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     }
     g.total_items = items;
     L->stage_begin(ST_WGRAD, st);
-    tc_wgrad_kernel<<<imin(s->sms, items), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, s->Xg_t, s->dU_t, s->Hh_t,
+    g.sched = s->sched + 8;
+    tc_wgrad_kernel<<<imin(grid_sms(L, s), items), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, s->Xg_t, s->dU_t, s->Hh_t,
                                                                        s->dYg_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel");
     L->stage_end(ST_WGRAD, st);
@@ -953,7 +1054,8 @@ int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dX
     p.kblocks = cdiv(E8, BK); p.n_out = d.C; p.b_rows_per_expert = 0; p.n_col_tiles = cdiv(d.C, BN);
     p.fixed_tiles = cdiv(w.n_tokens, BM); p.n_valid_rows = w.n_tokens;
     p.gather_src = (const bf16*)dXg; p.gather_pos = pos; p.gather_k = d.k;
-    tc_rows_kernel<MODE_DX><<<imin(s->sms, p.fixed_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
+    p.sched = s->sched + 10;
+    tc_rows_kernel<MODE_DX><<<imin(grid_sms(L, s), p.fixed_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
         mA, mA, mB, mB, mD, mD, mD, p);
     MGPT_LAUNCHED("tc_rows_kernel<dx>");
     return 0;
@@ -980,14 +1082,17 @@ int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void*
     chunks = cdiv(w.n_tokens, rows);
     q.n_groups = chunks; q.uniform_rows = rows; q.single_grad = L->p_grad[0]; q.item_begin = 0;
     g.total_items = chunks * per_chunk;
-    tc_wgrad_kernel<<<imin(s->sms, g.total_items), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, mA, mB, mA, mB, g);
+    g.sched = s->sched + 12;
+    tc_wgrad_kernel<<<imin(grid_sms(L, s), g.total_items), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, mA, mB, mA, mB, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wr>");
     return 0;
 }
 
 void tc_destroy(mgpt_moe_layer* L)
 {
-    delete (TcState*)L->tc_state;
+    TcState* s = (TcState*)L->tc_state;
+    if (s && s->sched) cudaFree(s->sched);
+    delete s;
     L->tc_state = nullptr;
 }
 

@@ -1,12 +1,17 @@
 """Expert-parallel MoE layer: tokens stay on their GPU, experts are sharded.
 
-One process per GPU.  Rank ``g`` of ``G`` owns experts ``[g*E/G, (g+1)*E/G)`` (weights,
-gradients) and a replica of the router.  Per step:
+One process per GPU.  Every rank owns ``E/G`` experts (weights, gradients) and a replica
+of the router.  Per step:
 
     route (local)  ->  counts all-to-all  ->  rows all-to-all  ->  experts (local)
                    ->  rows all-to-all back  ->  combine (local)
 
-and the mirror image for backward.  Rows travel tile-aligned: expert-major with every
+and the mirror image for backward.  With ``n_chunks > 1`` the experts are split into that
+many groups and the exchange of one group's rows runs while the previous group is being
+computed: expert ``e`` belongs to chunk ``c = e // (E/n_chunks)`` and, inside the chunk,
+to rank ``(e % (E/n_chunks)) // (E/(G*n_chunks))``, so that in the expert-major row order
+every chunk is one contiguous range made of one contiguous block per destination rank
+(``n_chunks = 1``: rank ``g`` owns experts ``[g*E/G, (g+1)*E/G)``).  Rows travel tile-aligned: expert-major with every
 expert's segment padded by zero rows to a multiple of 128, the layout the single-GPU
 layer uses internally.  The block for each destination is then one contiguous range and
 what arrives (one block per source rank, inside it one padded segment per local expert)
@@ -29,19 +34,27 @@ import torch.distributed as dist
 class CudaStages:
     """The six stage-level entry points of libmgpt_moe.so on torch CUDA tensors."""
 
-    def __init__(self, C, H, E, k, E_local, *, mode="bf16", device=0, lb_alpha=0.01):
+    def __init__(self, C, H, E, k, E_local, *, mode="bf16", device=0, lb_alpha=0.01, n_chunks=1, sm_budget=0):
         from . import _lib
         self._lib_mod = _lib
         self.lib = _lib.load()
+        if E_local % n_chunks:
+            raise ValueError(f"{E_local} local experts do not split into {n_chunks} chunks")
         self.C, self.H, self.E, self.k, self.E_local = C, H, E, k, E_local
+        self.n_chunks, self.E_chunk = n_chunks, E_local // n_chunks
         self.device = torch.device("cuda", device)
         self.act_dtype = torch.bfloat16 if mode == "bf16" else torch.float32
         m = {"fp32": _lib.FP32, "bf16": _lib.BF16}[mode]
-        self.home, self.local = ct.c_void_p(), ct.c_void_p()
+        self.home = ct.c_void_p()
         cfg = _lib.Config(C, H, E, k, lb_alpha, m, device, 0)
         _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(self.home)))
-        cfg = _lib.Config(C, H, E_local, 1, lb_alpha, m, device, 0)
-        _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(self.local)))
+        self.locals = []                 # one expert-side layer per chunk, each with E_chunk experts
+        for _ in range(n_chunks):
+            h = ct.c_void_p()
+            cfg = _lib.Config(C, H, self.E_chunk, 1, lb_alpha, m, device, 0)
+            _lib.check(self.lib.mgpt_moe_create(ct.byref(cfg), ct.byref(h)))
+            _lib.check(self.lib.mgpt_moe_set_sm_budget(h, sm_budget))
+            self.locals.append(h)
         f32 = dict(dtype=torch.float32, device=self.device)
         self.router_params = [torch.zeros(C, E, **f32), torch.zeros(1, E, **f32)]
         self.expert_params = []
@@ -51,14 +64,17 @@ class CudaStages:
         for p in self.router_params + self.expert_params:
             p.grad = torch.zeros_like(p)
         self._bind()
-        self._home_ws = self._local_ws = None
-        self._n = self._rows = 0
+        self._home_ws = None
+        self._local_ws = [None] * n_chunks
+        self._rows = [None] * n_chunks
+        self._seg_counts = [None] * n_chunks
+        self._n = 0
 
     def close(self):
-        for h in (self.home, self.local):
+        for h in [self.home] + self.locals:
             if h and h.value:
                 self.lib.mgpt_moe_destroy(h)
-        self.home, self.local = ct.c_void_p(), ct.c_void_p()
+        self.home, self.locals = ct.c_void_p(), []
 
     def __del__(self):
         try:
@@ -71,16 +87,19 @@ class CudaStages:
         rp = self.router_params
         c(self.lib.mgpt_moe_bind_params(self.home, (ct.c_void_p * 2)(*[p.data_ptr() for p in rp]),
                                         (ct.c_void_p * 2)(*[p.grad.data_ptr() for p in rp]), 2))
-        n = 2 + len(self.expert_params)
-        data = (ct.c_void_p * n)(None, None, *[p.data_ptr() for p in self.expert_params])
-        grad = (ct.c_void_p * n)(None, None, *[p.grad.data_ptr() for p in self.expert_params])
-        c(self.lib.mgpt_moe_bind_params(self.local, data, grad, n))
+        per = 6 * self.E_chunk
+        for ci, h in enumerate(self.locals):
+            mine = self.expert_params[ci * per: (ci + 1) * per]
+            n = 2 + per
+            data = (ct.c_void_p * n)(None, None, *[p.data_ptr() for p in mine])
+            grad = (ct.c_void_p * n)(None, None, *[p.grad.data_ptr() for p in mine])
+            c(self.lib.mgpt_moe_bind_params(h, data, grad, n))
         self.sync_weights()
 
     def sync_weights(self):
         c = self._lib_mod.check
-        c(self.lib.mgpt_moe_sync_weights(self.home, self._stream()))
-        c(self.lib.mgpt_moe_sync_weights(self.local, self._stream()))
+        for h in [self.home] + self.locals:
+            c(self.lib.mgpt_moe_sync_weights(h, self._stream()))
 
     @staticmethod
     def _stream():
@@ -102,12 +121,19 @@ class CudaStages:
 
     # ---- per-stage timing of the expert side (CUDA events inside the library)
     def set_profiling(self, enabled: bool) -> None:
-        self._lib_mod.check(self.lib.mgpt_moe_set_profiling(self.local, 1 if enabled else 0))
+        for h in self.locals:
+            self._lib_mod.check(self.lib.mgpt_moe_set_profiling(h, 1 if enabled else 0))
 
     def stage_ms(self) -> dict:
-        buf = (ct.c_float * self._lib_mod.N_STAGES)()
-        self._lib_mod.check(self.lib.mgpt_moe_stage_ms(self.local, buf))
-        return {self.lib.mgpt_moe_stage_name(i).decode(): float(buf[i]) for i in range(self._lib_mod.N_STAGES)}
+        """Per-stage milliseconds of the expert side, summed over the chunks."""
+        out = {}
+        for h in self.locals:
+            buf = (ct.c_float * self._lib_mod.N_STAGES)()
+            self._lib_mod.check(self.lib.mgpt_moe_stage_ms(h, buf))
+            for i in range(self._lib_mod.N_STAGES):
+                name = self.lib.mgpt_moe_stage_name(i).decode()
+                out[name] = out.get(name, 0.0) + float(buf[i])
+        return out
 
     # ---- routing side
     def route(self, x):
@@ -149,23 +175,26 @@ class CudaStages:
         return dx
 
     # ---- expert side
-    def experts_forward(self, rows, seg_counts, n_src):
-        """rows: n_src blocks of padded per-expert segments; seg_counts: int32 [n_src, E_local] real counts."""
+    def experts_forward(self, rows, seg_counts, n_src, chunk=0):
+        """rows: n_src blocks of padded per-expert segments of chunk ``chunk``;
+        seg_counts: int32 [n_src, E_chunk] real counts."""
         n = rows.shape[0]
-        self._local_ws = self._ws(self.local, n, False, self._local_ws)
+        h = self.locals[chunk]
+        self._local_ws[chunk] = self._ws(h, n, False, self._local_ws[chunk])
+        ws = self._local_ws[chunk]
         out = torch.empty_like(rows)
-        self._seg_counts = seg_counts.contiguous()
+        self._seg_counts[chunk] = seg_counts.contiguous()
         self._lib_mod.check(self.lib.mgpt_moe_experts_forward(
-            self.local, rows.data_ptr(), self._seg_counts.data_ptr(), n_src, n, out.data_ptr(),
-            self._local_ws.data_ptr(), self._local_ws.numel(), self._stream()))
-        self._rows = rows          # read again by the weight gradients
+            h, rows.data_ptr(), self._seg_counts[chunk].data_ptr(), n_src, n, out.data_ptr(),
+            ws.data_ptr(), ws.numel(), self._stream()))
+        self._rows[chunk] = rows          # read again by the weight gradients
         return out
 
-    def experts_backward(self, d_out):
+    def experts_backward(self, d_out, chunk=0):
         d_in = torch.empty_like(d_out)
+        ws = self._local_ws[chunk]
         self._lib_mod.check(self.lib.mgpt_moe_experts_backward(
-            self.local, d_out.data_ptr(), d_in.data_ptr(), self._local_ws.data_ptr(), self._local_ws.numel(),
-            self._stream()))
+            self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
         return d_in
 
 
@@ -173,7 +202,7 @@ class ExpertParallelMoE:
     """Same role as the reference's MoELayer, with the experts sharded over a process group."""
 
     def __init__(self, embed_dim, hidden_dim, num_experts, top_k, *, group=None, stages=None, mode="bf16",
-                 device=0, lb_alpha=0.01):
+                 device=0, lb_alpha=0.01, n_chunks=1, sm_budget=0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -183,9 +212,13 @@ class ExpertParallelMoE:
         self.H = 4 * embed_dim if hidden_dim == -1 else hidden_dim
         self.E, self.k = num_experts, top_k
         self.E_local = num_experts // self.world
-        self.first_expert = self.rank * self.E_local
         self.stages = stages if stages is not None else CudaStages(
-            self.C, self.H, self.E, self.k, self.E_local, mode=mode, device=device, lb_alpha=lb_alpha)
+            self.C, self.H, self.E, self.k, self.E_local, mode=mode, device=device, lb_alpha=lb_alpha,
+            n_chunks=n_chunks, sm_budget=sm_budget)
+        self.n_chunks = getattr(self.stages, "n_chunks", 1)
+        if self.E_local % self.n_chunks:
+            raise ValueError(f"{self.E_local} local experts do not split into {self.n_chunks} chunks")
+        self.E_chunk = self.E_local // self.n_chunks
         self._saved = None
         self.phase_events = None        # set to {} to record CUDA events around every phase of a step
 
@@ -207,10 +240,19 @@ class ExpertParallelMoE:
     def get_parameters(self):
         return list(self.stages.router_params) + list(self.stages.expert_params)
 
+    def global_expert(self, local_index: int, rank=None) -> int:
+        """Global id of local expert ``local_index`` (local order: chunk by chunk) of ``rank``."""
+        rank = self.rank if rank is None else rank
+        c, j = divmod(local_index, self.E_chunk)
+        return c * (self.E // self.n_chunks) + rank * self.E_chunk + j
+
     def load_parameters(self, full_params):
         """Takes the full 2+6E list (as numpy arrays or tensors) and keeps the router and this rank's experts."""
         import numpy as np
-        mine = list(full_params[:2]) + list(full_params[2 + 6 * self.first_expert: 2 + 6 * (self.first_expert + self.E_local)])
+        mine = list(full_params[:2])
+        for l in range(self.E_local):
+            e = self.global_expert(l)
+            mine += list(full_params[2 + 6 * e: 2 + 6 * (e + 1)])
         for p, a in zip(self.get_parameters(), mine):
             t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)) if not torch.is_tensor(a) else a
             p.copy_(t.reshape(p.shape))
@@ -227,59 +269,91 @@ class ExpertParallelMoE:
                 dist.all_reduce(p.grad, group=self.group)
 
     # ---- exchange helpers
-    def _all_to_all(self, send, send_splits, recv_splits):
-        recv = send.new_empty((int(sum(recv_splits)),) + tuple(send.shape[1:]))
+    def _exchange(self, recv, send, recv_splits, send_splits):
+        """Starts recv <- all-to-all(send) (rows split per rank); returns a handle to wait on, or None."""
         if self.world == 1:
             recv.copy_(send)
-        else:
-            dist.all_to_all_single(recv, send.contiguous(), list(recv_splits), list(send_splits), group=self.group)
-        return recv
+            return None
+        return dist.all_to_all_single(recv, send, list(recv_splits), list(send_splits), group=self.group, async_op=True)
 
     @staticmethod
     def _pad128(t):
         return (t + 127) // 128 * 128
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        G, El = self.world, self.E_local
+        G, nc, Ec = self.world, self.n_chunks, self.E_chunk
         if self.phase_events is not None:
             self.phase_events["order"] = []
         self._mark("start")
-        rows, counts = self.stages.route(x)                          # padded expert-major rows, counts[E]
+        rows, counts = self.stages.route(x)              # padded expert-major rows, counts[E] in (chunk, rank, j) order
         self._mark("route")
-        counts = counts.view(G, El)
-        recv_counts = torch.empty_like(counts)                       # [source rank, local expert]
+        send_counts = counts.view(nc, G, Ec).permute(1, 0, 2).contiguous()      # [destination, chunk, j]
+        recv_counts = torch.empty_like(send_counts)                            # [source, chunk, j]
         if G == 1:
-            recv_counts.copy_(counts)
+            recv_counts.copy_(send_counts)
         else:
-            dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)
-        both = torch.stack([self._pad128(counts).sum(1), self._pad128(recv_counts).sum(1)]).cpu()   # the one host sync
-        send_splits, recv_splits = both[0].tolist(), both[1].tolist()
-        n_send = int(sum(send_splits))
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        both = torch.stack([self._pad128(send_counts).sum(2).t(), self._pad128(recv_counts).sum(2).t()]).cpu()   # the one host sync
+        send_splits, recv_splits = both[0].tolist(), both[1].tolist()          # [chunk][rank] padded rows
+        starts, n_send = [], 0
+        for c in range(nc):
+            starts.append(n_send)
+            n_send += int(sum(send_splits[c]))
         self._mark("counts_exchange_and_host_sync")
-        recv_rows = self._all_to_all(rows[:n_send], send_splits, recv_splits)
-        self._mark("rows_all_to_all")
-        out_rows = self.stages.experts_forward(recv_rows, recv_counts, G)
-        self._mark("experts_forward")
-        rows_back = self._all_to_all(out_rows, recv_splits, send_splits)
+        # every chunk's exchange is started at once (they run in this order on the communication stream);
+        # chunk c is computed while chunk c+1 is still arriving and its results travel back during chunk c+1's work
+        recv_rows, pending = [], []
+        for c in range(nc):
+            r = rows.new_empty((int(sum(recv_splits[c])), self.C))
+            pending.append(self._exchange(r, rows[starts[c]: starts[c] + int(sum(send_splits[c]))],
+                                          recv_splits[c], send_splits[c]))
+            recv_rows.append(r)
+        rows_back = torch.empty_like(rows[:n_send])
+        back = []
+        for c in range(nc):
+            if pending[c] is not None:
+                pending[c].wait()
+            self._mark("rows_all_to_all")
+            out_rows = self.stages.experts_forward(recv_rows[c], recv_counts[:, c, :], G, *([c] if nc > 1 else []))
+            self._mark("experts_forward")
+            back.append(self._exchange(rows_back[starts[c]: starts[c] + int(sum(send_splits[c]))], out_rows,
+                                       send_splits[c], recv_splits[c]))
+        for wk in back:
+            if wk is not None:
+                wk.wait()
         self._mark("rows_back_all_to_all")
         y = self.stages.combine(rows_back, x)
         self._mark("combine")
-        self._saved = (x, rows_back, send_splits, recv_splits)
-        self.last_recv_counts = recv_counts
+        self._saved = (x, rows_back, send_splits, recv_splits, starts)
+        self.last_recv_counts = recv_counts.reshape(G, nc * Ec)      # [source rank, local expert]
         return y
 
     def backward(self, dy: torch.Tensor) -> torch.Tensor:
         if self._saved is None:
             raise RuntimeError("backward before forward")
-        x, rows_back, send_splits, recv_splits = self._saved
-        n_send = int(sum(send_splits))            # = every tile of the local plan
+        nc = self.n_chunks
+        x, rows_back, send_splits, recv_splits, starts = self._saved
         d_rows = self.stages.combine_backward(rows_back, dy)
         self._mark("combine_backward")
-        d_recv = self._all_to_all(d_rows[:n_send], send_splits, recv_splits)
-        self._mark("grad_rows_all_to_all")
-        d_in = self.stages.experts_backward(d_recv)
-        self._mark("experts_backward")
-        d_back = self._all_to_all(d_in, recv_splits, send_splits)
+        d_recv, pending = [], []
+        for c in range(nc):
+            r = d_rows.new_empty((int(sum(recv_splits[c])), self.C))
+            pending.append(self._exchange(r, d_rows[starts[c]: starts[c] + int(sum(send_splits[c]))],
+                                          recv_splits[c], send_splits[c]))
+            d_recv.append(r)
+        d_back = torch.empty_like(rows_back)
+        back = []
+        for c in range(nc):
+            if pending[c] is not None:
+                pending[c].wait()
+            self._mark("grad_rows_all_to_all")
+            d_in = self.stages.experts_backward(d_recv[c], *([c] if nc > 1 else []))
+            self._mark("experts_backward")
+            back.append(self._exchange(d_back[starts[c]: starts[c] + int(sum(send_splits[c]))], d_in,
+                                       send_splits[c], recv_splits[c]))
+        for wk in back:
+            if wk is not None:
+                wk.wait()
         self._mark("grad_rows_back_all_to_all")
         dx = self.stages.route_backward(x, d_back)
         self._mark("route_backward")

@@ -40,13 +40,14 @@ def run_rank(w, rank, world, make_stages, device, tol, io=torch.float32):
     assert rel_l2(dx.float().cpu().numpy(), mine["dx"]) <= tol, ("dx", rel_l2(dx.float().cpu().numpy(), mine["dx"]))
     # rows arrive ordered by (source rank, expert): the receive counts are the senders' counts
     got_counts = layer.last_recv_counts.cpu().numpy()
-    want = np.stack([refs[r]["counts"][rank * E_local:(rank + 1) * E_local] for r in range(world)])
+    mine_global = [layer.global_expert(l) for l in range(E_local)]        # local order: chunk by chunk
+    want = np.stack([refs[r]["counts"][mine_global] for r in range(world)])
     assert np.array_equal(got_counts, want)
     ps = layer.get_parameters()
     for i in range(2):      # router gradients: this shard only
         assert rel_l2(ps[i].grad.cpu().numpy(), mine["grads"][i]) <= tol, (f"router grad {i}",)
     for j in range(6 * E_local):      # expert gradients: sum over all shards
-        gi = 2 + 6 * rank * E_local + j
+        gi = 2 + 6 * mine_global[j // 6] + j % 6
         total = sum(r["grads"][gi] for r in refs)
         assert rel_l2(ps[2 + j].grad.cpu().numpy(), total) <= tol, (f"expert grad {gi}", rel_l2(ps[2 + j].grad.cpu().numpy(), total))
     return layer

@@ -14,8 +14,10 @@ def _silu(g):
 
 
 class CpuStages:
-    def __init__(self, C, H, E, k, E_local, alpha=0.01):
+    def __init__(self, C, H, E, k, E_local, alpha=0.01, n_chunks=1):
         self.C, self.H, self.E, self.k, self.E_local, self.alpha = C, H, E, k, E_local, alpha
+        self.n_chunks, self.E_chunk = n_chunks, E_local // n_chunks
+        self.saved = [None] * n_chunks
         z = lambda *s: torch.zeros(*s, dtype=torch.float32)
         self.router_params = [z(C, E), z(1, E)]
         self.expert_params = []
@@ -87,34 +89,37 @@ class CpuStages:
         return torch.from_numpy(dx + dL @ Wr.T)
 
     # ---- expert side: n_src blocks, each one padded segment per local expert
-    def experts_forward(self, rows, seg_counts, n_src):
-        X, sc = rows.numpy(), seg_counts.numpy().reshape(n_src, self.E_local)
-        index = [[] for _ in range(self.E_local)]
+    def experts_forward(self, rows, seg_counts, n_src, chunk=0):
+        Ec = self.E_chunk
+        X, sc = rows.numpy(), seg_counts.numpy().reshape(n_src, Ec)
+        index = [[] for _ in range(Ec)]
         r0 = 0
         for s in range(n_src):
-            for e in range(self.E_local):
+            for e in range(Ec):
                 c = int(sc[s, e])
                 index[e] += list(range(r0, r0 + c))
                 assert not X[r0 + c: r0 + (c + 127) // 128 * 128].any(), "padding rows must arrive as zeros"
                 r0 += (c + 127) // 128 * 128
         assert r0 == X.shape[0]
         out = np.zeros_like(X)
-        self.saved = []
-        for e in range(self.E_local):
+        saved = self.saved[chunk] = []
+        for e in range(Ec):
             idx = np.array(index[e], dtype=np.int64)
-            Wg, bg, Wu, bu, Wd, bd = [p.numpy() for p in self.expert_params[6 * e: 6 * e + 6]]
+            le = chunk * Ec + e                     # local expert
+            Wg, bg, Wu, bu, Wd, bd = [p.numpy() for p in self.expert_params[6 * le: 6 * le + 6]]
             xe = X[idx]
             G, U = xe @ Wg + bg, xe @ Wu + bu
             Hh = _silu(G) * U
             out[idx] = Hh @ Wd + bd
-            self.saved.append((idx, xe, G, U, Hh))
+            saved.append((idx, xe, G, U, Hh))
         return torch.from_numpy(out)
 
-    def experts_backward(self, d_out):
+    def experts_backward(self, d_out, chunk=0):
         D = d_out.numpy()
         d_in = np.zeros_like(D)
-        for e, (idx, xe, G, U, Hh) in enumerate(self.saved):
-            p = self.expert_params[6 * e: 6 * e + 6]
+        for e, (idx, xe, G, U, Hh) in enumerate(self.saved[chunk]):
+            le = chunk * self.E_chunk + e
+            p = self.expert_params[6 * le: 6 * le + 6]
             Wg, Wu, Wd = p[0].numpy(), p[2].numpy(), p[4].numpy()
             dy = D[idx]
             p[5].grad += torch.from_numpy(dy.sum(0, keepdims=True))

@@ -23,9 +23,9 @@ def _worker(rank, world, port, shape, q):
     try:
         torch.set_num_threads(1)
         init_pg(rank, world, "gloo", port)
-        n, C, H, E, k, skew = shape
+        n, C, H, E, k, skew, chunks = shape
         w = synth.Workload("ep", n, C, H, E, k, "fp32", skew=skew)
-        run_rank(w, rank, world, lambda w, el: CpuStages(w.C, w.H, w.E, w.k, el, w.alpha), "cpu", 2e-4)
+        run_rank(w, rank, world, lambda w, el: CpuStages(w.C, w.H, w.E, w.k, el, w.alpha, n_chunks=chunks), "cpu", 2e-4)
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok"))
@@ -34,7 +34,13 @@ def _worker(rank, world, port, shape, q):
         q.put((rank, traceback.format_exc()))
 
 
-@pytest.mark.parametrize("shape", [(48, 16, 24, 4, 2, False), (33, 16, 16, 8, 3, True)])
+@pytest.mark.parametrize("shape", [
+    (48, 16, 24, 4, 2, False, 1),
+    (33, 16, 16, 8, 3, True, 1),
+    (48, 16, 24, 4, 2, False, 2),       # two chunks of one expert per rank: exchange overlapped with the expert work
+    (61, 16, 16, 8, 3, True, 2),
+    (40, 16, 16, 16, 2, False, 4),
+])
 def test_expert_parallel_two_ranks_gloo(shape):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -49,9 +55,10 @@ def test_expert_parallel_two_ranks_gloo(shape):
         assert msg == "ok", f"rank {rank}: {msg}"
 
 
-def test_single_rank_needs_no_process_group():
+@pytest.mark.parametrize("chunks", [1, 2])
+def test_single_rank_needs_no_process_group(chunks):
     w = synth.Workload("ep1", 40, 16, 24, 4, 2, "fp32")
-    run_rank(w, 0, 1, lambda w, el: CpuStages(w.C, w.H, w.E, w.k, el, w.alpha), "cpu", 2e-4)
+    run_rank(w, 0, 1, lambda w, el: CpuStages(w.C, w.H, w.E, w.k, el, w.alpha, n_chunks=chunks), "cpu", 2e-4)
 
 
 def test_experts_must_divide_evenly():

@@ -14,16 +14,19 @@ from tests.ep_common import init_pg, run_rank
 pytestmark = pytest.mark.gpu
 
 
-def _stages(mode, device):
-    return lambda w, el: CudaStages(w.C, w.H, w.E, w.k, el, mode=mode, device=device, lb_alpha=w.alpha)
+def _stages(mode, device, chunks=1, sm_budget=0):
+    return lambda w, el: CudaStages(w.C, w.H, w.E, w.k, el, mode=mode, device=device, lb_alpha=w.alpha,
+                                    n_chunks=chunks, sm_budget=sm_budget)
 
 
+@pytest.mark.parametrize("chunks", [1, 2])
 @pytest.mark.parametrize("mode,tol", [("fp32", 1e-5), ("bf16", 2e-2)])
-def test_stage_entry_points_one_gpu(mode, tol):
-    """World size 1: the six stage calls compose to the whole layer."""
+def test_stage_entry_points_one_gpu(mode, tol, chunks):
+    """World size 1: the six stage calls compose to the whole layer (also with the experts in two chunks,
+    and with the persistent kernels held to fewer CTAs than SMs)."""
     w = synth.Workload("ep1", 600, 128, 192, 8, 2, mode)
     io = torch.bfloat16 if mode == "bf16" else torch.float32
-    run_rank(w, 0, 1, _stages(mode, 0), "cuda:0", tol, io=io)
+    run_rank(w, 0, 1, _stages(mode, 0, chunks, sm_budget=0 if chunks == 1 else 100), "cuda:0", tol, io=io)
 
 
 def _worker(rank, world, port, q):
@@ -35,6 +38,10 @@ def _worker(rank, world, port, q):
         run_rank(w, rank, world, _stages("bf16", rank), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
         w = synth.Workload("epskew", 900, 128, 128, 16, 4, "bf16", skew=True)
         run_rank(w, rank, world, _stages("bf16", rank), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        # experts in chunks: the second chunk's rows travel while the first chunk is computed
+        run_rank(w, rank, world, _stages("bf16", rank, chunks=2, sm_budget=120), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        w = synth.Workload("epchunks", 2000, 256, 192, 16, 2, "bf16")
+        run_rank(w, rank, world, _stages("bf16", rank, chunks=4), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok"))
