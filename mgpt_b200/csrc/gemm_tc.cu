@@ -272,7 +272,8 @@ __device__ __forceinline__ void cta_teardown(uint32_t tmem_base, int warp)
 // both, so the pair is ready for the next launch on the stream without a memset.
 // The value returned by the counter is first looked at in sched_publish (item >= total: no work left, published
 // as -1 so that the other roles stop at this entry too); between request and use lie an item's loads.
-__device__ __forceinline__ int sched_fetch(int32_t* counter) { return atomicAdd(counter, 1); }
+// A CTA's first item is its own index (no round trip before the first loads); the counter hands out the rest.
+__device__ __forceinline__ int sched_fetch(int32_t* counter) { return (int)gridDim.x + atomicAdd(counter, 1); }
 // Hands the CTA's n-th item to the other roles.  False: the wait for a free queue slot ran out.
 __device__ __forceinline__ bool sched_publish(const Pipe& pipe, uint32_t n, int& item, int total, int32_t* status)
 {
@@ -293,7 +294,7 @@ __device__ __forceinline__ int sched_consume(const Pipe& pipe, uint32_t n, int32
     return item;
 }
 __device__ __forceinline__ void sched_release(const Pipe& pipe, uint32_t n) { mbar_arrive(pipe.sched_empty(n % SCHED_Q)); }
-// Thread 0 of every CTA of the grid, after its last fetch (also CTAs that leave without fetching).
+// Once per CTA of the grid, by the producer thread after its last fetch (also CTAs that leave without fetching).
 __device__ __forceinline__ void sched_finish(int32_t* counter)
 {
     __threadfence();
@@ -424,18 +425,13 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            int item = sched_fetch(p.sched);
+            int item = blockIdx.x;
             ok = sched_publish(pipe, 0, item, total_items, p.status);
             for (uint32_t nf = 1; ok && item >= 0; ++nf) {
-                // the next item is requested now and handed on after this item's loads are under way,
-                // so the round trip to the counter stays off the critical path
-                int next = sched_fetch(p.sched);
                 const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
                 const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
                 const int brow = (MODE == MODE_DX ? 0 : p.tile_expert[row_tile] * p.b_rows_per_expert) + n0;
                 const int row0 = row_tile * BM;
-                // a last column tile with at most 128 valid columns takes half of B and a 128-wide MMA
-                const bool narrow = MODE != MODE_GATEUP && p.n_out - n0 <= BN / 2;
                 for (int kb = 0; kb < kb_per_item; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(pipe.empty(s), ((it / STAGES) - 1) & 1, p.status, ERR_EMPTY_WAIT)) {
@@ -443,7 +439,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         break;
                     }
                     const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                    mbar_expect_tx(pipe.full(s), narrow ? A_BYTES + HALF_B : STAGE_BYTES);
+                    mbar_expect_tx(pipe.full(s), STAGE_BYTES);
                     const bool second = MODE == MODE_DXG && kb >= p.kblocks;
                     const int kx = (second ? kb - p.kblocks : kb) * BK;
                     tma_load_2d(a_dst, second ? &tmA1 : &tmA0, kx, row0, pipe.full(s));
@@ -453,24 +449,26 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     } else {
                         const CUtensorMap* mb = second ? &tmB1 : &tmB0;
                         tma_load_2d(b_dst, mb, kx, brow, pipe.full(s));
-                        if (!narrow) tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
+                        tma_load_2d(b_dst + HALF_B, mb, kx, brow + BN / 2, pipe.full(s));
                     }
                 }
+                // the next item is claimed as late as possible (the ring is full by now, so the round trip to the
+                // counter does not starve the tensor core): early claims would sit behind this CTA's unfinished work
+                int next = sched_fetch(p.sched);
                 if (ok) ok = sched_publish(pipe, nf, next, total_items, p.status);
                 item = next;
             }
+            sched_finish(p.sched);                       // this CTA asks for no more items
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN, 0, 0);
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (; ok; ++t) {
                 const int item = sched_consume(pipe, t, p.status);
                 if (item >= 0) sched_release(pipe, t);
                 if (item < 0) break;
-                const int n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
-                const bool narrow = MODE != MODE_GATEUP && p.n_out - n0 <= BN / 2;
-                const uint32_t idesc = narrow ? make_idesc(BM, BN / 2, 0, 0) : make_idesc(BM, BN, 0, 0);
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
@@ -630,7 +628,6 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores landed before exit
     }
     cta_teardown(tmem_base, warp);
-    if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 // ---- weight gradients: grad[e][M,N] += A_e^T * B_e over the expert's rows ---------
@@ -701,12 +698,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            int item = sched_fetch(p.sched);
+            int item = blockIdx.x;
             ok = sched_publish(pipe, 0, item, total_items, p.status);
             for (uint32_t nf = 1; ok && item >= 0; ++nf) {
-                int next = sched_fetch(p.sched);      // handed on after this item's loads
                 const WgradItem w = wgrad_item(p, item);
-                const int nb = (min(BN, p.prob[w.pr].N - w.n0) + 63) / 64;   // 64-column boxes of B with valid columns
                 const CUtensorMap* mA = w.pr == 0 ? &tmA0 : w.pr == 1 ? &tmA1 : &tmA2;
                 const CUtensorMap* mB = w.pr == 0 ? &tmB0 : w.pr == 1 ? &tmB1 : &tmB2;
                 const bool segmented = p.n_seg > 0 && !p.prob[w.pr].uniform_rows;
@@ -721,21 +716,25 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                             break;
                         }
                         const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                        mbar_expect_tx(pipe.full(s), A_BYTES + nb * BOX);
+                        mbar_expect_tx(pipe.full(s), STAGE_BYTES);
                         const int row = seg_r0 + kb * BK;
 #pragma unroll
                         for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
 #pragma unroll
-                        for (int i = 0; i < BN / 64; ++i)
-                            if (i < nb) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
+                        for (int i = 0; i < BN / 64; ++i) tma_load_2d(b_dst + i * BOX, mB, w.n0 + 64 * i, row, pipe.full(s));
                     }
                 }
+                // the next item is claimed as late as possible (the ring is full by now, so the round trip to the
+                // counter does not starve the tensor core): early claims would sit behind this CTA's unfinished work
+                int next = sched_fetch(p.sched);
                 if (ok) ok = sched_publish(pipe, nf, next, total_items, p.status);
                 item = next;
             }
+            sched_finish(p.sched);                       // this CTA asks for no more items
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1);
             uint32_t it = 0, t = 0;
             bool ok = true;
             for (uint32_t nf = 0; ok; ++nf) {
@@ -744,8 +743,6 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                 sched_release(pipe, nf);
                 const WgradItem w = wgrad_item(p, item);
                 if (w.nkb <= 0) continue;
-                // a last column tile is as wide as its valid 64-column boxes
-                const uint32_t idesc = make_idesc(BM, 64 * ((min(BN, p.prob[w.pr].N - w.n0) + 63) / 64), 1, 1);
                 const uint32_t buf = t & 1u;
                 if (t >= 2 && !mbar_wait(pipe.acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
                 tc_fence_after();
@@ -824,7 +821,6 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
         }
     }
     cta_teardown(tmem_base, warp);
-    if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 // ---- host side: tensor maps ------------------------------------------------------
