@@ -24,10 +24,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "moe_layer_fwd_bwd_tokens_per_sec"
-# DRAM bytes (read + write) per launch from ncu captures, keyed by (workload, stage); see profiles/
+# DRAM bytes (read + write) per launch from ncu captures, keyed by (workload, stage); see profiles/.
+# c4 is too large to capture with many passes: its figures are those of c4q (a quarter of the tokens and of the
+# experts, same rows per expert) times four -- every term of the traffic is proportional to the number of experts.
 TRAFFIC = {
     ("c2", "wgrad_gemm"): 415.8e6, ("c2", "gateup_gemm"): 154.8e6, ("c2", "dhh_gemm"): 204.2e6,
     ("c2", "down_gemm"): 73.9e6, ("c2", "dxg_gemm"): 149.5e6,
+    ("c4q", "wgrad_gemm"): 1420.1e6, ("c4q", "gateup_gemm"): 374.8e6, ("c4q", "dhh_gemm"): 350.2e6,
+    ("c4q", "down_gemm"): 189.1e6, ("c4q", "dxg_gemm"): 342.2e6,
+    ("c4", "wgrad_gemm"): 4 * 1420.1e6, ("c4", "gateup_gemm"): 4 * 374.8e6, ("c4", "dhh_gemm"): 4 * 350.2e6,
+    ("c4", "down_gemm"): 4 * 189.1e6, ("c4", "dxg_gemm"): 4 * 342.2e6,
 }
 UNIT = "tokens/s"
 

@@ -34,6 +34,8 @@ WORKLOADS = {
     "c2": Workload("c2", 8192, 512, 1376, 16, 2, "bf16"),
     "c3": Workload("c3", 16384, 1024, 512, 64, 4, "bf16", skew=True),
     "c4": Workload("c4", 32768, 2048, 1408, 64, 2, "bf16"),
+    # a quarter of c4 (same rows per expert, so the same tiles per expert): small enough for multi-pass profiling
+    "c4q": Workload("c4q", 8192, 2048, 1408, 16, 2, "bf16"),
     "c5-8": Workload("c5-8", 8, 1024, 2816, 32, 2, "bf16", backward=False),
     "c5-64": Workload("c5-64", 64, 1024, 2816, 32, 2, "bf16", backward=False),
     "c5-256": Workload("c5-256", 256, 1024, 2816, 32, 2, "bf16", backward=False),
