@@ -193,26 +193,27 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float (&
 }
 
 // y[tok,:] = sum_j p[tok,j] * Yg[pos(tok,j),:], slots visited in ascending order
-// like the reference's scatter-add.  One warp per token, 8 channels per lane per step.
-template <typename TAct, typename TIo>
-__global__ void __launch_bounds__(256)
+// like the reference's scatter-add.  One warp per token, 8 channels per lane per step; K = top-k rounded up
+// to a power of two, so the sort is a fixed network and the kernel fits 32 registers (all 64 warps resident).
+template <typename TAct, typename TIo, int K>
+__global__ void __launch_bounds__(256, 8)
 combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos, const float* __restrict__ top_p,
                    int N, int C, int k, TIo* __restrict__ y)
 {
     const int lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (tok >= N) return;
-    int ps[MAX_TOPK];
-    float pr[MAX_TOPK];
+    int ps[K];
+    float pr[K];
 #pragma unroll
-    for (int j = 0; j < MAX_TOPK; ++j) {
+    for (int j = 0; j < K; ++j) {
         ps[j] = j < k ? pos[(size_t)tok * k + j] : 0x7fffffff;
         pr[j] = j < k ? top_p[(size_t)tok * k + j] : 0.0f;
     }
 #pragma unroll
-    for (int a = 0; a < MAX_TOPK - 1; ++a)          // tiny sorting network (bubble), static indices
+    for (int a = 0; a < K - 1; ++a)                 // tiny sorting network (bubble), static indices
 #pragma unroll
-        for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
+        for (int b = 0; b < K - 1 - a; ++b)
             if (ps[b] > ps[b + 1]) {
                 int ti = ps[b]; ps[b] = ps[b + 1]; ps[b + 1] = ti;
                 float tf = pr[b]; pr[b] = pr[b + 1]; pr[b + 1] = tf;
@@ -220,7 +221,7 @@ combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos,
     for (int c = lane * 8; c < C; c += 256) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-        for (int j = 0; j < MAX_TOPK; ++j) {
+        for (int j = 0; j < K; ++j) {
             if (j < k) {
                 float v[8];
                 load8(Yg + (size_t)ps[j] * C + c, v);
@@ -381,12 +382,20 @@ int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N
 {
     if (N <= 0) return 0;
     const int grid = (N + 7) / 8;
-    if (act_bytes == 4)
-        combine_fwd_kernel<float, float><<<grid, 256, 0, st>>>((const float*)rows, pos, top_p, N, C, k, (float*)y);
-    else if (io == MGPT_MOE_IO_F32)
-        combine_fwd_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (float*)y);
-    else
-        combine_fwd_kernel<bf16, bf16><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (bf16*)y);
+#define MGPT_COMBINE(KK)                                                                                                  \
+    do {                                                                                                                  \
+        if (act_bytes == 4)                                                                                               \
+            combine_fwd_kernel<float, float, KK><<<grid, 256, 0, st>>>((const float*)rows, pos, top_p, N, C, k, (float*)y); \
+        else if (io == MGPT_MOE_IO_F32)                                                                                   \
+            combine_fwd_kernel<bf16, float, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (float*)y); \
+        else                                                                                                              \
+            combine_fwd_kernel<bf16, bf16, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (bf16*)y);   \
+    } while (0)
+    if (k <= 1) MGPT_COMBINE(1);
+    else if (k <= 2) MGPT_COMBINE(2);
+    else if (k <= 4) MGPT_COMBINE(4);
+    else MGPT_COMBINE(8);
+#undef MGPT_COMBINE
     MGPT_LAUNCHED("combine_fwd_kernel");
     return 0;
 }
