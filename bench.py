@@ -316,8 +316,43 @@ def single_gpu_pass(args, w, rank, dev):
     single_gpu_pass.experts_touched = sum(1 for c in layer.get_expert_counts() if c > 0)
     res = measure(args, w, 1, 0, dev, step, step_host, host_checksum, layer.stage_ms, layer.set_profiling, barrier, N,
                   x_host.numel() * x_host.element_size(), graph_ok=not args.no_graph)
+    single_gpu_pass.optimizer = time_optimizer(layer, w) if w.backward and not args.no_optimizer else None
     layer.close()
     return res
+
+
+def time_optimizer(layer, w):
+    """Outside the timed steps: the fused AdamW + BF16-copy refresh against the copy refresh alone
+    (what an engine-side AdamW would have to be followed by).  CUDA events, three runs after one warm-up."""
+    import torch
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * reps)]
+        for i in range(reps):
+            ev[2 * i].record()
+            fn()
+            ev[2 * i + 1].record()
+        torch.cuda.synchronize()
+        return min(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(reps))
+
+    try:
+        step_no = [0]
+
+        def adamw():
+            step_no[0] += 1
+            layer.adamw_step(step_no[0])
+
+        adamw_ms = timed(adamw)
+        sync_ms = timed(layer.sync_weights)
+    except torch.OutOfMemoryError:
+        return None
+    n_w = sum(p.numel() for p in layer.get_parameters())
+    byts = n_w * (28 + (4 if w.dtype == "bf16" else 0))      # read w,g,m,v; write w,m,v (+ two BF16 copies)
+    return {"adamw_fused_ms": round(adamw_ms, 4), "adamw_fused_gbs": round(byts / (adamw_ms * 1e-3) / 1e9, 1),
+            "bytes": byts, "sync_weights_alone_ms": round(sync_ms, 4),
+            "note": "not part of the timed step; one optimiser step over all 2+6E tensors, copies refreshed in the same pass"}
 
 
 def run_ours(args, w):
@@ -464,6 +499,8 @@ def run_ours(args, w):
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "stages": stages,
         "cpu_baseline": cpu,
     }
+    if world == 1 and getattr(single_gpu_pass, "optimizer", None):
+        line["optimizer"] = single_gpu_pass.optimizer
     if reference_1gpu:
         line["same_workload_on_one_gpu"] = reference_1gpu
     if world > 1:
@@ -487,6 +524,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
     ap.add_argument("--no-single", action="store_true", help="N>1: skip the one-GPU pass of the same workload")
+    ap.add_argument("--no-optimizer", action="store_true", help="skip the untimed AdamW / copy-refresh measurement")
     args = ap.parse_args()
 
     from mgpt_b200 import synth

@@ -136,6 +136,20 @@ int  mgpt_moe_set_profiling(mgpt_moe_layer* layer, int enabled);
 int  mgpt_moe_stage_ms(mgpt_moe_layer* layer, float* ms);
 const char* mgpt_moe_stage_name(int stage);
 
+/* Optimiser step for the layer's own parameters, fused with the refresh of the
+ * BF16 weight copies. Replaces, for these tensors, the per-tensor
+ * Tensor::adamw_step calls of AdamWOptimizer::step
+ * (optimisers/AdamWOptimiser.h:24-36, utils/Tensor.cpp:683-699,
+ * utils/cuda_ops.cu:723-738) and the mgpt_moe_sync_weights call that would
+ * have to follow them. bind_optimizer_state takes the first and second moment
+ * buffers (FP32 device memory owned by the caller, zero at step 1, same order
+ * and NULL rules as bind_params); rebinding parameters unbinds them.
+ * adamw_step (t = 1-based step count) updates w, m, v in place with the CPU
+ * arm's arithmetic, bit for bit, and leaves the layer ready for forward. */
+int  mgpt_moe_bind_optimizer_state(mgpt_moe_layer* layer, float* const* m, float* const* v, int n);
+int  mgpt_moe_adamw_step(mgpt_moe_layer* layer, float lr, float beta1, float beta2, float eps, float weight_decay,
+                         int t, mgpt_stream_t stream);
+
 /* Upper bound on the CTAs of the persistent tensor-core kernels of this layer
  * (one CTA per SM; 0 = every SM, the default). A caller that overlaps these
  * kernels with communication kernels on another stream leaves SMs free for

@@ -169,6 +169,7 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
     cudaSetDevice(L->device);
     tc_destroy(L);
     cudaFree(L->d_tables);
+    cudaFree(L->d_opt);
     cudaFree(L->sWg); cudaFree(L->sWu); cudaFree(L->sWd);
     cudaFree(L->sWgT); cudaFree(L->sWuT); cudaFree(L->sWdT);
     cudaFree(L->sWr);
@@ -239,7 +240,52 @@ int mgpt_moe_bind_params(mgpt_moe_layer* L, float* const* data, float* const* gr
     MGPT_CUDA(cudaMemcpy(L->d_tables, h.data(), h.size() * sizeof(void*), cudaMemcpyHostToDevice));
     L->bound = router && experts;
     L->shadows_fresh = false;
+    L->opt_bound = false;      // the optimiser tables hold the old parameter pointers
     return 0;
+}
+
+int mgpt_moe_bind_optimizer_state(mgpt_moe_layer* L, float* const* m, float* const* v, int n)
+{
+    if (!L || !m || !v) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (!L->router_bound && !L->experts_bound) return fail(MGPT_MOE_ESTATE, "bind_params first");
+    if (!L->has_grad) return fail(MGPT_MOE_ESTATE, "bind_params with gradient buffers first");
+    if (n != L->n_params && n != 2) return fail(MGPT_MOE_EINVAL, "expected 2+6E state tensors (or the 2 router ones)");
+    if (L->experts_bound && n != L->n_params) return fail(MGPT_MOE_EINVAL, "expert parameters are bound: pass 2+6E state tensors");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    const int E = L->d.E, S = E < 2 ? 2 : E;
+    if (!L->d_opt) MGPT_CUDA(cudaMalloc(&L->d_opt, (size_t)16 * S * sizeof(void*)));
+    std::vector<void*> h((size_t)16 * S, nullptr);
+    for (int e = 0; e < E && L->experts_bound; ++e) {
+        const int b = 2 + 6 * e;
+        const int order[6] = {b + 0, b + 2, b + 4, b + 1, b + 3, b + 5};      // Wg Wu Wd bg bu bd
+        for (int j = 0; j < 6; ++j) {
+            if (!m[order[j]] || !v[order[j]]) return fail(MGPT_MOE_EINVAL, "null optimiser-state pointer");
+            h[(size_t)j * S + e] = m[order[j]];
+            h[(size_t)(6 + j) * S + e] = v[order[j]];
+        }
+    }
+    if (L->router_bound) {
+        for (int i = 0; i < 2; ++i) {
+            if (!m[i] || !v[i]) return fail(MGPT_MOE_EINVAL, "null optimiser-state pointer");
+            h[(size_t)12 * S + i] = L->p_data[i];
+            h[(size_t)13 * S + i] = L->p_grad[i];
+            h[(size_t)14 * S + i] = m[i];
+            h[(size_t)15 * S + i] = v[i];
+        }
+    }
+    MGPT_CUDA(cudaMemcpy(L->d_opt, h.data(), h.size() * sizeof(void*), cudaMemcpyHostToDevice));
+    L->opt_bound = true;
+    return 0;
+}
+
+int mgpt_moe_adamw_step(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
+                        mgpt_stream_t stream)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (!L->opt_bound) return fail(MGPT_MOE_ESTATE, "bind_optimizer_state first");
+    if (t < 1) return fail(MGPT_MOE_EINVAL, "the step count starts at 1");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    return launch_adamw(L, lr, beta1, beta2, eps, weight_decay, t, (cudaStream_t)stream);
 }
 
 int mgpt_moe_sync_weights(mgpt_moe_layer* L, mgpt_stream_t stream)

@@ -101,6 +101,8 @@ struct mgpt_moe_layer {
 
     // device tables: pointers to FP32 masters / grads per expert
     void* d_tables = nullptr;                // one allocation holding all tables
+    void* d_opt = nullptr;                   // optimiser-state tables (m, v per tensor kind; router w, g, m, v)
+    bool opt_bound = false;
     mgpt::ExpertPtrs master;                 // W pointers -> FP32 masters
     mgpt::ExpertPtrs shadow;                 // W pointers -> BF16 shadows (BF16 mode)
 
@@ -189,6 +191,9 @@ int simt_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaS
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 void tc_destroy(mgpt_moe_layer* L);
+int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st);
+int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
+                 cudaStream_t st);
 int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dXg, const int32_t* pos, void* dx,
                  cudaStream_t st);
 int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st);

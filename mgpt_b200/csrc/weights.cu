@@ -51,6 +51,19 @@ router_shadow_kernel(const float* __restrict__ Wr, int C, int E, int E8, bf16* _
 
 }  // namespace
 
+// After an optimiser step that wrote the expert copies itself: only the router's padded BF16 copy is rebuilt.
+int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st)
+{
+    const Dims& d = L->d;
+    if (d.mode == MGPT_MOE_BF16 && L->router_bound) {
+        const int E8 = (d.E + 7) / 8 * 8;
+        router_shadow_kernel<<<(d.C * E8 + 255) / 256, 256, 0, st>>>(L->p_data[0], d.C, d.E, E8, L->sWr);
+        MGPT_LAUNCHED("router_shadow_kernel");
+    }
+    L->shadows_fresh = true;
+    return 0;
+}
+
 int launch_sync_weights(mgpt_moe_layer* L, cudaStream_t st)
 {
     const Dims& d = L->d;

@@ -88,6 +88,22 @@ class MoELayer:
         for p in self.params:
             p.grad.zero_()
 
+    # -- optimiser -----------------------------------------------------------
+    def adamw_step(self, t: int, lr: float = 3e-4, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                   weight_decay: float = 0.01):
+        """One AdamW step over this layer's parameters (defaults and arithmetic of the reference's
+        AdamWOptimizer, optimisers/AdamWOptimiser.h:21-36), fused with the refresh of the BF16 copies:
+        no ``sync_weights`` is needed afterwards.  ``t`` counts steps from 1; the moment buffers
+        ``self.opt_m`` / ``self.opt_v`` are created (zero) on first use."""
+        if getattr(self, "opt_m", None) is None:
+            self.opt_m = [torch.zeros_like(p) for p in self.params]
+            self.opt_v = [torch.zeros_like(p) for p in self.params]
+            n = len(self.params)
+            m = (ct.c_void_p * n)(*[a.data_ptr() for a in self.opt_m])
+            v = (ct.c_void_p * n)(*[a.data_ptr() for a in self.opt_v])
+            _lib.check(self.lib.mgpt_moe_bind_optimizer_state(self._h, m, v, n))
+        _lib.check(self.lib.mgpt_moe_adamw_step(self._h, lr, beta1, beta2, eps, weight_decay, int(t), self._stream()))
+
     # -- memory ------------------------------------------------------------
     def get_footprint(self, B: int, T: int) -> int:
         """Arena bytes for B*T tokens (the reference reports floats, MoELayer.cpp:238-251)."""

@@ -468,3 +468,24 @@ int moe_oracle_bench(const moe_oracle_dims* d, const moe_oracle_inputs* in, int 
     free(dx);
     return rc;
 }
+
+/* utils/Tensor.cpp:683-699: bias-correction scales from powf once per step, then per element
+ * m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g;  w -= lr*wd*w;  w -= lr*(m*ms) / (sqrt(v*vs) + eps),
+ * every operation a separate FP32 rounding (the oracle is built with -ffp-contract=off). */
+int moe_oracle_adamw(float* w, const float* g, float* m, float* v, long n, float lr, float beta1, float beta2,
+                     float eps, float weight_decay, int t)
+{
+    if (!w || !g || !m || !v || n < 0 || t < 1) return 1;
+    const float ms = 1.0f / (1.0f - powf(beta1, (float)t));
+    const float vs = 1.0f / (1.0f - powf(beta2, (float)t));
+    for (long i = 0; i < n; ++i) {
+        const float gi = g[i];
+        m[i] = beta1 * m[i] + (1.0f - beta1) * gi;
+        v[i] = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+        const float m_hat = m[i] * ms;
+        const float v_hat = v[i] * vs;
+        w[i] -= lr * weight_decay * w[i];
+        w[i] -= lr * m_hat / (sqrtf(v_hat) + eps);
+    }
+    return 0;
+}

@@ -69,6 +69,11 @@ int moe_oracle_route(const moe_oracle_dims* d, const moe_oracle_inputs* in,
 int moe_oracle_bench(const moe_oracle_dims* d, const moe_oracle_inputs* in, int iters, double* seconds,
                      int n_threads);
 
+/* One AdamW step on a flat tensor of n floats, in place on w, m, v: the reference's CPU arithmetic
+ * (utils/Tensor.cpp:683-699, driven by optimisers/AdamWOptimiser.h:24-36).  t is the 1-based step count. */
+int moe_oracle_adamw(float* w, const float* g, float* m, float* v, long n, float lr, float beta1, float beta2,
+                     float eps, float weight_decay, int t);
+
 #ifdef __cplusplus
 }
 #endif

@@ -177,3 +177,19 @@ def bench(dims: Dims, x, params, dy=None, *, which: str = "oracle", iters: int =
     if rc != 0:
         raise RuntimeError(f"{which} bench returned {rc}")
     return list(secs)
+
+
+def adamw(w, g, m, v, *, lr, beta1, beta2, eps, weight_decay, t, which: str = "oracle"):
+    """One AdamW step on flat float32 arrays; returns new (w, m, v).  ``which``: "oracle" (C restatement of
+    utils/Tensor.cpp:683-699) or "ref" (the reference's own Tensor::adamw_step)."""
+    w, m, v = (np.array(a, dtype=np.float32).ravel() for a in (w, m, v))
+    g = np.ascontiguousarray(g, dtype=np.float32).ravel()
+    _load(which)
+    lib = ct.CDLL(ORACLE_SO if which == "oracle" else REF_SO)
+    fn = lib.moe_oracle_adamw if which == "oracle" else lib.moe_ref_adamw
+    fn.argtypes = [_FP, _FP, _FP, _FP, ct.c_long] + [ct.c_float] * 5 + [ct.c_int]
+    fn.restype = ct.c_int
+    rc = fn(_fp(w), _fp(g), _fp(m), _fp(v), w.size, lr, beta1, beta2, eps, weight_decay, int(t))
+    if rc != 0:
+        raise RuntimeError(f"{which} adamw returned {rc}")
+    return w, m, v

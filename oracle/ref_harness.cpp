@@ -129,3 +129,25 @@ extern "C" int moe_ref_route(const moe_oracle_dims* d, const moe_oracle_inputs* 
         return 1;
     }
 }
+
+/* The reference's own AdamW step (Tensor::adamw_step, CPU arm) on a flat tensor, in place on w, m, v. */
+extern "C" int moe_ref_adamw(float* w, const float* g, float* m, float* v, long n, float lr, float beta1, float beta2,
+                             float eps, float weight_decay, int t)
+{
+    try {
+        Tensor p({(int)n}, 0.0f, Device::CPU), mt({(int)n}, 0.0f, Device::CPU), vt({(int)n}, 0.0f, Device::CPU);
+        p.zero_grad();
+        std::memcpy(p.data.data(), w, (size_t)n * sizeof(float));
+        std::memcpy(p.grad.data(), g, (size_t)n * sizeof(float));
+        std::memcpy(mt.data.data(), m, (size_t)n * sizeof(float));
+        std::memcpy(vt.data.data(), v, (size_t)n * sizeof(float));
+        p.adamw_step(mt, vt, lr, beta1, beta2, eps, weight_decay, t);
+        std::memcpy(w, p.data.data(), (size_t)n * sizeof(float));
+        std::memcpy(m, mt.data.data(), (size_t)n * sizeof(float));
+        std::memcpy(v, vt.data.data(), (size_t)n * sizeof(float));
+        return 0;
+    } catch (const std::exception& e) {
+        std::cerr << "moe_ref_adamw: " << e.what() << std::endl;
+        return 1;
+    }
+}

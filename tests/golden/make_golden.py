@@ -100,6 +100,25 @@ def main() -> None:
         arrays["input_sha256"] = np.frombuffer(input_digest(x, params, dy).encode(), dtype=np.uint8)
         np.savez_compressed(golden_path(name), **arrays)
         print(f"{name}: counts {r['counts'].tolist()} -> {os.path.getsize(golden_path(name))} bytes")
+    make_adamw_golden()
+
+
+def make_adamw_golden() -> None:
+    """Three steps of the reference's own AdamW (Tensor::adamw_step, CPU arm) on a seeded flat tensor."""
+    from oracle import oracle
+
+    rng = np.random.default_rng(20240611)
+    n = 1537
+    w = rng.normal(0, 0.02, n).astype(np.float32)
+    g = rng.normal(0, 1e-2, n).astype(np.float32)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    hyper = dict(lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+    w3, m3, v3 = w, m, v
+    for t in (1, 2, 3):
+        w3, m3, v3 = oracle.adamw(w3, g, m3, v3, t=t, which="ref", **hyper)
+    np.savez_compressed(golden_path("adamw"), w=w, g=g, m=m, v=v, w3=w3, m3=m3, v3=v3,
+                        **{k: np.float32(x) for k, x in hyper.items()})
+    print(f"adamw: {os.path.getsize(golden_path('adamw'))} bytes")
 
 
 if __name__ == "__main__":

@@ -100,3 +100,32 @@ def test_numpy_plan_reference_matches_golden(name):
     r = plan_reference(gold["top_idx"], w.E)
     for key in ("counts", "offsets", "map"):
         assert np.array_equal(r[key], gold[key]), key
+
+
+def test_adamw_restatement_matches_reference_live():
+    """oracle/moe_oracle.c:moe_oracle_adamw against the reference's Tensor::adamw_step (CPU arm), bit for bit."""
+    if not oracle.have_ref():
+        pytest.skip("reference build absent")
+    rng = np.random.default_rng(3)
+    n = 4099
+    w = rng.normal(0, 0.02, n).astype(np.float32)
+    g = rng.normal(0, 1e-2, n).astype(np.float32)
+    m = rng.normal(0, 1e-3, n).astype(np.float32)
+    v = (rng.random(n) * 1e-5).astype(np.float32)
+    for t in (1, 2, 17, 5000):
+        a = oracle.adamw(w, g, m, v, lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, t=t)
+        b = oracle.adamw(w, g, m, v, lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, t=t, which="ref")
+        for x, y in zip(a, b):
+            assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+
+
+def test_adamw_restatement_matches_golden():
+    """tests/golden/adamw.npz holds the reference build's own outputs (make_golden.py)."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "adamw.npz"))
+    w, m, v = z["w"], z["m"], z["v"]
+    for t in (1, 2, 3):
+        w, m, v = oracle.adamw(w, z["g"], m, v, lr=float(z["lr"]), beta1=float(z["beta1"]), beta2=float(z["beta2"]),
+                               eps=float(z["eps"]), weight_decay=float(z["weight_decay"]), t=t)
+    for got, want in ((w, z["w3"]), (m, z["m3"]), (v, z["v3"])):
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
