@@ -71,11 +71,32 @@ void MoELayer::ensure_bound()
         check(mgpt_moe_bind_params(handle, data.data(), grad.data(), (int)data.size()), "bind_params");
         bound = true;
         weights_dirty = true;
+        opt_bound = false;
     }
     if (weights_dirty) {
         check(mgpt_moe_sync_weights(handle, nullptr), "sync_weights");
         weights_dirty = false;
     }
+}
+
+void MoELayer::adamw_step(const std::vector<Tensor*>& m, const std::vector<Tensor*>& v, float lr, float beta1,
+                          float beta2, float eps, float weight_decay, int t)
+{
+    const bool rebound = !bound;
+    ensure_bound();
+    if (rebound || !opt_bound) {
+        if (m.size() != params.size() || v.size() != params.size())
+            throw std::runtime_error("MoELayer::adamw_step: expected one m and one v tensor per parameter");
+        std::vector<float*> mp, vp;
+        for (size_t i = 0; i < params.size(); ++i) {
+            mp.push_back(m[i]->get_data_ptr());
+            vp.push_back(v[i]->get_data_ptr());
+        }
+        check(mgpt_moe_bind_optimizer_state(handle, mp.data(), vp.data(), (int)mp.size()), "bind_optimizer_state");
+        opt_bound = true;
+    }
+    check(mgpt_moe_adamw_step(handle, lr, beta1, beta2, eps, weight_decay, t, nullptr), "adamw_step");
+    weights_dirty = false;      // the step wrote the BF16 copies itself
 }
 
 float* MoELayer::take_workspace(size_t n_tokens)

@@ -29,6 +29,7 @@ private:
     mgpt_moe_layer* handle = nullptr;
     bool bound = false;
     bool weights_dirty = true;
+    bool opt_bound = false;
 
     Tensor cached_out;
     Tensor cached_dX;
@@ -56,6 +57,13 @@ public:
     // Call after an optimiser step or a checkpoint load: the BF16 weight copies are
     // rebuilt at the next forward.  Without it every forward rebuilds them.
     void weights_updated() { weights_dirty = true; }
+
+    // Optional: one AdamW step over this layer's 2+6E tensors in a few launches, fused with the
+    // rebuild of the BF16 weight copies (same arithmetic as Tensor::adamw_step, Tensor.cpp:683-699).
+    // An optimiser that uses it skips these tensors in its own loop (AdamWOptimiser.h:24-36);
+    // m and v are its moment tensors for get_parameters()[i], in the same order.
+    void adamw_step(const std::vector<Tensor*>& m, const std::vector<Tensor*>& v, float lr, float beta1, float beta2,
+                    float eps, float weight_decay, int t);
 
     Tensor forward(const Tensor& input) override;
     void forward_into(const Tensor& input, Tensor& output) override;
