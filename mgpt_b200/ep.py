@@ -105,6 +105,24 @@ class CudaStages:
     def _stream():
         return ct.c_void_p(torch.cuda.current_stream().cuda_stream)
 
+    def adamw_step(self, t, lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
+        """One fused AdamW step (BF16 copies refreshed in the same pass) over the router replica and this
+        rank's experts; moment buffers ``opt_m`` / ``opt_v`` (router first, then the experts) are created on first use."""
+        c = self._lib_mod.check
+        if getattr(self, "opt_m", None) is None:
+            ps = self.router_params + self.expert_params
+            self.opt_m = [torch.zeros_like(p) for p in ps]
+            self.opt_v = [torch.zeros_like(p) for p in ps]
+            arr = lambda ts: (ct.c_void_p * len(ts))(*[None if a is None else a.data_ptr() for a in ts])
+            c(self.lib.mgpt_moe_bind_optimizer_state(self.home, arr(self.opt_m[:2]), arr(self.opt_v[:2]), 2))
+            per = 6 * self.E_chunk
+            for ci, h in enumerate(self.locals):
+                m = [None, None] + self.opt_m[2 + ci * per: 2 + (ci + 1) * per]
+                v = [None, None] + self.opt_v[2 + ci * per: 2 + (ci + 1) * per]
+                c(self.lib.mgpt_moe_bind_optimizer_state(h, arr(m), arr(v), 2 + per))
+        for h in [self.home] + self.locals:
+            c(self.lib.mgpt_moe_adamw_step(h, lr, beta1, beta2, eps, weight_decay, int(t), self._stream()))
+
     def _io(self, t):
         return self._lib_mod.IO_BF16 if t.dtype == torch.bfloat16 else self._lib_mod.IO_F32
 
@@ -261,6 +279,11 @@ class ExpertParallelMoE:
     def zero_grad(self):
         for p in self.get_parameters():
             p.grad.zero_()
+
+    def adamw_step(self, t, **hyper):
+        """Optimiser step over the router replica and this rank's experts (sum the router gradients over the
+        group first with ``allreduce_router_grads()`` if the replicas are to stay identical)."""
+        self.stages.adamw_step(t, **hyper)
 
     def allreduce_router_grads(self):
         """Sum the router gradients over the group so that the replicas stay identical."""

@@ -26,7 +26,19 @@ def test_stage_entry_points_one_gpu(mode, tol, chunks):
     and with the persistent kernels held to fewer CTAs than SMs)."""
     w = synth.Workload("ep1", 600, 128, 192, 8, 2, mode)
     io = torch.bfloat16 if mode == "bf16" else torch.float32
-    run_rank(w, 0, 1, _stages(mode, 0, chunks, sm_budget=0 if chunks == 1 else 100), "cuda:0", tol, io=io)
+    layer = run_rank(w, 0, 1, _stages(mode, 0, chunks, sm_budget=0 if chunks == 1 else 100), "cuda:0", tol, io=io)
+    # the fused optimiser step over router + expert-side layers: bit-exact against the reference's AdamW arithmetic
+    import numpy as np
+    from oracle import oracle
+    hyper = dict(lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
+    before = [(p.cpu().numpy().copy(), p.grad.cpu().numpy().copy()) for p in layer.get_parameters()]
+    layer.adamw_step(1, **hyper)
+    torch.cuda.synchronize()
+    for (w0, g0), p in zip(before, layer.get_parameters()):
+        want, _, _ = oracle.adamw(w0, g0, np.zeros_like(w0), np.zeros_like(w0), t=1, **hyper)
+        assert np.array_equal(p.cpu().numpy().ravel().view(np.uint32), want.view(np.uint32))
+    y2 = layer.forward(torch.zeros(8, w.C, dtype=io, device="cuda:0"))      # runs without sync_weights
+    assert torch.isfinite(y2.float()).all()
 
 
 def _worker(rank, world, port, q):
