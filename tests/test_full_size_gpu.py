@@ -1,0 +1,90 @@
+"""The 64-expert configuration at its full size (32768 tokens, C=2048, H=1408, E=64, top-2, BF16).
+
+The CPU oracle needs ~20 s per step for this configuration whatever the token count (it walks all
+64 experts' weights), so the full-size run is checked through what does not depend on the size:
+routing against the oracle's routing pass (bit-exact), the outputs of a token subset against the oracle
+run on that subset alone (tokens are independent in forward), additivity of the weight gradients over
+the two halves of the batch, and the invariants of the plan.
+"""
+import numpy as np
+import pytest
+import torch
+
+from mgpt_b200 import MoELayer, synth
+from oracle import oracle
+from tests.util import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 2e-2
+
+
+@pytest.fixture(scope="module")
+def c4():
+    w = synth.WORKLOADS["c4"]
+    gen = torch.Generator(device="cuda").manual_seed(4242)
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode="bf16", lb_alpha=w.alpha)
+    for p in layer.get_parameters():           # N(0, 0.02) rounded to BF16, biases small but non-zero
+        std = 0.02
+        p.copy_((torch.randn(p.shape, generator=gen, device="cuda") * std).bfloat16().float())
+    layer.sync_weights()
+    x = torch.randn(w.n_tokens, w.C, generator=gen, device="cuda").bfloat16()
+    dy = torch.randn(w.n_tokens, w.C, generator=gen, device="cuda").bfloat16()
+    params = [p.cpu().numpy() for p in layer.get_parameters()]
+    yield w, layer, x, dy, params
+    layer.close()
+
+
+def test_c4_routing_bit_exact_and_plan_invariants(c4):
+    w, layer, x, dy, params = c4
+    layer.forward(x)
+    torch.cuda.synchronize()
+    N, E, k = w.n_tokens, w.E, w.k
+    d = oracle.Dims(N, w.C, w.H, E, k, w.alpha)
+    ref = oracle.run(d, x.float().cpu().numpy(), params, route_only=True, threads=16)
+    i32 = torch.int32
+    view = lambda name, shape=None: layer.workspace_view(name, i32, shape).cpu().numpy()
+    assert np.array_equal(view("top_idx", (N, k)), ref["top_idx"])
+    assert np.array_equal(view("counts"), ref["counts"])
+    assert np.array_equal(view("offsets"), ref["offsets"])
+    assert np.array_equal(view("map"), ref["map"])
+    assert np.array_equal(layer.workspace_view("logits", torch.float32, (N, E)).cpu().numpy(), ref["logits"])
+    # plan: counts add up, padded segments are whole tiles, pos is a bijection onto the non-padding rows
+    counts, poff, pos = ref["counts"], view("padded_offsets"), view("pos")
+    assert counts.sum() == N * k
+    assert np.array_equal(np.diff(poff), (counts + 127) // 128 * 128)
+    row_src = view("row_src")[: poff[-1]]
+    assert np.array_equal(np.sort(row_src[row_src >= 0]), np.arange(N * k))
+    assert np.array_equal(row_src[pos], np.arange(N * k))
+    assert int(view("status")[0]) == 0
+
+
+def test_c4_outputs_of_a_token_subset_match_the_oracle(c4):
+    w, layer, x, dy, params = c4
+    y = layer.forward(x)
+    sub = 384
+    d = oracle.Dims(sub, w.C, w.H, w.E, w.k, w.alpha)
+    ref = oracle.run(d, x[:sub].float().cpu().numpy(), params, None, threads=16)
+    assert rel_l2(y[:sub].float().cpu().numpy(), ref["y"]) <= TOL_BF16
+
+
+def test_c4_weight_gradients_add_up_over_half_batches(c4):
+    """grads(whole batch) = grads(first half) + grads(second half) for every expert tensor (routing is per token;
+    the load-balance term only reaches the router).  The halves run as their own forward+backward."""
+    w, layer, x, dy, params = c4
+    layer.zero_grad()
+    layer.forward(x)
+    layer.backward(dy)
+    whole = [p.grad.clone() for p in layer.get_parameters()[2:]]
+    layer.zero_grad()
+    h = w.n_tokens // 2
+    for sl in (slice(0, h), slice(h, None)):
+        layer.forward(x[sl].contiguous())
+        layer.backward(dy[sl].contiguous())          # accumulates
+    torch.cuda.synchronize()
+    worst = 0.0
+    for a, p in zip(whole, layer.get_parameters()[2:]):
+        den = float(a.double().norm())
+        err = float((a.double() - p.grad.double()).norm())
+        worst = max(worst, err / den if den > 0 else err)
+    assert worst <= 1e-3, worst        # same products, different summation order over rows
