@@ -316,9 +316,37 @@ def single_gpu_pass(args, w, rank, dev):
     single_gpu_pass.experts_touched = sum(1 for c in layer.get_expert_counts() if c > 0)
     res = measure(args, w, 1, 0, dev, step, step_host, host_checksum, layer.stage_ms, layer.set_profiling, barrier, N,
                   x_host.numel() * x_host.element_size(), graph_ok=not args.no_graph)
+    single_gpu_pass.recompute = time_recompute(layer, x, y) if w.backward and not args.no_optimizer else None
     single_gpu_pass.optimizer = time_optimizer(layer, w) if w.backward and not args.no_optimizer else None
     layer.close()
     return res
+
+
+def time_recompute(layer, x, y):
+    """Outside the timed steps: forward alone against the recompute forward that takes the saved routing
+    (activation checkpointing runs the forward twice per step).  CUDA events, best of three."""
+    import torch
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            t = a.elapsed_time(b)
+            best = t if best is None else min(best, t)
+        return best
+
+    fwd_ms = timed(lambda: layer.forward_into(x, y))
+    routing = layer.save_routing()
+    re_ms = timed(lambda: layer.recompute_into(x, y, routing))
+    return {"forward_ms": round(fwd_ms, 4), "recompute_forward_ms": round(re_ms, 4),
+            "routing_state_bytes": int(routing.numel()),
+            "note": "not part of the timed step; the recompute skips router and plan"}
 
 
 def time_optimizer(layer, w):
@@ -501,6 +529,8 @@ def run_ours(args, w):
     }
     if world == 1 and getattr(single_gpu_pass, "optimizer", None):
         line["optimizer"] = single_gpu_pass.optimizer
+    if world == 1 and getattr(single_gpu_pass, "recompute", None):
+        line["checkpointing"] = single_gpu_pass.recompute
     if reference_1gpu:
         line["same_workload_on_one_gpu"] = reference_1gpu
     if world > 1:

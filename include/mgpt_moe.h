@@ -136,6 +136,22 @@ int  mgpt_moe_set_profiling(mgpt_moe_layer* layer, int enabled);
 int  mgpt_moe_stage_ms(mgpt_moe_layer* layer, float* ms);
 const char* mgpt_moe_stage_name(int stage);
 
+/* Recompute forward for activation checkpointing. The reference runs every block's
+ * forward twice per step (GPT.cpp:79-96: once without keeping activations, once more
+ * before that block's backward, the arena rewound in between). The same tokens route
+ * the same way, so the second run can skip router and plan: after the first forward
+ * save_routing copies the routing results and the plan (routing_bytes(n_tokens) bytes:
+ * probabilities, top-k, counts, offsets, tile list, row permutation) into memory the
+ * caller keeps outside the arena; forward_with_routing takes them back instead of
+ * recomputing them and then runs dispatch, the expert products and combine as
+ * mgpt_moe_forward does. Backward follows it as usual. The caller guarantees that x,
+ * the weights and n_tokens are those of the forward that was saved. */
+size_t mgpt_moe_routing_bytes(const mgpt_moe_layer* layer, int n_tokens);
+int  mgpt_moe_save_routing(mgpt_moe_layer* layer, void* dst, mgpt_stream_t stream);
+int  mgpt_moe_forward_with_routing(mgpt_moe_layer* layer, const void* x, void* y, int n_tokens, int io_dtype,
+                                   void* workspace, size_t workspace_bytes, const void* routing,
+                                   mgpt_stream_t stream);
+
 /* Optimiser step for the layer's own parameters, fused with the refresh of the
  * BF16 weight copies. Replaces, for these tensors, the per-tensor
  * Tensor::adamw_step calls of AdamWOptimizer::step

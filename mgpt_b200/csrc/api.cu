@@ -343,8 +343,47 @@ static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, s
     return 0;
 }
 
+// Routing results and plan of one forward: the workspace bytes from probs up to (not including) the plan's
+// scratch -- probs, top_idx, top_p, counts, offsets, padded_offsets, tile_expert, n_tiles, status, map, pos, row_src.
+static size_t routing_begin(const Workspace& w) { return w.probs; }
+static size_t routing_end(const Workspace& w) { return w.blk_cnt; }
+
+size_t mgpt_moe_routing_bytes(const mgpt_moe_layer* L, int n_tokens)
+{
+    if (!L || n_tokens < 0) return 0;
+    const Workspace w = make_workspace(L->d, n_tokens);
+    return routing_end(w) - routing_begin(w);
+}
+
+int mgpt_moe_save_routing(mgpt_moe_layer* L, void* dst, mgpt_stream_t stream)
+{
+    if (!L || !dst) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (!L->fwd_done) return fail(MGPT_MOE_ESTATE, "save_routing without a forward");
+    const Workspace w = make_workspace(L->d, L->last_n);
+    MGPT_CUDA(cudaSetDevice(L->device));
+    MGPT_CUDA(cudaMemcpyAsync(dst, (const char*)L->last_ws + routing_begin(w), routing_end(w) - routing_begin(w),
+                              cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return 0;
+}
+
+static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing);
+
 int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io,
                      void* workspace, size_t ws_bytes, mgpt_stream_t stream)
+{
+    return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, nullptr);
+}
+
+int mgpt_moe_forward_with_routing(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io,
+                                  void* workspace, size_t ws_bytes, const void* routing, mgpt_stream_t stream)
+{
+    if (!routing) return fail(MGPT_MOE_EINVAL, "null routing state");
+    return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, routing);
+}
+
+static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing)
 {
     Workspace w;
     MGPT_TRY(check_call(L, n_tokens, io, workspace, ws_bytes, &w));
@@ -357,16 +396,25 @@ int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, in
     L->ext_Xg = L->ext_Yg = L->ext_dYg = L->ext_dXg = nullptr;      // whole-layer calls keep every buffer in the workspace
     L->n_seg = 0;
     for (int s = 0; s < ST_COUNT; ++s) L->ev_used[s] = false;
-    if (n_tokens > 0) {
-        L->stage_begin(ST_ROUTER, st);
-        MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
-                                   (float*)(ws + w.logits), (float*)(ws + w.probs),
-                                   (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
-        L->stage_end(ST_ROUTER, st);
+    if (routing) {
+        // recompute of a forward whose routing was saved: the same tokens route the same way, so router and plan
+        // are replaced by one copy (the logits are not part of the saved state and stay undefined)
+        L->stage_begin(ST_PLAN, st);
+        MGPT_CUDA(cudaMemcpyAsync(ws + routing_begin(w), routing, routing_end(w) - routing_begin(w),
+                                  cudaMemcpyDeviceToDevice, st));
+        L->stage_end(ST_PLAN, st);
+    } else {
+        if (n_tokens > 0) {
+            L->stage_begin(ST_ROUTER, st);
+            MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
+                                       (float*)(ws + w.logits), (float*)(ws + w.probs),
+                                       (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
+            L->stage_end(ST_ROUTER, st);
+        }
+        L->stage_begin(ST_PLAN, st);
+        MGPT_TRY(launch_plan(d, w, ws, st));
+        L->stage_end(ST_PLAN, st);
     }
-    L->stage_begin(ST_PLAN, st);
-    MGPT_TRY(launch_plan(d, w, ws, st));
-    L->stage_end(ST_PLAN, st);
     if (n_tokens > 0) {
         L->stage_begin(ST_DISPATCH, st);
         MGPT_TRY(launch_dispatch(d, w, ws, x, io, st));

@@ -145,6 +145,27 @@ class MoELayer:
         self.forward_into(x, out)
         return out
 
+    # -- activation checkpointing: keep the routing of a forward, recompute without router and plan
+    def save_routing(self) -> torch.Tensor:
+        """Routing results and plan of the last forward, in memory of their own (the reference rewinds its
+        arena between the first forward and the recompute, GPT.cpp:79-96)."""
+        n = int(self.lib.mgpt_moe_routing_bytes(self._h, self._n))
+        state = torch.empty(n, dtype=torch.uint8, device=self.device)
+        _lib.check(self.lib.mgpt_moe_save_routing(self._h, state.data_ptr(), self._stream()))
+        return state
+
+    def recompute_into(self, x: torch.Tensor, out: torch.Tensor, routing: torch.Tensor) -> None:
+        """Forward again on the same tokens with the saved routing; backward may follow."""
+        assert x.is_cuda and x.is_contiguous() and x.shape[-1] == self.C
+        assert out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous()
+        n = x.numel() // self.C
+        assert routing.numel() == int(self.lib.mgpt_moe_routing_bytes(self._h, n)), "routing state of another size"
+        ws = self._workspace(n)
+        _lib.check(self.lib.mgpt_moe_forward_with_routing(self._h, x.data_ptr(), out.data_ptr(), n, self._io(x),
+                                                          ws.data_ptr(), ws.numel(), routing.data_ptr(), self._stream()))
+        self._x, self._n = x, n
+        self.cached_out = out
+
     def backward_into(self, dout: torch.Tensor, din: torch.Tensor) -> None:
         if self._x is None:
             raise MoeError("backward before forward")
