@@ -136,6 +136,15 @@ int  mgpt_moe_set_profiling(mgpt_moe_layer* layer, int enabled);
 int  mgpt_moe_stage_ms(mgpt_moe_layer* layer, float* ms);
 const char* mgpt_moe_stage_name(int stage);
 
+/* Forward with the block's skip connection folded into the combine write:
+ * y = residual + moe(x), where the reference's caller adds the two in a separate pass
+ * (TransformerBlock.cpp:42-46: x2 = x1 + moe(ln2(x1)); residual = x1, same dtype and
+ * shape as y). The sum over a token's experts is formed first and the residual added
+ * last, which is the reference's order, so FP32 results are bit-identical to
+ * forward followed by the add. Backward is unchanged: the residual's gradient is dy itself. */
+int  mgpt_moe_forward_residual(mgpt_moe_layer* layer, const void* x, const void* residual, void* y, int n_tokens,
+                               int io_dtype, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
 /* Recompute forward for activation checkpointing. The reference runs every block's
  * forward twice per step (GPT.cpp:79-96: once without keeping activations, once more
  * before that block's backward, the arena rewound in between). The same tokens route

@@ -17,7 +17,7 @@ SYMBOLS = [
     "mgpt_moe_forward", "mgpt_moe_backward", "mgpt_moe_expert_counts", "mgpt_moe_workspace_view",
     "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
     "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name", "mgpt_moe_set_sm_budget", "mgpt_moe_bind_optimizer_state", "mgpt_moe_adamw_step",
-    "mgpt_moe_routing_bytes", "mgpt_moe_save_routing", "mgpt_moe_forward_with_routing",
+    "mgpt_moe_forward_residual", "mgpt_moe_routing_bytes", "mgpt_moe_save_routing", "mgpt_moe_forward_with_routing",
     "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes", "mgpt_moe_op_plan_noalloc",
     "mgpt_moe_stage_workspace_bytes", "mgpt_moe_route", "mgpt_moe_combine", "mgpt_moe_combine_backward",
     "mgpt_moe_route_backward", "mgpt_moe_experts_forward", "mgpt_moe_experts_backward",
@@ -68,6 +68,7 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_launch_count.restype = ct.c_long
     lib.mgpt_moe_set_profiling.argtypes = [vp, i32]
     lib.mgpt_moe_set_sm_budget.argtypes = [vp, i32]
+    lib.mgpt_moe_forward_residual.argtypes = [vp, vp, vp, vp, i32, i32, vp, ct.c_size_t, vp]
     lib.mgpt_moe_routing_bytes.argtypes = [vp, i32]
     lib.mgpt_moe_routing_bytes.restype = ct.c_size_t
     lib.mgpt_moe_save_routing.argtypes = [vp, vp, vp]

@@ -367,7 +367,7 @@ int mgpt_moe_save_routing(mgpt_moe_layer* L, void* dst, mgpt_stream_t stream)
 }
 
 static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
-                        size_t ws_bytes, mgpt_stream_t stream, const void* routing);
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual = nullptr);
 
 int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io,
                      void* workspace, size_t ws_bytes, mgpt_stream_t stream)
@@ -382,8 +382,15 @@ int mgpt_moe_forward_with_routing(mgpt_moe_layer* L, const void* x, void* y, int
     return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, routing);
 }
 
+int mgpt_moe_forward_residual(mgpt_moe_layer* L, const void* x, const void* residual, void* y, int n_tokens, int io,
+                              void* workspace, size_t ws_bytes, mgpt_stream_t stream)
+{
+    if (n_tokens > 0 && !residual) return fail(MGPT_MOE_EINVAL, "null residual");
+    return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, nullptr, residual);
+}
+
 static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
-                        size_t ws_bytes, mgpt_stream_t stream, const void* routing)
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual)
 {
     Workspace w;
     MGPT_TRY(check_call(L, n_tokens, io, workspace, ws_bytes, &w));
@@ -422,7 +429,7 @@ static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens,
         if (use_tc(L)) MGPT_TRY(tc_experts_forward(L, w, ws, st));
         else MGPT_TRY(simt_experts_forward(L, w, ws, st));
         L->stage_begin(ST_COMBINE, st);
-        MGPT_TRY(launch_combine_fwd(d, w, ws, y, io, st));
+        MGPT_TRY(launch_combine_fwd(d, w, ws, y, io, st, residual));
         L->stage_end(ST_COMBINE, st);
     }
     L->last_n = n_tokens;

@@ -168,14 +168,15 @@ int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const voi
 // plan.cu
 int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st);
 int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st);
-int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st);
+int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st,
+                       const void* residual = nullptr);
 int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st);
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st);
 int gather_rows(const void* src, int src_io, const int32_t* row_src, const int32_t* n_tiles, int rows, int grid_rows,
                 int C, int k, void* dst, size_t act_bytes, cudaStream_t st);
 int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,
-                 size_t act_bytes, cudaStream_t st);
+                 size_t act_bytes, cudaStream_t st, const void* residual = nullptr);
 int combine_rows_backward(const void* dy, int io, const void* rows, const int32_t* row_src, const float* top_p,
                           const int32_t* n_tiles, int n_rows, int grid_rows, int C, int k, void* d_rows, float* d_top_p,
                           size_t act_bytes, cudaStream_t st);

@@ -198,7 +198,7 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float (&
 template <typename TAct, typename TIo, int K>
 __global__ void __launch_bounds__(256, 8)
 combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos, const float* __restrict__ top_p,
-                   int N, int C, int k, TIo* __restrict__ y)
+                   int N, int C, int k, const TIo* __restrict__ residual, TIo* __restrict__ y)
 {
     const int lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -228,6 +228,12 @@ combine_fwd_kernel(const TAct* __restrict__ Yg, const int32_t* __restrict__ pos,
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], pr[j]));
             }
+        }
+        if (residual) {                 // y = residual + moe(x): the block's skip connection (TransformerBlock.cpp:44)
+            float r[8];
+            load8(residual + (size_t)tok * C + c, r);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(r[i], acc[i]);
         }
         store8(y + (size_t)tok * C + c, acc);
     }
@@ -378,18 +384,18 @@ int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, 
 
 // y = weighted gather-sum of rows[pos[tok,j]]
 int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,
-                 size_t act_bytes, cudaStream_t st)
+                 size_t act_bytes, cudaStream_t st, const void* residual)
 {
     if (N <= 0) return 0;
     const int grid = (N + 7) / 8;
 #define MGPT_COMBINE(KK)                                                                                                  \
     do {                                                                                                                  \
         if (act_bytes == 4)                                                                                               \
-            combine_fwd_kernel<float, float, KK><<<grid, 256, 0, st>>>((const float*)rows, pos, top_p, N, C, k, (float*)y); \
+            combine_fwd_kernel<float, float, KK><<<grid, 256, 0, st>>>((const float*)rows, pos, top_p, N, C, k, (const float*)residual, (float*)y); \
         else if (io == MGPT_MOE_IO_F32)                                                                                   \
-            combine_fwd_kernel<bf16, float, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (float*)y); \
+            combine_fwd_kernel<bf16, float, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (const float*)residual, (float*)y); \
         else                                                                                                              \
-            combine_fwd_kernel<bf16, bf16, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (bf16*)y);   \
+            combine_fwd_kernel<bf16, bf16, KK><<<grid, 256, 0, st>>>((const bf16*)rows, pos, top_p, N, C, k, (const bf16*)residual, (bf16*)y);   \
     } while (0)
     if (k <= 1) MGPT_COMBINE(1);
     else if (k <= 2) MGPT_COMBINE(2);
@@ -400,10 +406,10 @@ int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N
     return 0;
 }
 
-int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st)
+int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st, const void* residual)
 {
     return combine_rows(ws + w.Yg, (const int32_t*)(ws + w.pos), (const float*)(ws + w.top_p), w.n_tokens, d.C, d.k, y,
-                        io, w.act_bytes, st);
+                        io, w.act_bytes, st, residual);
 }
 
 // d_rows[p] = top_p * dy[tok], d_top_p[flat] = <rows[p], dy[tok]> for p < rows (rows < 0: every tile of the plan)

@@ -130,13 +130,19 @@ class MoELayer:
             return IO_BF16
         raise MoeError(f"unsupported token dtype {t.dtype}")
 
-    def forward_into(self, x: torch.Tensor, out: torch.Tensor) -> None:
+    def forward_into(self, x: torch.Tensor, out: torch.Tensor, residual: torch.Tensor = None) -> None:
+        """``out = moe(x)``, or ``out = residual + moe(x)`` (the block's skip connection, TransformerBlock.cpp:44)."""
         assert x.is_cuda and x.is_contiguous() and x.shape[-1] == self.C
         assert out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous()
         n = x.numel() // self.C
         ws = self._workspace(n)
-        _lib.check(self.lib.mgpt_moe_forward(self._h, x.data_ptr(), out.data_ptr(), n, self._io(x),
-                                             ws.data_ptr(), ws.numel(), self._stream()))
+        if residual is None:
+            _lib.check(self.lib.mgpt_moe_forward(self._h, x.data_ptr(), out.data_ptr(), n, self._io(x),
+                                                 ws.data_ptr(), ws.numel(), self._stream()))
+        else:
+            assert residual.shape == x.shape and residual.dtype == x.dtype and residual.is_contiguous()
+            _lib.check(self.lib.mgpt_moe_forward_residual(self._h, x.data_ptr(), residual.data_ptr(), out.data_ptr(), n,
+                                                          self._io(x), ws.data_ptr(), ws.numel(), self._stream()))
         self._x, self._n = x, n
         self.cached_out = out
 

@@ -53,3 +53,24 @@ def test_recompute_checks_its_arguments():
     with pytest.raises(AssertionError):
         layer.recompute_into(torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda"),
                              torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda"), st)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_forward_with_residual_equals_forward_plus_add(mode):
+    w = synth.Workload("res", 333, 128, 160, 8, 2, mode)
+    x, params, dy = synth.make_inputs(w, seed=31, bias_std=0.02)
+    io = torch.bfloat16 if mode == "bf16" else torch.float32
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode=mode)
+    layer.load_parameters(params)
+    xt = torch.from_numpy(x).cuda().to(io)
+    res = torch.from_numpy(dy).cuda().to(io)            # any tensor of the right shape
+    y = layer.forward(xt)
+    out = torch.empty_like(xt)
+    layer.forward_into(xt, out, residual=res)
+    torch.cuda.synchronize()
+    if mode == "fp32":
+        assert torch.equal(out, res + y)                # the residual is added last, as the reference's caller does
+    else:
+        # the fused sum is rounded once; forward + add rounds y first
+        assert torch.allclose(out.float(), res.float() + y.float(), rtol=2e-2, atol=2e-2)
+        assert float((out.float() - (res.float() + y.float())).abs().max()) <= 2 ** -6 * float(out.float().abs().max())
