@@ -383,6 +383,27 @@ def time_optimizer(layer, w):
             "note": "not part of the timed step; one optimiser step over all 2+6E tensors, copies refreshed in the same pass"}
 
 
+def bind_to_gpu_numa_node(index: int) -> None:
+    """Restricts this process to the CPU cores NVML reports as local to GPU `index` (read-only query), so that
+    the pinned host buffers of the end-to-end path are first touched on that GPU's NUMA node.  With one rank
+    per GPU and no binding, every rank's buffers can end up on one socket and all copies cross the
+    socket interconnect.  Best effort: any failure leaves the affinity as it was."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        n_cpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (n_cpu + 63) // 64)
+        cpus = {64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+        pynvml.nvmlShutdown()
+    except Exception:
+        pass
+
+
 def run_ours(args, w):
     import torch
     import torch.distributed as dist
@@ -403,6 +424,7 @@ def run_ours(args, w):
     else:
         from mgpt_b200.ep import ExpertParallelMoE
 
+        bind_to_gpu_numa_node(local)        # before any pinned allocation: host buffers land next to this rank's GPU
         dist.init_process_group("nccl", device_id=dev)
         if w.E % world:
             raise SystemExit(f"workload {w.name}: {w.E} experts do not divide over {world} GPUs")
@@ -434,12 +456,26 @@ def run_ours(args, w):
             if w.backward:
                 layer.backward(dy)
 
+        xd, dyd = torch.empty_like(x), torch.empty_like(dy)
+        copy_stream = torch.cuda.Stream(device=dev)
+
         def step_host():
-            xd = x_host.to(dev, non_blocking=True)
-            y = layer.forward(xd)
-            y_host.copy_(y, non_blocking=True)
+            # as in mgpt_moe_step_host: dy goes up while forward runs, y comes down while backward runs
+            cur = torch.cuda.current_stream()
+            xd.copy_(x_host, non_blocking=True)
+            up = torch.cuda.Event()
             if w.backward:
-                dyd = dy_host.to(dev, non_blocking=True)
+                copy_stream.wait_stream(cur)           # the previous step's backward has finished with dyd
+                with torch.cuda.stream(copy_stream):
+                    dyd.copy_(dy_host, non_blocking=True)
+                    up.record()
+            y = layer.forward(xd)
+            copy_stream.wait_stream(cur)
+            with torch.cuda.stream(copy_stream):
+                y_host.copy_(y, non_blocking=True)
+            y.record_stream(copy_stream)
+            if w.backward:
+                cur.wait_event(up)
                 dx_host.copy_(layer.backward(dyd), non_blocking=True)
             torch.cuda.synchronize()
 
