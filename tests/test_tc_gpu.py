@@ -50,6 +50,7 @@ def test_tc_matches_oracle_small(name):
     (1000, 256, 384, 8, 2, False),     # several row tiles per expert, full 64-wide k blocks
     (700, 192, 200, 5, 2, False),      # ragged k (200 = 3*64+8) and column tails
     (3000, 128, 96, 16, 4, True),      # skewed: empty and one-row experts next to large ones
+    (600, 128, 64, 128, 8, False),     # the largest expert count and top-k the library takes
 ])
 @pytest.mark.parametrize("io", [torch.float32, torch.bfloat16])
 def test_tc_against_simt_and_oracle(shape, io):
