@@ -80,29 +80,50 @@ def cpu_step_estimate_s(w, sample_tokens: int) -> float:
 
 
 def run_reference_arm(args, w):
-    """--impl reference: the reference's CPU implementation of the path, bounded sample per step.
-    The run is held to about four minutes: when the requested steps would take longer (every step walks all
-    experts' weights, 2.2 GB at the 64-expert configuration), fewer are run and the line says how many."""
+    """--impl reference: the reference's CPU implementation of the path on bounded samples.
+
+    Every CPU step has a fixed cost whatever the sample (it walks all experts' weights and weight gradients,
+    2.2 GB each at the 64-expert configuration) plus a cost per token, so one small sample divided by its time
+    understates the full configuration's throughput.  Two sample sizes are timed; the fixed and the per-token
+    cost are fitted through the two means and ``value`` is the full configuration's tokens/s extrapolated from
+    them (``ms_per_step`` likewise).  Both raw points are in ``sample``.  The run is held to about four minutes:
+    when the requested steps would take longer, fewer are run and the line says how many."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = min(w.n_tokens, args.cpu_sample or 256)
-    allowed = max(2, int(240.0 / cpu_step_estimate_s(w, sample)))
+    small = min(w.n_tokens, args.cpu_sample or 256)
+    large = min(w.n_tokens, 4 * small)
+    sizes = [small] if large == small else [small, large]
+    per_step = sum(cpu_step_estimate_s(w, n) for n in sizes)
+    allowed = max(2, int(240.0 / per_step))            # steps (warm-up included) per size
     warmup = min(args.warmup, max(1, allowed // 4))
     steps = max(1, min(args.steps, allowed - warmup))
-    secs, kind, cores = cpu_reference_step(w, sample, threads=os.cpu_count() or 1, iters=warmup + steps)
-    times = secs[warmup:]
-    sec = sum(times) / max(1, len(times))
-    value = sample / sec
-    sample_txt = f"{sample} tokens of {w.name} per step (same C,H,E,k), forward+backward"
+    points, kind, cores = [], None, 1
+    for n in sizes:
+        secs, kind, cores = cpu_reference_step(w, n, threads=os.cpu_count() or 1, iters=warmup + steps)
+        t = secs[warmup:]
+        points.append((n, sum(t) / len(t)))
+    if len(points) == 2 and points[1][1] > points[0][1]:
+        (n0, t0), (n1, t1) = points
+        per_token = (t1 - t0) / (n1 - n0)
+        fixed = max(0.0, t0 - per_token * n0)
+    else:                                              # one size (the workload is that small): no extrapolation
+        per_token, fixed = points[0][1] / points[0][0], 0.0
+    sec_full = fixed + per_token * w.n_tokens
+    value = w.n_tokens / sec_full
+    sample_txt = ("forward+backward of " + " and ".join(f"{n} tokens ({t:.2f} s/step, {n / t:.1f} tok/s)" for n, t in points)
+                  + f" of {w.name} (same C,H,E,k); fitted {fixed:.2f} s fixed + {per_token * 1e3:.3f} ms per token -> "
+                  f"{sec_full:.1f} s per step of all {w.n_tokens} tokens (value and ms_per_step are this extrapolation)")
     if steps != args.steps or warmup != args.warmup:
-        sample_txt += f"; {steps} timed steps after {warmup} warm-up (of {args.steps}/{args.warmup} asked) to bound the run"
+        sample_txt += f"; {steps} timed steps after {warmup} warm-up per size (of {args.steps}/{args.warmup} asked) to bound the run"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec_full * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": describe(w), "sample": sample_txt},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample_txt},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample_txt,
+                         "points": [{"tokens": n, "s_per_step": round(t, 3)} for n, t in points],
+                         "fixed_s": round(fixed, 3), "per_token_ms": round(per_token * 1e3, 4)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -169,39 +190,52 @@ def stage_model(w):
     return flops, byts
 
 
-def init_weights(params, w, dev, seed_of):
-    """Random-init weights of the architecture: N(0, 0.02), biases 0 (the router bias carries the skew);
-    values rounded to bf16 for bf16 workloads.  seed_of(i) seeds tensor i."""
+SEED = 1234
+
+
+def load_synth_params(params, w, dev, global_index):
+    """Weights of the workload from the seeded generator the oracle uses (mgpt_b200/synth.py: Philox keyed by
+    seed and tensor id; N(0, 0.02), biases 0, the skewed workload's router bias; rounded to bf16 for bf16
+    workloads), so a bench run can be re-checked against the CPU oracle afterwards.  global_index(i) maps this
+    process's parameter i to the index in the full 2+6E list."""
     import torch
+
+    from mgpt_b200 import synth
     for i, p in enumerate(params):
-        if p.shape[0] == 1:
-            p.zero_()
-            if i == 1 and w.skew:
-                p.copy_((2.0 * torch.log(1.0 / (torch.arange(w.E, device=dev, dtype=torch.float64) + 1.0))).float()[None, :])
-        else:
-            g = torch.Generator(device=dev)
-            g.manual_seed(seed_of(i))
-            p.normal_(0.0, 0.02, generator=g)
-            if w.dtype == "bf16":
-                p.copy_(p.to(torch.bfloat16).float())
+        a = synth.make_param(w, global_index(i), seed=SEED)
+        p.copy_(torch.from_numpy(a).reshape(p.shape))
+
+
+def host_tokens(w, rank):
+    """Pinned host x and dy of this rank (seed + rank: rank 0's are the oracle's own inputs) plus output buffers."""
+    import torch
+
+    from mgpt_b200 import synth
+    io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
+    x, dy = synth.make_tokens(w, seed=SEED + rank)
+    x_host = torch.from_numpy(x).to(io).pin_memory()
+    dy_host = torch.from_numpy(dy).to(io).pin_memory()
+    return x_host, dy_host, torch.empty_like(x_host).pin_memory(), torch.empty_like(x_host).pin_memory()
 
 
 def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms, set_profiling, barrier, N, io_bytes,
-            graph_ok=False):
+            graph_ok=False, steps=None, warmup=None, sample_clocks=True):
     """Warm-up, K timed steps (CUDA events, L2 flushed between steps, max over ranks), then the host-buffer path."""
     import torch
     import torch.distributed as dist
 
     from mgpt_b200 import launch_count
 
+    steps = steps or args.steps
+    warmup = max(warmup if warmup is not None else args.warmup, 3)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
-    sampler = ClockSampler(dev.index) if rank == 0 else None           # samples every 100 ms from here on
-    for _ in range(max(args.warmup, 3)):
+    sampler = ClockSampler(dev.index) if rank == 0 and sample_clocks else None   # samples every 100 ms from here on
+    for _ in range(warmup):
         flush.zero_()
         step()
     set_profiling(True)
     barrier()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     stage_sum = {}
     launch_count(reset=True)
     for s, e in ev:
@@ -219,7 +253,7 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
     set_profiling(False)
     total_ms = sum(s.elapsed_time(e) for s, e in ev)
     launch_mode = "stream launches"
-    stream_ms = total_ms / args.steps
+    stream_ms = total_ms / steps
     if graph_ok and world == 1:
         # The whole forward+backward enqueues without a host synchronisation, so it can be replayed as one
         # CUDA graph; the timed value is then free of launch gaps.  Stage times above come from the stream pass.
@@ -247,20 +281,22 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
     t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
-    # a short run can end before nvidia-smi has printed a sample: keep the same load up (untimed) for
-    # about 0.7 s in total; the count is derived from the all-reduced step time, so every rank runs the same
-    extra = min(2000, max(0, int(700.0 / max(ms_per_step, 1e-3)) - args.steps - max(args.warmup, 3)))
-    for _ in range(extra):
-        step()
-    barrier()
-    clocks = sampler.stop() if sampler else None
+    ms_per_step = float(t.item()) / steps
+    clocks = None
+    if sample_clocks:
+        # a short run can end before nvidia-smi has printed a sample: keep the same load up (untimed) for
+        # about 0.7 s in total; the count is derived from the all-reduced step time, so every rank runs the same
+        extra = min(2000, max(0, int(700.0 / max(ms_per_step, 1e-3)) - steps - warmup))
+        for _ in range(extra):
+            step()
+        barrier()
+        clocks = sampler.stop() if sampler else None
 
     for _ in range(2):
         step_host()
     barrier()
     e2e_ms = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.zero_()
         torch.cuda.synchronize()
         if world > 1:
@@ -271,29 +307,27 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
     t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / args.steps
+    e2e_ms = float(t.item()) / steps
     n_dir = 2 if w.backward else 1
     checksum = host_checksum()             # of the last step's output, computed outside the timed region
     e2e = {"value": world * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": io_bytes * n_dir, "d2h_bytes_per_step": io_bytes * n_dir, "checksum": checksum}
-    return ms_per_step, stage_sum, int(launches), clocks, e2e, launch_mode, stream_ms
+    return {"ms_per_step": ms_per_step, "stage_sum": stage_sum, "steps": steps, "launches": int(launches),
+            "clocks": clocks, "e2e": e2e, "launch_mode": launch_mode, "stream_ms": stream_ms}
 
 
-def single_gpu_pass(args, w, rank, dev):
-    """One replica of the whole layer on this GPU (all experts local)."""
+def single_gpu_pass(args, w, rank, dev, *, light=False):
+    """One replica of the whole layer on this GPU (all experts local).  ``light``: a short pass for the
+    secondary workloads (fewer steps, no clock sampling, no optimiser / recompute timing)."""
     import torch
 
     from mgpt_b200 import MoELayer
 
     N, C = w.n_tokens, w.C
-    io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
     layer = MoELayer(w.C, w.H, w.E, w.k, mode=w.dtype, device=dev.index, lb_alpha=w.alpha)
-    init_weights(layer.get_parameters(), w, dev, lambda i: 1234 + i)
+    load_synth_params(layer.get_parameters(), w, dev, lambda i: i)
     layer.sync_weights()
-    x_host = torch.randn(N, C, generator=torch.Generator().manual_seed(99 + rank)).to(io).pin_memory()
-    dy_host = torch.randn(N, C, generator=torch.Generator().manual_seed(199 + rank)).to(io).pin_memory()
-    y_host = torch.empty_like(x_host).pin_memory()
-    dx_host = torch.empty_like(x_host).pin_memory()
+    x_host, dy_host, y_host, dx_host = host_tokens(w, rank)
     x, dy = x_host.to(dev), dy_host.to(dev)
     y, dx = torch.empty_like(x), torch.empty_like(x)
 
@@ -313,11 +347,16 @@ def single_gpu_pass(args, w, rank, dev):
 
     layer.zero_grad()
     step()
-    single_gpu_pass.experts_touched = sum(1 for c in layer.get_expert_counts() if c > 0)
+    counts = layer.get_expert_counts()                 # also reads the layer's error word
     res = measure(args, w, 1, 0, dev, step, step_host, host_checksum, layer.stage_ms, layer.set_profiling, barrier, N,
-                  x_host.numel() * x_host.element_size(), graph_ok=not args.no_graph)
-    single_gpu_pass.recompute = time_recompute(layer, x, y) if w.backward and not args.no_optimizer else None
-    single_gpu_pass.optimizer = time_optimizer(layer, w) if w.backward and not args.no_optimizer else None
+                  x_host.numel() * x_host.element_size(), graph_ok=not args.no_graph,
+                  steps=min(args.steps, 10) if light else None, warmup=3 if light else None, sample_clocks=not light)
+    layer.check_status()
+    res["experts_touched"] = sum(1 for c in counts if c > 0)
+    res["counts"] = counts
+    res["y"], res["dx"] = y, (dx if w.backward else None)          # of the last timed step (device tensors)
+    res["recompute"] = time_recompute(layer, x, torch.empty_like(y)) if w.backward and not args.no_optimizer and not light else None
+    res["optimizer"] = time_optimizer(layer, w) if w.backward and not args.no_optimizer and not light else None
     layer.close()
     return res
 
@@ -404,6 +443,67 @@ def bind_to_gpu_numa_node(index: int) -> None:
         pass
 
 
+def score(w, res, peaks, world):
+    """Per-stage achieved TFLOP/s or GB/s and the roofline of the dominant kernel, from the stage times."""
+    flops, byts = stage_model(w)
+    stages = {}
+    for name, ms in res["stage_sum"].items():
+        ms /= res["steps"]
+        if ms <= 0:
+            continue
+        ent = {"ms": round(ms, 4)}
+        if name in flops:
+            ent["tflops"] = round(flops[name] / (ms * 1e-3) / 1e12, 1)
+        elif name in byts and world == 1:
+            ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
+        stages[name] = ent
+    gemm = {k: v for k, v in stages.items() if k in flops}
+    roofline = None
+    if gemm:
+        dom = max(gemm, key=lambda k: gemm[k]["ms"])
+        achieved = flops[dom] / (gemm[dom]["ms"] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        roofline = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "unit": "TFLOP/s",
+                    "frac": round(achieved / peak, 4), "traffic": TRAFFIC.get((w.name, dom)),
+                    "all_gemms_tflops": round(sum(flops[k] for k in gemm) / (sum(v["ms"] for v in gemm.values()) * 1e-3) / 1e12, 1)}
+    if not w.backward and gemm and world == 1:
+        # decode shapes stream the touched experts' weights once: HBM-bound, scored in GB/s
+        touched = res.get("experts_touched", w.E)
+        wbytes = touched * 3.0 * w.C * w.H * 2
+        ms = sum(v["ms"] for v in gemm.values())
+        ach = wbytes / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gateup_gemm+down_gemm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"],
+                    "peak_source": f"{peaks['source']} copy bandwidth", "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
+                    "traffic": None, "experts_touched": touched}
+    return stages, roofline
+
+
+def rel_l2(a, b) -> float:
+    import torch
+    a, b = a.double().reshape(-1), b.double().reshape(-1)
+    den = float(torch.linalg.vector_norm(b))
+    err = float(torch.linalg.vector_norm(a - b))
+    return err / den if den > 0 else err
+
+
+def oracle_check(w, y, sample):
+    """The bench's own outputs against the CPU oracle: forward of the first `sample` tokens (tokens are independent
+    in forward, and the seeded generator's first rows are the same whatever the token count)."""
+    import numpy as np
+    import torch
+
+    from mgpt_b200 import synth
+    from oracle import oracle
+    ws = w.scaled(sample)
+    x, params, _ = synth.make_inputs(ws, seed=SEED)
+    d = oracle.Dims(ws.n_tokens, ws.C, ws.H, ws.E, ws.k, ws.alpha)
+    ref = oracle.run(d, x, params, None, which="ref" if oracle.have_ref() else "oracle", threads=os.cpu_count() or 1)
+    got = y[:sample].float().cpu()
+    return {"tokens": sample, "y_rel_l2": rel_l2(got, torch.from_numpy(np.ascontiguousarray(ref["y"]))),
+            "against": "the reference's CPU MoELayer" if oracle.have_ref() else "the C restatement", "bar": 2e-2}
+
+
 def run_ours(args, w):
     import torch
     import torch.distributed as dist
@@ -417,9 +517,11 @@ def run_ours(args, w):
     N, C = w.n_tokens, w.C
     reference_1gpu = None
     ep_phases = None
+    ep_check = None
+    single = None
 
     if world == 1:
-        ms_per_step, stage_sum, launches, clocks, e2e, launch_mode, stream_ms = single_gpu_pass(args, w, rank, dev)
+        res = single = single_gpu_pass(args, w, rank, dev)
         parallelism = "single GPU"
     else:
         from mgpt_b200.ep import ExpertParallelMoE
@@ -429,32 +531,30 @@ def run_ours(args, w):
         if w.E % world:
             raise SystemExit(f"workload {w.name}: {w.E} experts do not divide over {world} GPUs")
         if rank == 0 and not args.no_single:
-            # the same per-GPU problem on one GPU with every expert local: the reference point of the scaling
-            r = single_gpu_pass(args, w, rank, dev)
-            reference_1gpu = {"n_gpus": 1, "value": N / (r[0] * 1e-3), "unit": UNIT, "ms_per_step": r[0],
+            # the same per-GPU problem on one GPU with every expert local: the reference point of the scaling,
+            # and (same seeded weights and tokens) the check of the expert-parallel result below
+            single = single_gpu_pass(args, w, rank, dev)
+            reference_1gpu = {"n_gpus": 1, "value": N / (single["ms_per_step"] * 1e-3), "unit": UNIT,
+                              "ms_per_step": single["ms_per_step"],
                               "workload": describe(w), "note": "all experts local, no exchange"}
             torch.cuda.empty_cache()
         dist.barrier()
-        io = torch.bfloat16 if w.dtype == "bf16" else torch.float32
         E_local = w.E // world
         chunks = args.ep_chunks if E_local % max(1, args.ep_chunks) == 0 else 1
         layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha,
                                   n_chunks=chunks, sm_budget=args.ep_sm_budget)
-        params = layer.get_parameters()
-        # router: same values on every rank; experts: seeded by their global index
-        init_weights(params, w, dev,
-                     lambda i: 1234 + (i if i < 2 else 2 + 6 * layer.global_expert((i - 2) // 6) + (i - 2) % 6))
+        # router: the same tensors on every rank; experts: those this rank owns, by their global index
+        load_synth_params(layer.get_parameters(), w, dev,
+                          lambda i: i if i < 2 else 2 + 6 * layer.global_expert((i - 2) // 6) + (i - 2) % 6)
         layer.stages.sync_weights()
-        x_host = torch.randn(N, C, generator=torch.Generator().manual_seed(99 + rank)).to(io).pin_memory()
-        dy_host = torch.randn(N, C, generator=torch.Generator().manual_seed(199 + rank)).to(io).pin_memory()
-        y_host = torch.empty_like(x_host).pin_memory()
-        dx_host = torch.empty_like(x_host).pin_memory()
+        x_host, dy_host, y_host, dx_host = host_tokens(w, rank)
         x, dy = x_host.to(dev), dy_host.to(dev)
+        last = {}
 
         def step():
-            layer.forward(x)
+            last["y"] = layer.forward(x)
             if w.backward:
-                layer.backward(dy)
+                last["dx"] = layer.backward(dy)
 
         xd, dyd = torch.empty_like(x), torch.empty_like(dy)
         copy_stream = torch.cuda.Stream(device=dev)
@@ -488,61 +588,46 @@ def run_ours(args, w):
             torch.cuda.synchronize()
 
         layer.zero_grad()
-        ms_per_step, stage_sum, launches, clocks, e2e, launch_mode, stream_ms = measure(
-            args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms, layer.stages.set_profiling, barrier, N,
-            x_host.numel() * x_host.element_size())
+        res = measure(args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms,
+                      layer.stages.set_profiling, barrier, N, x_host.numel() * x_host.element_size())
         # one more step with CUDA events around every phase (exchange vs compute), outside the timed region
         layer.phase_events = {}
         step()
         torch.cuda.synchronize()
         ep_phases = {k: round(v, 3) for k, v in layer.phase_ms().items()}
         layer.phase_events = None
+        layer.stages.check_status()
+        if rank == 0 and single is not None:
+            # rank 0's tokens through the expert-parallel layer against the same tokens through the one-GPU layer
+            # (same weights; the load-balance term uses this rank's own counts in both)
+            counts_ep = layer.stages.routing_view("counts", torch.int32).cpu().tolist()
+            ep_check = {"y_rel_l2": rel_l2(last["y"], single["y"]),
+                        "dx_rel_l2": rel_l2(last["dx"], single["dx"]) if w.backward else None,
+                        "counts_equal": counts_ep == [int(c) for c in single["counts"]],
+                        "note": "rank 0: expert-parallel result vs the one-GPU layer on the same seeded tokens and weights"}
         dist.barrier()
         parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
                        f"NCCL all-to-all for dispatch and combine, experts in {chunks} chunk(s) "
                        "(a chunk's exchange overlaps the previous chunk's expert work)")
 
+    ms_per_step = res["ms_per_step"]
     value = world * N / (ms_per_step * 1e-3)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # per-stage scores and the roofline of the dominant kernel
-    flops, byts = stage_model(w)
-    stages = {}
-    for name, ms in stage_sum.items():
-        ms /= args.steps
-        if ms <= 0:
-            continue
-        ent = {"ms": round(ms, 4)}
-        if name in flops:
-            ent["tflops"] = round(flops[name] / (ms * 1e-3) / 1e12, 1)
-        elif name in byts and world == 1:
-            ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
-        stages[name] = ent
-    launches_per = {"gateup_gemm": 1, "down_gemm": 1, "dhh_gemm": 1, "dxg_gemm": 1, "wgrad_gemm": 1}
-    gemm = {k: v for k, v in stages.items() if k in flops}
-    roofline = None
-    if gemm:
-        dom = max(gemm, key=lambda k: gemm[k]["ms"] / launches_per[k])
-        per_launch_ms = gemm[dom]["ms"] / launches_per[dom]
-        achieved = flops[dom] / launches_per[dom] / (per_launch_ms * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"]
-        roofline = {"bound": "tensor", "kernel": dom, "achieved": round(achieved, 1), "peak": peak,
-                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "unit": "TFLOP/s",
-                    "frac": round(achieved / peak, 4), "traffic": TRAFFIC.get((w.name, dom)),
-                    "all_gemms_tflops": round(sum(flops[k] for k in gemm) / (sum(v["ms"] for v in gemm.values()) * 1e-3) / 1e12, 1)}
-
-    if not w.backward and gemm and world == 1:
-        # decode shapes stream the touched experts' weights once: HBM-bound, scored in GB/s
-        touched = getattr(single_gpu_pass, "experts_touched", w.E)
-        wbytes = touched * 3.0 * w.C * w.H * 2
-        ms = sum(v["ms"] for v in gemm.values())
-        ach = wbytes / (ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "gateup_gemm+down_gemm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"],
-                    "peak_source": f"{peaks['source']} copy bandwidth", "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
-                    "traffic": None, "experts_touched": touched}
+    stages, roofline = score(w, res, peaks, world)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": res["steps"], "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": describe(w), "parallelism": parallelism,
+                   "l2": "flushed between timed steps by a 256 MiB write", "hbm_peak_gbs": peaks["hbm_gbs"],
+                   "launch": res["launch_mode"], "ms_per_step_stream_launches": round(res["stream_ms"], 4),
+                   "inputs": f"seeded synthetic (Philox, seed {SEED} + rank for tokens), the CPU oracle's generator"},
+        "clocks": res["clocks"], "e2e": res["e2e"], "gpu_launches": res["launches"], "roofline": roofline, "stages": stages,
+    }
 
     cpu = None
     if world == 1 and not args.no_cpu:
@@ -551,26 +636,38 @@ def run_ours(args, w):
                                                iters=2 if cpu_step_estimate_s(w, sample) < 10 else 1)
         sec = min(secs)
         cpu = {"value": sample / sec, "unit": UNIT, "cores": cores, "kind": kind,
-               "sample": f"{sample} tokens of {w.name} (same C,H,E,k), one forward+backward, {sec:.1f} s"}
-
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": describe(w), "parallelism": parallelism,
-                   "l2": "flushed between timed steps by a 256 MiB write", "hbm_peak_gbs": peaks["hbm_gbs"],
-                   "launch": launch_mode, "ms_per_step_stream_launches": round(stream_ms, 4)},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "stages": stages,
-        "cpu_baseline": cpu,
-    }
-    if world == 1 and getattr(single_gpu_pass, "optimizer", None):
-        line["optimizer"] = single_gpu_pass.optimizer
-    if world == 1 and getattr(single_gpu_pass, "recompute", None):
-        line["checkpointing"] = single_gpu_pass.recompute
+               "sample": f"{sample} tokens of {w.name} (same C,H,E,k), one forward+backward, {sec:.1f} s "
+                         "(includes the fixed cost of walking every expert's weights; --impl reference fits it out)"}
+        line["oracle_check"] = oracle_check(w, single["y"], min(sample, 512))
+    line["cpu_baseline"] = cpu
+    if world == 1 and single.get("optimizer"):
+        line["optimizer"] = single["optimizer"]
+    if world == 1 and single.get("recompute"):
+        line["checkpointing"] = single["recompute"]
     if reference_1gpu:
         line["same_workload_on_one_gpu"] = reference_1gpu
     if world > 1:
         line["ep_phases_ms"] = ep_phases
+        line["ep_check"] = ep_check
+    if world == 1 and not args.no_others and args.workload is None:
+        # the other configurations of the baseline, each a short pass after the timed run (not part of `value`)
+        from mgpt_b200 import synth
+        single = None
+        torch.cuda.empty_cache()
+        others = {}
+        for name in ("c2", "c3", "c5-8", "c5-64", "c5-256"):
+            ow = synth.WORKLOADS[name]
+            r = single_gpu_pass(args, ow, 0, dev, light=True)
+            st, rf = score(ow, r, peaks, 1)
+            others[name] = {"workload": describe(ow), "ms_per_step": round(r["ms_per_step"], 4),
+                            "tokens_per_s": round(ow.n_tokens / (r["ms_per_step"] * 1e-3), 1), "steps": r["steps"],
+                            "launch": r["launch_mode"],
+                            "roofline": None if rf is None else {k: rf[k] for k in ("bound", "kernel", "achieved", "unit", "frac", "traffic") if k in rf},
+                            "e2e": {"value": round(r["e2e"]["value"], 1), "ms_per_step": round(r["e2e"]["ms_per_step"], 4)},
+                            "stages_ms": {k: v["ms"] for k, v in st.items()}}
+            del r
+            torch.cuda.empty_cache()
+        line["other_workloads"] = others
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -591,6 +688,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
     ap.add_argument("--no-single", action="store_true", help="N>1: skip the one-GPU pass of the same workload")
     ap.add_argument("--no-optimizer", action="store_true", help="skip the untimed AdamW / copy-refresh measurement")
+    ap.add_argument("--no-others", action="store_true", help="skip the short passes over the other configurations")
     args = ap.parse_args()
 
     from mgpt_b200 import synth

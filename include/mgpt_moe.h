@@ -175,6 +175,33 @@ int  mgpt_moe_bind_optimizer_state(mgpt_moe_layer* layer, float* const* m, float
 int  mgpt_moe_adamw_step(mgpt_moe_layer* layer, float lr, float beta1, float beta2, float eps, float weight_decay,
                          int t, mgpt_stream_t stream);
 
+/* The same step with the two guards the reference's GPU kernel applies to the gradient before the update
+ * (utils/cuda_ops.cu:727-728): skip_nonfinite != 0 leaves an element whose gradient is NaN or Inf untouched
+ * (w, m, v keep their values), grad_clip > 0 clamps the gradient to [-grad_clip, grad_clip] (the reference
+ * uses 10).  With grad_clip = 0 and skip_nonfinite = 0 this is mgpt_moe_adamw_step.  The arithmetic after the
+ * guards is the CPU arm's, as above. */
+int  mgpt_moe_adamw_step_guarded(mgpt_moe_layer* layer, float lr, float beta1, float beta2, float eps,
+                                 float weight_decay, int t, float grad_clip, int skip_nonfinite,
+                                 mgpt_stream_t stream);
+
+/* Error word of the layer's kernels.  Every wait inside the tensor-core kernels is bounded; a wait that runs
+ * out, or an expert id outside [0, num_experts) met by the dispatch plan, sets a bit in a device word owned
+ * by the layer instead of hanging or faulting (the reference's kernels abort the process on a CUDA error,
+ * utils/cuda_ops.cu:10-18; there is nothing to return there).  check_status copies that word to the host on
+ * the stream of the layer's last call, synchronises that stream, and returns MGPT_MOE_OK when it is zero, else
+ * MGPT_MOE_ECUDA with the decoded bits in mgpt_moe_last_error() (the word is then cleared).  bits may be
+ * NULL.  mgpt_moe_step_host, mgpt_moe_expert_counts and mgpt_moe_stage_ms, which synchronise anyway, make the
+ * same check.  Bits: 1 plan overflow, 2/4/8/16 a bounded wait ran out (operands, stage release, accumulator,
+ * work queue), 32 expert id out of range. */
+int  mgpt_moe_check_status(mgpt_moe_layer* layer, int32_t* bits);
+
+/* Self-test of the error path, for failure-detection tests: launches one tiny kernel that waits, with the
+ * tensor-core kernels' own bounded wait and a limit of 4096 polls, on a barrier nothing arrives on.  The wait
+ * runs out within microseconds, bit 2 is set in the layer's error word and the kernel returns; no fault, no
+ * hang, the context stays usable.  The next mgpt_moe_check_status reports MGPT_MOE_ECUDA once.  No reference
+ * counterpart. */
+int  mgpt_moe_selftest_bounded_wait(mgpt_moe_layer* layer, mgpt_stream_t stream);
+
 /* Upper bound on the CTAs of the persistent tensor-core kernels of this layer
  * (one CTA per SM; 0 = every SM, the default). A caller that overlaps these
  * kernels with communication kernels on another stream leaves SMs free for
@@ -202,7 +229,9 @@ int  mgpt_moe_op_router(const void* x, int io_dtype, const float* Wr, const floa
  * segment rounded up to 128 rows), tile_expert[row_cap/128], n_tiles[1],
  * map[n_rows] (compact slot -> flat index, the reference's sorted_token_ids),
  * pos[n_rows] (flat index -> padded row), row_src[row_cap] (padded row -> flat
- * index, -1 for padding; written for the n_tiles*128 rows in use), status[1] (0 = ok).
+ * index, -1 for padding; written for the n_tiles*128 rows in use), status[1] (0 = ok;
+ * 32 = some top_idx value was outside [0, E): those entries get no slot and are left
+ * out of counts, map and pos stay unwritten for them).
  * row_cap: a multiple of 128, at least (n_rows + E*127) rounded down to 128.
  * scratch: device memory of mgpt_moe_op_plan_scratch_bytes(n_rows, E) bytes. */
 size_t mgpt_moe_op_plan_scratch_bytes(int n_rows, int E);
@@ -269,9 +298,11 @@ int  mgpt_moe_experts_backward(mgpt_moe_layer* layer, const void* d_out_rows, vo
  *     (different streams, no ordering between them) race on it; keep them in
  *     stream order or use mgpt_moe_op_plan with separate scratch;
  *   - the first call on each device looks up the array's device address
- *     (once, with that device current); make that first call before any
- *     stream capture begins.
- * It calls no cudaMalloc, cudaFree or other allocating routine. */
+ *     (once, with that device current); that lookup may make the CUDA runtime
+ *     load the library's module on the device, which allocates and
+ *     synchronises inside the driver.  Make that first call during set-up,
+ *     outside the step loop and before any stream capture begins.
+ * The call itself makes no cudaMalloc, cudaFree or other allocating call. */
 #define MGPT_MOE_PLAN_NOALLOC_MAX_ROWS 1048576
 int  mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int E,
                               int32_t* counts, int32_t* offsets, int32_t* padded_offsets,

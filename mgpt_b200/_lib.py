@@ -21,6 +21,7 @@ SYMBOLS = [
     "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes", "mgpt_moe_op_plan_noalloc",
     "mgpt_moe_stage_workspace_bytes", "mgpt_moe_route", "mgpt_moe_combine", "mgpt_moe_combine_backward",
     "mgpt_moe_route_backward", "mgpt_moe_experts_forward", "mgpt_moe_experts_backward",
+    "mgpt_moe_check_status", "mgpt_moe_adamw_step_guarded", "mgpt_moe_selftest_bounded_wait",
 ]
 PLAN_NOALLOC_MAX_ROWS = 1048576
 N_STAGES = 12
@@ -75,6 +76,9 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_forward_with_routing.argtypes = [vp, vp, vp, i32, i32, vp, ct.c_size_t, vp, vp]
     lib.mgpt_moe_bind_optimizer_state.argtypes = [vp, ct.POINTER(vp), ct.POINTER(vp), i32]
     lib.mgpt_moe_adamw_step.argtypes = [vp] + [ct.c_float] * 5 + [i32, vp]
+    lib.mgpt_moe_adamw_step_guarded.argtypes = [vp] + [ct.c_float] * 5 + [i32, ct.c_float, i32, vp]
+    lib.mgpt_moe_check_status.argtypes = [vp, ct.POINTER(ct.c_int32)]
+    lib.mgpt_moe_selftest_bounded_wait.argtypes = [vp, vp]
     lib.mgpt_moe_stage_ms.argtypes = [vp, ct.POINTER(ct.c_float)]
     lib.mgpt_moe_stage_name.argtypes = [i32]
     lib.mgpt_moe_stage_name.restype = ct.c_char_p

@@ -57,6 +57,7 @@ void MoELayer::to(Device target_device)
 {
     Layer::to(target_device);      // moves every parameter (Layer.h:49-53)
     bound = false;
+    weights_dirty = true;
 }
 
 void MoELayer::ensure_bound()
@@ -152,6 +153,8 @@ void MoELayer::backward_into(const Tensor& dout, Tensor& din)
                             workspace, workspace_floats * sizeof(float), nullptr),
           "backward");
     cached_dX = din;
+    // gradients exist now, so the optimiser is about to move the FP32 masters: the BF16 copies are stale
+    if (auto_refresh) weights_dirty = true;
 }
 
 const std::vector<float>& MoELayer::get_expert_counts() const

@@ -29,6 +29,7 @@ private:
     mgpt_moe_layer* handle = nullptr;
     bool bound = false;
     bool weights_dirty = true;
+    bool auto_refresh = true;
     bool opt_bound = false;
 
     Tensor cached_out;
@@ -54,9 +55,19 @@ public:
     // Per-expert routed rows of the last forward (reference: MoELayer.h:39).
     const std::vector<float>& get_expert_counts() const;
 
-    // Call after an optimiser step or a checkpoint load: the BF16 weight copies are
-    // rebuilt at the next forward.  Without it every forward rebuilds them.
+    // The tensor-core products read BF16 copies of the FP32 masters, so the copies must be rebuilt whenever the
+    // masters change.  The engine changes them behind the layer's back (AdamWOptimizer::step, load_weights_bin,
+    // --resume all go through get_parameters()), so the safe default is: the copies are marked stale when the
+    // layer is created or moved, and after every backward (an optimiser step follows gradients), and rebuilt at
+    // the next forward.  Under activation checkpointing that is still one rebuild per training step: the
+    // recompute forward that precedes backward finds them fresh.  An engine that writes the masters at any other
+    // moment (loading a checkpoint between two forwards without a backward) calls weights_updated() itself.
     void weights_updated() { weights_dirty = true; }
+
+    // An engine that calls weights_updated() after each of its own parameter writes can switch the automatic
+    // marking after backward off (saves the rebuild when several forward/backward pairs share one optimiser
+    // step, i.e. gradient accumulation).
+    void set_auto_refresh(bool on) { auto_refresh = on; }
 
     // Optional: one AdamW step over this layer's 2+6E tensors in a few launches, fused with the
     // rebuild of the BF16 weight copies (same arithmetic as Tensor::adamw_step, Tensor.cpp:683-699).

@@ -21,10 +21,14 @@ namespace {
 
 struct AdamwScalars {
     float b1, b2, omb1, omb2, eps, lr, lrwd, ms, vs;
+    float clip;       // > 0: the gradient is clamped to [-clip, clip] first (the GPU arm's 10, utils/cuda_ops.cu:728)
+    int skip_bad;     // != 0: an element whose gradient is NaN or Inf is left as it is (utils/cuda_ops.cu:727)
 };
 
 __device__ __forceinline__ void adamw_elem(float& w, float g, float& m, float& v, const AdamwScalars& a)
 {
+    if (a.skip_bad && !isfinite(g)) return;
+    if (a.clip > 0.0f) g = fminf(fmaxf(g, -a.clip), a.clip);
     m = __fadd_rn(__fmul_rn(a.b1, m), __fmul_rn(a.omb1, g));
     v = __fadd_rn(__fmul_rn(a.b2, v), __fmul_rn(__fmul_rn(a.omb2, g), g));
     const float mh = __fmul_rn(m, a.ms), vh = __fmul_rn(v, a.vs);
@@ -84,7 +88,7 @@ adamw_flat_kernel(float* const* __restrict__ w_ptrs, const float* const* __restr
 }  // namespace
 
 int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
-                 cudaStream_t st)
+                 cudaStream_t st, float grad_clip, int skip_nonfinite)
 {
     const Dims& d = L->d;
     AdamwScalars a;
@@ -92,6 +96,8 @@ int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float ep
     a.lrwd = lr * weight_decay;
     a.ms = 1.0f / (1.0f - std::pow(beta1, (float)t));
     a.vs = 1.0f / (1.0f - std::pow(beta2, (float)t));
+    a.clip = grad_clip;
+    a.skip_bad = skip_nonfinite;
     void** tab = (void**)L->d_opt;     // [m: Wg Wu Wd bg bu bd | v: same | router: w g m v for Wr, br][E]
     const int E = d.E, S = E < 2 ? 2 : E;          // table stride (the router rows hold two entries)
     auto T = [&](int i) { return tab + (size_t)i * S; };
@@ -112,11 +118,13 @@ int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float ep
         MGPT_LAUNCHED("adamw_matrix_kernel<Wd>");
         adamw_flat_kernel<<<dim3((d.H + 255) / 256, E), 256, 0, st>>>((float* const*)L->master.bg, (const float* const*)L->master.gbg,
                                                                       (float* const*)T(3), (float* const*)T(9), d.H, a);
+        MGPT_LAUNCHED("adamw_flat_kernel<bg>");
         adamw_flat_kernel<<<dim3((d.H + 255) / 256, E), 256, 0, st>>>((float* const*)L->master.bu, (const float* const*)L->master.gbu,
                                                                       (float* const*)T(4), (float* const*)T(10), d.H, a);
+        MGPT_LAUNCHED("adamw_flat_kernel<bu>");
         adamw_flat_kernel<<<dim3((d.C + 255) / 256, E), 256, 0, st>>>((float* const*)L->master.bd, (const float* const*)L->master.gbd,
                                                                       (float* const*)T(5), (float* const*)T(11), d.C, a);
-        MGPT_LAUNCHED("adamw_flat_kernel<biases>");
+        MGPT_LAUNCHED("adamw_flat_kernel<bd>");
     }
     if (L->router_bound) {
         // router tables: rows 12..15 hold {w, g, m, v}, entry 0 = Wr, entry 1 = br
@@ -125,8 +133,9 @@ int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float ep
         float* const* rm = (float* const*)T(14);
         float* const* rv = (float* const*)T(15);
         adamw_flat_kernel<<<dim3((d.C * E + 255) / 256, 1), 256, 0, st>>>(rw, rg, rm, rv, d.C * E, a);
+        MGPT_LAUNCHED("adamw_flat_kernel<Wr>");
         adamw_flat_kernel<<<dim3((E + 255) / 256, 1), 256, 0, st>>>(rw + 1, rg + 1, rm + 1, rv + 1, E, a);
-        MGPT_LAUNCHED("adamw_flat_kernel<router>");
+        MGPT_LAUNCHED("adamw_flat_kernel<br>");
     }
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return cuda_fail(err, "adamw launch");

@@ -143,6 +143,23 @@ int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
     L->shadow = L->master;
     L->shadow.Wg = (const void**)tab(12); L->shadow.Wu = (const void**)tab(13); L->shadow.Wd = (const void**)tab(14);
 
+    // error word of the layer's kernels (zero until something goes wrong) and the pinned word it is read into
+    e = cudaMalloc(&L->d_status, 256);
+    if (e == cudaSuccess) e = cudaMemset(L->d_status, 0, 256);
+    if (e == cudaSuccess) e = cudaHostAlloc(&L->h_status, sizeof(int32_t), cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        mgpt_moe_destroy(L);
+        return cuda_fail(e, "cudaMalloc(status)");
+    }
+    *L->h_status = 0;
+    if (cfg->mode == MGPT_MOE_BF16 && cfg->gemm_impl == 0) {
+        const int rc = tc_init(L);      // kernel attributes and the zeroed work-item counters, before any launch
+        if (rc != 0) {
+            mgpt_moe_destroy(L);
+            return rc;
+        }
+    }
     if (cfg->mode == MGPT_MOE_BF16) {
         e = cudaMalloc(&L->sWr, (size_t)C * ((E + 7) / 8 * 8) * sizeof(bf16));
         if (e != cudaSuccess) {
@@ -170,6 +187,8 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
     tc_destroy(L);
     cudaFree(L->d_tables);
     cudaFree(L->d_opt);
+    cudaFree(L->d_status);
+    if (L->h_status) cudaFreeHost(L->h_status);
     cudaFree(L->sWg); cudaFree(L->sWu); cudaFree(L->sWd);
     cudaFree(L->sWgT); cudaFree(L->sWuT); cudaFree(L->sWdT);
     cudaFree(L->sWr);
@@ -288,6 +307,17 @@ int mgpt_moe_adamw_step(mgpt_moe_layer* L, float lr, float beta1, float beta2, f
     return launch_adamw(L, lr, beta1, beta2, eps, weight_decay, t, (cudaStream_t)stream);
 }
 
+int mgpt_moe_adamw_step_guarded(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay,
+                                int t, float grad_clip, int skip_nonfinite, mgpt_stream_t stream)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (!L->opt_bound) return fail(MGPT_MOE_ESTATE, "bind_optimizer_state first");
+    if (t < 1) return fail(MGPT_MOE_EINVAL, "the step count starts at 1");
+    if (!(grad_clip >= 0.0f)) return fail(MGPT_MOE_EINVAL, "grad_clip must be >= 0 (0 = no clamp)");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    return launch_adamw(L, lr, beta1, beta2, eps, weight_decay, t, (cudaStream_t)stream, grad_clip, skip_nonfinite);
+}
+
 int mgpt_moe_sync_weights(mgpt_moe_layer* L, mgpt_stream_t stream)
 {
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
@@ -341,6 +371,50 @@ static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, s
     if (L->d.mode == MGPT_MOE_BF16 && !L->shadows_fresh)
         return fail(MGPT_MOE_ESTATE, "sync_weights after bind_params / optimiser step");
     return 0;
+}
+
+static std::string describe_status(int32_t bits)
+{
+    std::string m = "a kernel of this layer reported an error since the last check (status " + std::to_string(bits) + "):";
+    if (bits & ST_PLAN_OVERFLOW) m += " dispatch plan overflow;";
+    if (bits & ST_FULL_WAIT) m += " operand tiles never arrived (bounded wait ran out);";
+    if (bits & ST_EMPTY_WAIT) m += " an operand stage was never released (bounded wait ran out);";
+    if (bits & ST_ACC_WAIT) m += " an accumulator wait ran out;";
+    if (bits & ST_SCHED_WAIT) m += " the work-item queue stalled (bounded wait ran out);";
+    if (bits & ST_BAD_EXPERT) m += " an expert id outside [0, num_experts) was skipped;";
+    m += " outputs and gradients of the affected step are incomplete";
+    return m;
+}
+
+// Reads the layer's error word on `st`; the caller synchronises `st` afterwards and calls status_result().
+static int status_fetch(mgpt_moe_layer* L, cudaStream_t st)
+{
+    MGPT_CUDA(cudaMemcpyAsync(L->h_status, L->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    return 0;
+}
+static int status_result(mgpt_moe_layer* L, cudaStream_t st, int32_t* bits_out)
+{
+    const int32_t bits = *L->h_status;
+    if (bits_out) *bits_out = bits;
+    if (bits == 0) return 0;
+    cudaMemsetAsync(L->d_status, 0, sizeof(int32_t), st);      // reported once
+    return fail(MGPT_MOE_ECUDA, describe_status(bits));
+}
+
+int mgpt_moe_check_status(mgpt_moe_layer* L, int32_t* bits)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    MGPT_TRY(status_fetch(L, L->last_stream));
+    MGPT_CUDA(cudaStreamSynchronize(L->last_stream));
+    return status_result(L, L->last_stream, bits);
+}
+
+int mgpt_moe_selftest_bounded_wait(mgpt_moe_layer* L, mgpt_stream_t stream)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    return tc_selftest_bounded_wait(L, (cudaStream_t)stream);
 }
 
 // Routing results and plan of one forward: the workspace bytes from probs up to (not including) the plan's
@@ -419,7 +493,7 @@ static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens,
             L->stage_end(ST_ROUTER, st);
         }
         L->stage_begin(ST_PLAN, st);
-        MGPT_TRY(launch_plan(d, w, ws, st));
+        MGPT_TRY(launch_plan(d, w, ws, st, L->d_status));
         L->stage_end(ST_PLAN, st);
     }
     if (n_tokens > 0) {
@@ -478,8 +552,9 @@ int mgpt_moe_expert_counts(mgpt_moe_layer* L, int32_t* host_counts)
     const Workspace w = make_workspace(L->d, L->last_n);
     MGPT_CUDA(cudaMemcpyAsync(host_counts, (char*)L->last_ws + w.counts, (size_t)L->d.E * sizeof(int32_t),
                               cudaMemcpyDeviceToHost, L->last_stream));
+    MGPT_TRY(status_fetch(L, L->last_stream));
     MGPT_CUDA(cudaStreamSynchronize(L->last_stream));
-    return 0;
+    return status_result(L, L->last_stream, nullptr);
 }
 
 int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_host, void* y_host, void* dx_host,
@@ -538,8 +613,9 @@ int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_hos
     } else {
         MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, st));
     }
+    MGPT_TRY(status_fetch(L, st));
     MGPT_CUDA(cudaStreamSynchronize(st));
-    return 0;
+    return status_result(L, st, nullptr);
 }
 
 static const char* const kStageNames[ST_COUNT] = {
@@ -582,7 +658,9 @@ int mgpt_moe_stage_ms(mgpt_moe_layer* L, float* ms)
         MGPT_CUDA(cudaEventSynchronize(L->ev_end[s]));
         MGPT_CUDA(cudaEventElapsedTime(&ms[s], L->ev_begin[s], L->ev_end[s]));
     }
-    return 0;
+    // the stages just waited for have finished: a time measured on a step that reported an error is not a time
+    MGPT_CUDA(cudaMemcpy(L->h_status, L->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    return status_result(L, L->last_stream, nullptr);
 }
 
 int mgpt_moe_op_router(const void* x, int io, const float* Wr, const float* br, int n_tokens, int C, int E, int k,

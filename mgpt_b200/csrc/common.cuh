@@ -21,6 +21,17 @@ constexpr int MAX_TOPK = 8;
 constexpr int MAX_SOURCES = 64;  // source ranks an expert-side layer can receive row segments from
 constexpr int MAX_SEGMENTS = 4096;  // sources x local experts
 
+// Bits of the status words (the per-step word in the workspace and the layer's own, which keeps every bit
+// until mgpt_moe_check_status reads it).  A set bit means results of that step are incomplete.
+enum StatusBits {
+    ST_PLAN_OVERFLOW = 1,     // more row tiles than the workspace holds (cannot happen with a workspace of the stated size)
+    ST_FULL_WAIT = 2,         // a bounded wait of a tensor-core kernel ran out: operand tiles never arrived
+    ST_EMPTY_WAIT = 4,        //   ... a stage of the operand ring was never released
+    ST_ACC_WAIT = 8,          //   ... an accumulator was never completed / released
+    ST_SCHED_WAIT = 16,       //   ... the work-item queue stalled
+    ST_BAD_EXPERT = 32,       // an expert id outside [0, E) was met by the dispatch plan and skipped
+};
+
 enum Stage {
     ST_ROUTER = 0, ST_PLAN, ST_DISPATCH, ST_GATEUP, ST_DOWN, ST_COMBINE,
     ST_COMBINE_BWD, ST_DHH, ST_DXG, ST_WGRAD, ST_BIAS_GRAD, ST_ROUTER_BWD, ST_COUNT
@@ -99,6 +110,12 @@ struct mgpt_moe_layer {
     bool bound = false, has_grad = false, shadows_fresh = false;
     bool router_bound = false, experts_bound = false;
 
+    // Error bits of every kernel of this layer since the last mgpt_moe_check_status (device word, zero at create)
+    // and the pinned host word they are read into.
+    int32_t* d_status = nullptr;
+    int32_t* h_status = nullptr;
+    bool router_dx_attr = false;             // shared-memory opt-in of router_dx_kernel done on this layer's device
+
     // device tables: pointers to FP32 masters / grads per expert
     void* d_tables = nullptr;                // one allocation holding all tables
     void* d_opt = nullptr;                   // optimiser-state tables (m, v per tensor kind; router w, g, m, v)
@@ -166,13 +183,14 @@ int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const voi
                       void* dx, cudaStream_t st, const void* dXg_rows = nullptr, const int32_t* pos_rows = nullptr);
 
 // plan.cu
-int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st);
+int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st, int32_t* sticky);
 int launch_dispatch(const Dims& d, const Workspace& w, char* ws, const void* x, int io, cudaStream_t st);
 int launch_combine_fwd(const Dims& d, const Workspace& w, char* ws, void* y, int io, cudaStream_t st,
                        const void* residual = nullptr);
 int launch_combine_bwd(const Dims& d, const Workspace& w, char* ws, const void* dy, int io, cudaStream_t st);
 int launch_bias_grads(const mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
-int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st);
+int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st,
+                         int32_t* sticky);
 int gather_rows(const void* src, int src_io, const int32_t* row_src, const int32_t* n_tiles, int rows, int grid_rows,
                 int C, int k, void* dst, size_t act_bytes, cudaStream_t st);
 int combine_rows(const void* rows, const int32_t* pos, const float* top_p, int N, int C, int k, void* y, int io,
@@ -182,7 +200,8 @@ int combine_rows_backward(const void* dy, int io, const void* rows, const int32_
                           size_t act_bytes, cudaStream_t st);
 int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
              int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
-             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of);
+             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of,
+             int32_t* sticky);
 
 // gemm_simt.cu
 int simt_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
@@ -191,10 +210,12 @@ int simt_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaS
 // gemm_tc.cu (tcgen05 / TMEM / TMA)
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
 int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int tc_init(mgpt_moe_layer* L);
+int tc_selftest_bounded_wait(mgpt_moe_layer* L, cudaStream_t st);
 void tc_destroy(mgpt_moe_layer* L);
 int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st);
 int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
-                 cudaStream_t st);
+                 cudaStream_t st, float grad_clip = 0.0f, int skip_nonfinite = 0);
 int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dXg, const int32_t* pos, void* dx,
                  cudaStream_t st);
 int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st);

@@ -42,7 +42,7 @@ constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-17 epilogue
 
-enum { ERR_FULL_WAIT = 2, ERR_EMPTY_WAIT = 4, ERR_ACC_WAIT = 8, ERR_SCHED_WAIT = 16 };
+enum { ERR_FULL_WAIT = ST_FULL_WAIT, ERR_EMPTY_WAIT = ST_EMPTY_WAIT, ERR_ACC_WAIT = ST_ACC_WAIT, ERR_SCHED_WAIT = ST_SCHED_WAIT };
 constexpr int SCHED_Q = 8;                           // queue entries: the producer runs up to ~4 items ahead of the slowest epilogue warp
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -69,9 +69,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait: returns false (and records why) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status, int code,
+                                          uint32_t limit = SPIN_LIMIT)
 {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try(bar, parity)) return true;
     atomicOr(status, code);
     return false;
@@ -924,8 +925,12 @@ int prepare_attrs(mgpt_moe_layer* L)
         MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
+        // the work-item counters must read zero before the first launch on any stream: allocate and clear them
+        // here, at layer creation, and wait for the clear (nothing orders the legacy stream with a caller's
+        // non-blocking stream)
         MGPT_CUDA(cudaMalloc(&s->sched, 64 * sizeof(int32_t)));
         MGPT_CUDA(cudaMemset(s->sched, 0, 64 * sizeof(int32_t)));
+        MGPT_CUDA(cudaDeviceSynchronize());
         s->attr_set = true;
     }
     return 0;
@@ -947,7 +952,7 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
-    p.status = (int32_t*)(ws + w.status);
+    p.status = L->d_status;
     // gate/up + SwiGLU: K = C, 128 hidden units per item
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN / 2);
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
@@ -979,7 +984,7 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
-    p.status = (int32_t*)(ws + w.status);
+    p.status = L->d_status;
     // dHh = dYg * Wd^T  (K = C), SwiGLU backward in the epilogue
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN);
     p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
@@ -1005,7 +1010,7 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     g.padded_offsets = (const int32_t*)(ws + w.padded_offsets);
     g.seg = (const int32_t*)(ws + w.seg);
     g.n_seg = L->n_seg;
-    g.status = (int32_t*)(ws + w.status);
+    g.status = L->d_status;
     g.n_probs = 3;
     float* const* grads[3] = {L->master.gWg, L->master.gWu, L->master.gWd};
     int items = 0;
@@ -1046,7 +1051,7 @@ int tc_router_dx(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* dX
     RowsP p = {};
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
-    p.status = (int32_t*)(ws + w.status);
+    p.status = L->d_status;
     p.kblocks = cdiv(E8, BK); p.n_out = d.C; p.b_rows_per_expert = 0; p.n_col_tiles = cdiv(d.C, BN);
     p.fixed_tiles = cdiv(w.n_tokens, BM); p.n_valid_rows = w.n_tokens;
     p.gather_src = (const bf16*)dXg; p.gather_pos = pos; p.gather_k = d.k;
@@ -1068,7 +1073,7 @@ int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void*
     MGPT_TRY(make_map(&mA, x, (uint64_t)w.n_tokens, (uint64_t)d.C, 64));
     MGPT_TRY(make_map(&mB, ws + w.dl16, (uint64_t)w.n_tokens, (uint64_t)E8, 64));
     WgradP g = {};
-    g.status = (int32_t*)(ws + w.status);
+    g.status = L->d_status;
     g.n_probs = 1;
     WgradProb& q = g.prob[0];
     q.M = d.C; q.N = d.E; q.n_tiles_m = cdiv(d.C, BM); q.n_tiles_n = cdiv(d.E, BN);
@@ -1083,6 +1088,29 @@ int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void*
     MGPT_LAUNCHED("tc_wgrad_kernel<Wr>");
     return 0;
 }
+
+// One barrier nothing ever arrives on, waited for with the kernels' own bounded wait and a short limit: the wait
+// runs out after a few thousand polls, the error bit is set and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int32_t* status)
+{
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait(smem_u32(&bar), 0, status, ERR_FULL_WAIT, 1u << 12);
+    }
+}
+
+int tc_selftest_bounded_wait(mgpt_moe_layer* L, cudaStream_t st)
+{
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(L->d_status);
+    MGPT_LAUNCHED("bounded_wait_selftest_kernel");
+    L->last_stream = st;
+    return 0;
+}
+
+// Called once from mgpt_moe_create (the layer's device is current): function attributes, SM count, work counters.
+int tc_init(mgpt_moe_layer* L) { return prepare_attrs(L); }
 
 void tc_destroy(mgpt_moe_layer* L)
 {

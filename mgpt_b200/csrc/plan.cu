@@ -40,7 +40,10 @@ plan_count_kernel(const int32_t* __restrict__ top_idx, int R, int E, int32_t* __
     if (threadIdx.x < E) cnt[threadIdx.x] = 0;
     __syncthreads();
     const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
-    if (i < R) atomicAdd(&cnt[top_idx[i]], 1);
+    if (i < R) {
+        const int e = top_idx[i];
+        if ((unsigned)e < (unsigned)E) atomicAdd(&cnt[e], 1);      // ids outside [0, E) are reported by plan_assign_kernel
+    }
     __syncthreads();
     if (threadIdx.x < E) blk_cnt[(size_t)blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
 }
@@ -50,7 +53,8 @@ __global__ void __launch_bounds__(MAX_EXPERTS)
 plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
                  int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert,
-                 int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ status)
+                 int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ status,
+                 int32_t* __restrict__ sticky)
 {
     __shared__ int tot[MAX_EXPERTS];
     __shared__ int poff[MAX_EXPERTS + 1];
@@ -79,7 +83,8 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
         padded_offsets[E] = p;
         const int nt = p / ROW_TILE;
         *n_tiles = nt;
-        *status = nt > max_tiles ? 1 : 0;          // cannot happen: max_tiles bounds sum(ceil); also clears the word
+        *status = nt > max_tiles ? ST_PLAN_OVERFLOW : 0;      // cannot happen: max_tiles bounds sum(ceil); also clears the word
+        if (sticky && nt > max_tiles) atomicOr(sticky, ST_PLAN_OVERFLOW);
     }
     __syncthreads();
     if (e < E) {
@@ -91,18 +96,24 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
 // (3) stable rank of every flat index within its expert -> map / pos / row_src
 __global__ void __launch_bounds__(PLAN_BLOCK)
 plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
-                   const int32_t* __restrict__ blk_base, const int32_t* __restrict__ offsets,
-                   const int32_t* __restrict__ padded_offsets,
+                   const int32_t* __restrict__ blk_base, const int32_t* __restrict__ counts,
+                   const int32_t* __restrict__ offsets, const int32_t* __restrict__ padded_offsets,
                    int32_t* __restrict__ map, int32_t* __restrict__ pos, int32_t* __restrict__ row_src,
-                   int32_t* __restrict__ slot_of)
+                   int32_t* __restrict__ slot_of, int32_t* __restrict__ status, int32_t* __restrict__ sticky)
 {
     __shared__ int warp_cnt[PLAN_BLOCK / 32][MAX_EXPERTS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < (PLAN_BLOCK / 32) * MAX_EXPERTS; i += PLAN_BLOCK) (&warp_cnt[0][0])[i] = 0;
     __syncthreads();
     const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
-    const bool valid = i < R;
-    const int e = valid ? top_idx[i] : -1 - lane;                 // distinct keys for idle lanes
+    bool valid = i < R;
+    int e = valid ? top_idx[i] : 0;
+    if (valid && (unsigned)e >= (unsigned)E) {                    // an id no expert has: no slot, and the caller is told
+        atomicOr(status, ST_BAD_EXPERT);
+        if (sticky) atomicOr(sticky, ST_BAD_EXPERT);
+        valid = false;
+    }
+    if (!valid) e = -1 - lane;                                    // distinct keys for idle lanes
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
     if (valid && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
@@ -121,9 +132,7 @@ plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
     // padding rows of every expert's segment carry no source (block 0, one thread per expert)
     if (blockIdx.x == 0 && threadIdx.x < E) {
         const int e2 = threadIdx.x;
-        const int cnt = offsets[e2 + 1 < E ? e2 + 1 : e2] - offsets[e2];      // compact count (last expert: below)
-        const int real = e2 + 1 < E ? cnt : R - offsets[e2];
-        for (int q = padded_offsets[e2] + real; q < padded_offsets[e2 + 1]; ++q) row_src[q] = -1;
+        for (int q = padded_offsets[e2] + counts[e2]; q < padded_offsets[e2 + 1]; ++q) row_src[q] = -1;
     }
 }
 
@@ -336,26 +345,28 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(BiasGradArgs a)
 // every element is written by plan_count_kernel before it is read, so it needs no clearing.
 int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
              int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
-             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of)
+             int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of,
+             int32_t* sticky)
 {
     const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
     (void)row_cap;      // rows beyond the plan's tiles are never read; padding rows are marked by plan_assign_kernel
     plan_count_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
     MGPT_LAUNCHED("plan_count_kernel");
     plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, plan_blocks, E, counts, offsets, padded_offsets, tile_expert,
-                                                n_tiles, max_tiles, status);
+                                                n_tiles, max_tiles, status, sticky);
     MGPT_LAUNCHED("plan_scan_kernel");
-    plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, offsets, padded_offsets, map, pos, row_src, slot_of);
+    plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, counts, offsets, padded_offsets, map, pos,
+                                                           row_src, slot_of, status, sticky);
     MGPT_LAUNCHED("plan_assign_kernel");
     return 0;
 }
 
-int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st)
+int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st, int32_t* sticky)
 {
     return run_plan((const int32_t*)(ws + w.top_idx), w.R, d.E, (int32_t*)(ws + w.counts), (int32_t*)(ws + w.offsets),
                     (int32_t*)(ws + w.padded_offsets), (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
                     w.max_tiles, (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos), (int32_t*)(ws + w.row_src),
-                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st, (int32_t*)(ws + w.slot));
+                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st, (int32_t*)(ws + w.slot), sticky);
 }
 
 // dst[p,:] = src[row_src[p]/k,:] for p < rows (zero where row_src[p] < 0).  rows < 0: every tile of the plan.
@@ -463,7 +474,7 @@ __global__ void __launch_bounds__(256)
 segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, int32_t* __restrict__ counts,
                      int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_order,
                      int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ seg,
-                     int32_t* __restrict__ status)
+                     int32_t* __restrict__ status, int32_t* __restrict__ sticky)
 {
     __shared__ int first_tile[MAX_SEGMENTS + 1];     // in arrival order (s, e)
     __shared__ int first_item[MAX_SEGMENTS];         // in processing order (e, s)
@@ -476,7 +487,8 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
         }
         first_tile[n] = t;
         *n_tiles = t;
-        *status = t > max_tiles ? 1 : 0;
+        *status = t > max_tiles ? ST_PLAN_OVERFLOW : 0;
+        if (sticky && t > max_tiles) atomicOr(sticky, ST_PLAN_OVERFLOW);
         int it = 0;
         for (int e = 0; e < E; ++e)
             for (int s_ = 0; s_ < n_src; ++s_) {
@@ -504,13 +516,14 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
     }
 }
 
-int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st)
+int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st,
+                         int32_t* sticky)
 {
     if (n_src * d.E > MAX_SEGMENTS) return fail(MGPT_MOE_EINVAL, "sources x local experts must not exceed 4096");
     segment_tiles_kernel<<<1, 256, 0, st>>>(seg_counts, n_src, d.E, (int32_t*)(ws + w.counts),
                                             (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.tile_order),
                                             (int32_t*)(ws + w.n_tiles), w.max_tiles, (int32_t*)(ws + w.seg),
-                                            (int32_t*)(ws + w.status));
+                                            (int32_t*)(ws + w.status), sticky);
     MGPT_LAUNCHED("segment_tiles_kernel");
     return 0;
 }
@@ -549,7 +562,7 @@ extern "C" int mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E, int32
     if (scratch_bytes < mgpt_moe_op_plan_scratch_bytes(n_rows, E))
         return fail(MGPT_MOE_ENOMEM, "scratch smaller than mgpt_moe_op_plan_scratch_bytes()");
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream, nullptr);
+                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream, nullptr, nullptr);
 }
 
 // ---- dispatch plan without any allocation ------------------------------------------
@@ -602,5 +615,5 @@ extern "C" int mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int 
     // The array still holds the previous call's block bases.  Nothing has to be cleared:
     // plan_count_kernel writes all plan_blocks*E entries this call reads before they are read.
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream, nullptr);
+                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream, nullptr, nullptr);
 }

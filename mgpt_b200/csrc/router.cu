@@ -562,12 +562,11 @@ int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const voi
         const int chunk = DX_WS_FLOATS / epad;                 // channels per CTA (multiple of 8)
         dim3 grid((N + DX_TOK - 1) / DX_TOK, (C + chunk - 1) / chunk);
         const size_t sm = (size_t)(DX_WS_FLOATS + 4 * MAX_EXPERTS + DX_TOK * E) * sizeof(float);
-        static bool attr_done = false;
-        if (!attr_done) {
+        if (!L->router_dx_attr) {                   // a per-device attribute: one opt-in per layer (layers live on one device)
             MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
             MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
             MGPT_CUDA(cudaFuncSetAttribute(router_dx_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
-            attr_done = true;
+            L->router_dx_attr = true;
         }
         if (w.act_bytes == 4) {
             router_dx_kernel<float, float><<<grid, 256, sm, st>>>((const float*)dXg, pos, dl, Wr, N, C, E, k, chunk, (float*)dx);

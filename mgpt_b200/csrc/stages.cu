@@ -72,7 +72,7 @@ int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void*
     if (n_tokens > 0)
         MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k, (float*)(ws + w.logits),
                                    (float*)(ws + w.probs), (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
-    MGPT_TRY(launch_plan(d, w, ws, st));
+    MGPT_TRY(launch_plan(d, w, ws, st, L->d_status));
     // expert-major rows, each expert padded to whole tiles with zero rows; stable within an expert
     MGPT_TRY(gather_rows(x, io, (const int32_t*)(ws + w.row_src), (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, d.C,
                          d.k, send_rows, w.act_bytes, st));
@@ -148,7 +148,7 @@ int mgpt_moe_experts_forward(mgpt_moe_layer* L, const void* rows, const int32_t*
     L->n_seg = n_src;
     // tile -> expert table in arrival order and every expert's segment list, from the real counts
     L->stage_begin(ST_PLAN, st);
-    MGPT_TRY(launch_segment_tiles(d, w, ws, seg_counts, n_src, st));
+    MGPT_TRY(launch_segment_tiles(d, w, ws, seg_counts, n_src, st, L->d_status));
     L->stage_end(ST_PLAN, st);
     if (n_rows > 0) {
         if (d.mode == MGPT_MOE_BF16 && d.gemm_impl == 0) MGPT_TRY(tc_experts_forward(L, w, ws, st));

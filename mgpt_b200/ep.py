@@ -137,6 +137,11 @@ class CudaStages:
         self._lib_mod.check(self.lib.mgpt_moe_workspace_view(handle, n, name.encode(), ct.byref(off), ct.byref(nb)))
         return ws[off.value: off.value + nb.value].view(dtype)
 
+    def check_status(self) -> None:
+        """Raises if a kernel of the routing side or of any expert chunk reported an error since the last check."""
+        for h in [self.home] + self.locals:
+            self._lib_mod.check(self.lib.mgpt_moe_check_status(h, None))
+
     # ---- per-stage timing of the expert side (CUDA events inside the library)
     def set_profiling(self, enabled: bool) -> None:
         for h in self.locals:

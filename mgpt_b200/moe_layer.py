@@ -90,11 +90,12 @@ class MoELayer:
 
     # -- optimiser -----------------------------------------------------------
     def adamw_step(self, t: int, lr: float = 3e-4, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
-                   weight_decay: float = 0.01):
+                   weight_decay: float = 0.01, grad_clip: float = 0.0, skip_nonfinite: bool = False):
         """One AdamW step over this layer's parameters (defaults and arithmetic of the reference's
         AdamWOptimizer, optimisers/AdamWOptimiser.h:21-36), fused with the refresh of the BF16 copies:
         no ``sync_weights`` is needed afterwards.  ``t`` counts steps from 1; the moment buffers
-        ``self.opt_m`` / ``self.opt_v`` are created (zero) on first use."""
+        ``self.opt_m`` / ``self.opt_v`` are created (zero) on first use.  ``grad_clip`` / ``skip_nonfinite``
+        apply the guards of the reference's GPU kernel (utils/cuda_ops.cu:727-728) to the gradient first."""
         if getattr(self, "opt_m", None) is None:
             self.opt_m = [torch.zeros_like(p) for p in self.params]
             self.opt_v = [torch.zeros_like(p) for p in self.params]
@@ -102,7 +103,11 @@ class MoELayer:
             m = (ct.c_void_p * n)(*[a.data_ptr() for a in self.opt_m])
             v = (ct.c_void_p * n)(*[a.data_ptr() for a in self.opt_v])
             _lib.check(self.lib.mgpt_moe_bind_optimizer_state(self._h, m, v, n))
-        _lib.check(self.lib.mgpt_moe_adamw_step(self._h, lr, beta1, beta2, eps, weight_decay, int(t), self._stream()))
+        if grad_clip or skip_nonfinite:
+            _lib.check(self.lib.mgpt_moe_adamw_step_guarded(self._h, lr, beta1, beta2, eps, weight_decay, int(t),
+                                                            float(grad_clip), int(bool(skip_nonfinite)), self._stream()))
+        else:
+            _lib.check(self.lib.mgpt_moe_adamw_step(self._h, lr, beta1, beta2, eps, weight_decay, int(t), self._stream()))
 
     # -- memory ------------------------------------------------------------
     def get_footprint(self, B: int, T: int) -> int:
@@ -192,6 +197,17 @@ class MoELayer:
         buf = (ct.c_int32 * self.E)()
         _lib.check(self.lib.mgpt_moe_expert_counts(self._h, buf))
         return list(buf)
+
+    def check_status(self) -> None:
+        """Raises MoeError if a kernel of this layer reported an error since the last check (a bounded wait
+        that ran out, an expert id out of range); synchronises the stream of the last call."""
+        _lib.check(self.lib.mgpt_moe_check_status(self._h, None))
+
+    def status_bits(self) -> int:
+        """The error word itself (0 = ok); reading clears it."""
+        bits = ct.c_int32(0)
+        self.lib.mgpt_moe_check_status(self._h, ct.byref(bits))
+        return int(bits.value)
 
     def set_profiling(self, enabled: bool) -> None:
         _lib.check(self.lib.mgpt_moe_set_profiling(self._h, 1 if enabled else 0))

@@ -66,6 +66,28 @@ def _normal(seed: int, tensor_id: int, shape, std: float) -> np.ndarray:
     return a
 
 
+def make_param(w: Workload, i: int, seed: int = 1234, bias_std: float = 0.0) -> np.ndarray:
+    """Parameter tensor ``i`` (index in the 2+6E order) of ``make_inputs(w, seed, bias_std)``, alone: what an
+    expert-parallel rank calls for the tensors it owns."""
+    s = param_shapes(w.C, w.H, w.E)[i]
+    if s[0] == 1:
+        p = _normal(seed, 2 + i, s, bias_std) if bias_std > 0 else np.zeros(s, np.float32)
+        if i == 1 and w.skew:
+            p = p + (2.0 * np.log(1.0 / (np.arange(w.E, dtype=np.float64) + 1.0))).astype(np.float32)[None, :]
+    else:
+        p = _normal(seed, 2 + i, s, 0.02)
+    return bf16_round(p) if w.dtype == "bf16" else p
+
+
+def make_tokens(w: Workload, seed: int = 1234):
+    """(x, dy) of ``make_inputs(w, seed)``, alone."""
+    x = _normal(seed, 0, (w.n_tokens, w.C), 1.0)
+    dy = _normal(seed, 1, (w.n_tokens, w.C), 1.0)
+    if w.dtype == "bf16":
+        x, dy = bf16_round(x), bf16_round(dy)
+    return x, dy
+
+
 def make_inputs(w: Workload, seed: int = 1234, bias_std: float = 0.0):
     """Returns (x [N,C], params list, dy [N,C]) as float32 arrays.
 

@@ -61,10 +61,29 @@ def param_shapes(C: int, H: int, E: int):
     return shapes
 
 
+ENGINE_BIN = os.path.join(HERE, "_ref", "engine_moe_driver")
+
+
+def reference_dir():
+    """Checkout of the reference to compile ``_ref`` from: ``$MGPT_REFERENCE_DIR``, else a directory named
+    ``reference`` beside this repository.  None when neither has the MoE layer's sources."""
+    cands = [os.environ.get("MGPT_REFERENCE_DIR"),
+             os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "src", "main", "neuralnetwork", "layers", "MoELayer.cpp")):
+            return c
+    return None
+
+
 def build(ref: bool = True) -> None:
-    """Compile liboracle.so (and _ref/libmgpt_ref.so when the reference sources are present)."""
-    target = ["all"] if ref else [ORACLE_SO]
-    subprocess.run(["make", "-C", HERE] + target, check=True, stdout=subprocess.DEVNULL)
+    """Compile liboracle.so and, when a checkout of the reference is at hand, ``_ref/libmgpt_ref.so`` (its own
+    MoELayer, CPU arm) and ``_ref/engine_moe_driver`` (its engine around this repository's adapter; needs the
+    CUDA library built first)."""
+    rd = reference_dir() if ref else None
+    if rd is None:
+        subprocess.run(["make", "-C", HERE, ORACLE_SO], check=True, stdout=subprocess.DEVNULL)
+    else:
+        subprocess.run(["make", "-C", HERE, "all", f"REF={rd}"], check=True, stdout=subprocess.DEVNULL)
 
 
 def have_ref() -> bool:

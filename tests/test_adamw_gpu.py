@@ -69,3 +69,38 @@ def test_adamw_needs_state_and_valid_step():
         _lib.check(layer.lib.mgpt_moe_adamw_step(layer._h, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1, None))
     with pytest.raises(_lib.MoeError):
         layer.adamw_step(0)
+
+
+def test_guarded_step_skips_nonfinite_and_clamps_like_the_gpu_arm():
+    """utils/cuda_ops.cu:727-728: an element whose gradient is NaN or Inf is left untouched, the others see the
+    gradient clamped to [-10, 10]; after the guards the arithmetic is the CPU arm's, bit for bit."""
+    w = synth.Workload("adamw3", 64, 64, 72, 2, 1, "bf16")
+    _, params, _ = synth.make_inputs(w, seed=3, bias_std=0.02)
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode="bf16")
+    layer.load_parameters(params)
+    rng = np.random.default_rng(1)
+    grads = []
+    for p in layer.get_parameters():
+        g = (rng.standard_normal(p.shape) * 8.0).astype(np.float32)        # a good share beyond +-10
+        flat = g.reshape(-1)
+        flat[:: 7] = np.nan
+        flat[3:: 11] = np.inf
+        flat[5:: 13] = -np.inf
+        p.grad.copy_(torch.from_numpy(g))
+        grads.append(g)
+    layer.adamw_step(1, grad_clip=10.0, skip_nonfinite=True, **HYPER)
+    torch.cuda.synchronize()
+    for i, (p0, g) in enumerate(zip(params, grads)):
+        ok = np.isfinite(g).reshape(-1)
+        gc = np.clip(np.where(np.isfinite(g), g, 0.0), -10.0, 10.0).astype(np.float32)
+        nw, nm, nv = oracle.adamw(p0, gc, np.zeros_like(p0), np.zeros_like(p0), t=1, **HYPER)
+        want_w = np.where(ok, nw, p0.reshape(-1))
+        want_m = np.where(ok, nm, 0.0).astype(np.float32)
+        got_w = layer.get_parameters()[i].cpu().numpy().reshape(-1)
+        assert np.array_equal(_bits(got_w), _bits(want_w)), f"parameter {i}"
+        assert np.array_equal(_bits(layer.opt_m[i].cpu().numpy().reshape(-1)), _bits(want_m)), f"m of {i}"
+    # the BF16 copies were written from the guarded result: forward agrees with a fresh sync
+    x = torch.randn(w.n_tokens, w.C, device="cuda").bfloat16()
+    y0 = layer.forward(x).clone()
+    layer.sync_weights()
+    assert torch.equal(y0, layer.forward(x))

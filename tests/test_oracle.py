@@ -129,3 +129,19 @@ def test_adamw_restatement_matches_golden():
                                eps=float(z["eps"]), weight_decay=float(z["weight_decay"]), t=t)
     for got, want in ((w, z["w3"]), (m, z["m3"]), (v, z["v3"])):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_seeded_tokens_have_the_prefix_property():
+    """bench.py checks the first rows of a full-size run against the oracle run on a token subset: the generator's
+    first rows must not depend on the token count, and the per-tensor generators must equal make_inputs."""
+    from mgpt_b200 import synth
+    w = synth.WORKLOADS["c2"]
+    x, params, dy = synth.make_inputs(w)
+    xs, _, dys = synth.make_inputs(w.scaled(300))
+    assert np.array_equal(x[:300], xs) and np.array_equal(dy[:300], dys)
+    xt, dyt = synth.make_tokens(w)
+    assert np.array_equal(x, xt) and np.array_equal(dy, dyt)
+    for i in (0, 1, 2, 3, 6, 7, len(params) - 1):
+        assert np.array_equal(params[i], synth.make_param(w, i))
+    w3 = synth.WORKLOADS["c3"].scaled(16)
+    assert np.array_equal(synth.make_inputs(w3)[1][1], synth.make_param(w3, 1))

@@ -36,7 +36,6 @@ def run_layer(w, x, params, dy, *, mode, gemm_impl=0, io=torch.float32):
     out["map"] = layer.workspace_view("map", i32).cpu().numpy()
     out["padded_offsets"] = layer.workspace_view("padded_offsets", i32).cpu().numpy()
     out["pos"] = layer.workspace_view("pos", i32).cpu().numpy()
-    out["status"] = int(layer.workspace_view("status", i32).cpu().numpy()[0])
     if dy is not None:
         dyt = torch.from_numpy(dy).cuda().to(io).contiguous()
         dx = layer.backward(dyt)
@@ -45,6 +44,8 @@ def run_layer(w, x, params, dy, *, mode, gemm_impl=0, io=torch.float32):
         out["d_top_p"] = layer.workspace_view("d_top_p", f32, (N, k)).cpu().numpy()
         out["dlogits"] = layer.workspace_view("dlogits", f32, (N, E)).cpu().numpy()
     torch.cuda.synchronize()
+    # the per-step word of the plan in the workspace, and every bit any kernel of the layer has set since creation
+    out["status"] = int(layer.workspace_view("status", i32).cpu().numpy()[0]) | layer.status_bits()
     return out
 
 
