@@ -353,6 +353,9 @@ def single_gpu_pass(args, w, rank, dev, *, light=False):
                   steps=min(args.steps, 10) if light else None, warmup=3 if light else None, sample_clocks=not light)
     layer.check_status()
     res["experts_touched"] = sum(1 for c in counts if c > 0)
+    if w.dtype == "bf16":
+        # tokens whose routing the tensor-core pass of the router could not prove and the exact pass recomputed
+        res["router_recomputed"] = int(layer.workspace_view("router_recompute", torch.int32).cpu()[0])
     res["counts"] = counts
     res["y"], res["dx"] = y, (dx if w.backward else None)          # of the last timed step (device tensors)
     res["recompute"] = time_recompute(layer, x, torch.empty_like(y)) if w.backward and not args.no_optimizer and not light else None
@@ -456,6 +459,8 @@ def score(w, res, peaks, world):
             ent["tflops"] = round(flops[name] / (ms * 1e-3) / 1e12, 1)
         elif name in byts and world == 1:
             ent["gbs"] = round(byts[name] / (ms * 1e-3) / 1e9, 1)
+        if name == "router" and "router_recomputed" in res:
+            ent["tokens_recomputed_exactly"] = res["router_recomputed"]
         stages[name] = ent
     gemm = {k: v for k, v in stages.items() if k in flops}
     roofline = None

@@ -109,10 +109,13 @@ int  mgpt_moe_expert_counts(mgpt_moe_layer* layer, int32_t* host_counts);
 /* Offset and size of a named buffer inside the workspace for n_tokens, for
  * tests and for callers that read routing results in place. Names:
  * logits probs top_idx top_p counts offsets padded_offsets map pos row_src
- * tile_expert n_tiles Xg G U Hh Yg dYg dG dU dXg d_top_p dlogits status.
+ * tile_expert n_tiles Xg G U Hh Yg dYg dG dU dXg d_top_p dlogits status
+ * router_recompute (one int32: tokens the BF16-token router recomputed exactly).
  * Activation buffers are row-major [padded rows, width], except G and U on
  * the tensor-core path (mode BF16, gemm_impl 0), which only its own epilogues
- * read: [row tile][8-column chunk][128 rows][8 values]. */
+ * read: there the buffer named G holds U*sigmoid(G)*(1 + G*(1 - sigmoid(G))) and
+ * the buffer named U holds silu(G) -- the two factors backward multiplies dHh by
+ * (utils/Tensor.cpp:2020-2027) -- laid out [row tile][8-column chunk][128 rows][8 values]. */
 int  mgpt_moe_workspace_view(const mgpt_moe_layer* layer, int n_tokens, const char* name,
                              size_t* offset, size_t* bytes);
 
@@ -202,6 +205,16 @@ int  mgpt_moe_check_status(mgpt_moe_layer* layer, int32_t* bits);
  * counterpart. */
 int  mgpt_moe_selftest_bounded_wait(mgpt_moe_layer* layer, mgpt_stream_t stream);
 
+/* Expert weight gradients written instead of accumulated.  The reference adds into gradient tensors its trainer
+ * zeroed at the start of the step (Tensor::add_grad, utils/Tensor.cpp:638-650; pipeline/Trainer.cpp:303-305): a
+ * zero fill plus a read-modify-write of 12 bytes per expert weight.  With this switch on (tensor-core path only),
+ * backward STORES gWg, gWu and gWd of every expert (zeros for an expert without rows), which equals accumulating
+ * into zeroed tensors bit for bit and makes the caller's zero fill of those tensors unnecessary.  Only valid for
+ * the first backward after the caller's zero_grad: with gradient accumulation over micro-batches
+ * (pipeline/Trainer.cpp:311-325) later backwards must run with the switch off.  Bias and router gradients always
+ * accumulate.  Default off. */
+int  mgpt_moe_set_weight_grad_overwrite(mgpt_moe_layer* layer, int enabled);
+
 /* Upper bound on the CTAs of the persistent tensor-core kernels of this layer
  * (one CTA per SM; 0 = every SM, the default). A caller that overlaps these
  * kernels with communication kernels on another stream leaves SMs free for
@@ -286,6 +299,15 @@ int  mgpt_moe_experts_forward(mgpt_moe_layer* layer, const void* rows, const int
  * mgpt_moe_combine_backward writes it); accumulates the expert parameter gradients (MoELayer.cpp:159-181). */
 int  mgpt_moe_experts_backward(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
                                void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
+/* mgpt_moe_experts_backward in two calls, for callers that overlap the exchange with compute: _rows computes
+ * d_in_rows (everything the other GPUs are waiting for), _params then accumulates the expert parameter gradients
+ * from the same buffers; the caller starts sending d_in_rows back between the two.  Same arguments; calling
+ * _rows then _params equals one mgpt_moe_experts_backward.  (On the CUDA-core paths _rows does all the work.) */
+int  mgpt_moe_experts_backward_rows(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
+                                    void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+int  mgpt_moe_experts_backward_params(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
+                                      void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
 
 /* The same plan for callers that can neither pass scratch nor let the library
  * allocate: an engine whose arena already owns all device memory, or a step

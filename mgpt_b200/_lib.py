@@ -22,6 +22,7 @@ SYMBOLS = [
     "mgpt_moe_stage_workspace_bytes", "mgpt_moe_route", "mgpt_moe_combine", "mgpt_moe_combine_backward",
     "mgpt_moe_route_backward", "mgpt_moe_experts_forward", "mgpt_moe_experts_backward",
     "mgpt_moe_check_status", "mgpt_moe_adamw_step_guarded", "mgpt_moe_selftest_bounded_wait",
+    "mgpt_moe_set_weight_grad_overwrite", "mgpt_moe_experts_backward_rows", "mgpt_moe_experts_backward_params",
 ]
 PLAN_NOALLOC_MAX_ROWS = 1048576
 N_STAGES = 12
@@ -69,6 +70,7 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_launch_count.restype = ct.c_long
     lib.mgpt_moe_set_profiling.argtypes = [vp, i32]
     lib.mgpt_moe_set_sm_budget.argtypes = [vp, i32]
+    lib.mgpt_moe_set_weight_grad_overwrite.argtypes = [vp, i32]
     lib.mgpt_moe_forward_residual.argtypes = [vp, vp, vp, vp, i32, i32, vp, ct.c_size_t, vp]
     lib.mgpt_moe_routing_bytes.argtypes = [vp, i32]
     lib.mgpt_moe_routing_bytes.restype = ct.c_size_t
@@ -94,6 +96,8 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_route_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]
     lib.mgpt_moe_experts_forward.argtypes = [vp, vp, vp, i32, i32, vp, vp, sz, vp]
     lib.mgpt_moe_experts_backward.argtypes = [vp, vp, vp, vp, sz, vp]
+    lib.mgpt_moe_experts_backward_rows.argtypes = [vp, vp, vp, vp, sz, vp]
+    lib.mgpt_moe_experts_backward_params.argtypes = [vp, vp, vp, vp, sz, vp]
     lib.mgpt_moe_op_plan_noalloc.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
     _lib = lib
     return lib

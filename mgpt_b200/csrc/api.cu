@@ -60,6 +60,8 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     w.map = take(N * k * 4);
     w.pos = take(N * k * 4);
     w.row_src = take(rc * 4);
+    w.pairs = take((size_t)w.max_tiles * 8);           // part of the plan: inside the range save_routing copies
+    w.n_pairs = take(4);
     w.blk_cnt = take((size_t)w.plan_blocks * E * 4);
     w.slot = take(N * k * 4);
     w.seg = take(E * MAX_SOURCES * 2 * 4);
@@ -87,6 +89,8 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     }
     w.rw_part = take((size_t)w.rw_chunks * (C * E + E) * 4);
     w.dl16 = take(N * ((E + 7) / 8 * 8) * 2);          // dlogits in bf16 for the tensor-core router backward
+    w.rt_list = take(N * 4);                            // screened router: tokens recomputed by the exact pass
+    w.rt_count = take(4);
     w.total = off;
     return w;
 }
@@ -166,6 +170,19 @@ int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
             mgpt_moe_destroy(L);
             return cuda_fail(e, "cudaMalloc(router shadow)");
         }
+        if (cfg->gemm_impl == 0) {
+            L->router_ne = router_tc_ne(E);
+            const size_t pieces = (size_t)2 * L->router_ne * C * sizeof(bf16);
+            e = cudaMalloc(&L->sWrT2, pieces);
+            if (e == cudaSuccess) e = cudaMemset(L->sWrT2, 0, pieces);      // rows of experts beyond E stay zero
+            if (e == cudaSuccess) e = cudaMalloc(&L->d_rstat, 2 * sizeof(float));
+            if (e == cudaSuccess) e = cudaMemset(L->d_rstat, 0, 2 * sizeof(float));
+            if (e == cudaSuccess) e = cudaDeviceSynchronize();
+            if (e != cudaSuccess) {
+                mgpt_moe_destroy(L);
+                return cuda_fail(e, "cudaMalloc(router pieces)");
+            }
+        }
         const size_t n = (size_t)E * C * H;
         bf16** s[6] = {&L->sWg, &L->sWu, &L->sWd, &L->sWgT, &L->sWuT, &L->sWdT};
         for (auto p : s) {
@@ -192,6 +209,8 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
     cudaFree(L->sWg); cudaFree(L->sWu); cudaFree(L->sWd);
     cudaFree(L->sWgT); cudaFree(L->sWuT); cudaFree(L->sWdT);
     cudaFree(L->sWr);
+    cudaFree(L->sWrT2);
+    cudaFree(L->d_rstat);
     cudaFree(L->h_x); cudaFree(L->h_dy); cudaFree(L->h_y); cudaFree(L->h_dx); cudaFree(L->h_ws);
     for (int s = 0; s < ST_COUNT; ++s) {
         if (L->ev_begin[s]) cudaEventDestroy(L->ev_begin[s]);
@@ -346,7 +365,7 @@ int mgpt_moe_workspace_view(const mgpt_moe_layer* L, int n_tokens, const char* n
         {"row_src", w.row_src, rc * 4}, {"slot", w.slot, N * k * 4}, {"Xg", w.Xg, rc * C * ab}, {"G", w.G, rc * H * ab}, {"U", w.U, rc * H * ab},
         {"Hh", w.Hh, rc * H * ab}, {"Yg", w.Yg, rc * C * ab}, {"dYg", w.dYg, rc * C * ab}, {"dG", w.dG, rc * H * ab},
         {"dU", w.dU, rc * H * ab}, {"dXg", w.dXg, rc * C * ab}, {"d_top_p", w.d_top_p, N * k * 4},
-        {"dlogits", w.dlogits, N * E * 4},
+        {"dlogits", w.dlogits, N * E * 4}, {"router_recompute", w.rt_count, 4},
     };
     for (auto& t : tab)
         if (!strcmp(t.n, name)) {
@@ -418,7 +437,8 @@ int mgpt_moe_selftest_bounded_wait(mgpt_moe_layer* L, mgpt_stream_t stream)
 }
 
 // Routing results and plan of one forward: the workspace bytes from probs up to (not including) the plan's
-// scratch -- probs, top_idx, top_p, counts, offsets, padded_offsets, tile_expert, n_tiles, status, map, pos, row_src.
+// scratch -- probs, top_idx, top_p, counts, offsets, padded_offsets, tile_expert, n_tiles, status, map, pos, row_src,
+// pairs, n_pairs.
 static size_t routing_begin(const Workspace& w) { return w.probs; }
 static size_t routing_end(const Workspace& w) { return w.blk_cnt; }
 
@@ -487,9 +507,12 @@ static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens,
     } else {
         if (n_tokens > 0) {
             L->stage_begin(ST_ROUTER, st);
-            MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
-                                       (float*)(ws + w.logits), (float*)(ws + w.probs),
-                                       (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
+            if (tc_router_usable(L, x, io))
+                MGPT_TRY(tc_router_fwd(L, w, ws, x, st));
+            else
+                MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
+                                           (float*)(ws + w.logits), (float*)(ws + w.probs),
+                                           (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
             L->stage_end(ST_ROUTER, st);
         }
         L->stage_begin(ST_PLAN, st);
@@ -533,7 +556,7 @@ int mgpt_moe_backward(mgpt_moe_layer* L, const void* x, const void* dy, void* dx
     L->stage_end(ST_COMBINE_BWD, st);
     if (use_tc(L)) MGPT_TRY(tc_experts_backward(L, w, ws, st));
     else MGPT_TRY(simt_experts_backward(L, w, ws, st));
-    if (L->has_grad) {
+    if (L->has_grad && !(use_tc(L) && tc_fused_bias_grads(L->d))) {      // the tensor-core weight-gradient kernel sums the bias gradients itself
         L->stage_begin(ST_BIAS_GRAD, st);
         MGPT_TRY(launch_bias_grads(L, w, ws, st));
         L->stage_end(ST_BIAS_GRAD, st);
@@ -625,6 +648,14 @@ static const char* const kStageNames[ST_COUNT] = {
 const char* mgpt_moe_stage_name(int stage)
 {
     return (stage >= 0 && stage < ST_COUNT) ? kStageNames[stage] : "";
+}
+
+int mgpt_moe_set_weight_grad_overwrite(mgpt_moe_layer* L, int enabled)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    if (enabled && !use_tc(L)) return fail(MGPT_MOE_EINVAL, "only the tensor-core path (BF16 mode, gemm_impl 0) can overwrite");
+    L->bwd_overwrite = enabled != 0;
+    return 0;
 }
 
 int mgpt_moe_set_sm_budget(mgpt_moe_layer* L, int n_sms)

@@ -72,10 +72,12 @@ struct Workspace {
     // plan
     size_t counts, offsets, padded_offsets, tile_expert, n_tiles, status;
     size_t map, pos, row_src, blk_cnt, slot, seg, tile_order;
+    size_t pairs, n_pairs;      // row tiles two by two within an expert ({first, second or -1}), in processing order
     // forward activations (kept for backward)
     size_t Xg, G, U, Hh, Yg;
     // backward temporaries
     size_t dYg, dG, dU, dXg, d_top_p, dlogits, rw_part, dl16;
+    size_t rt_list, rt_count;   // screened router: tokens to recompute exactly, and how many
     size_t total;
     // derived sizes
     int n_tokens, R, max_tiles, row_cap, plan_blocks, rw_chunks;
@@ -115,6 +117,7 @@ struct mgpt_moe_layer {
     int32_t* d_status = nullptr;
     int32_t* h_status = nullptr;
     bool router_dx_attr = false;             // shared-memory opt-in of router_dx_kernel done on this layer's device
+    bool router_tc_attr = false;             // the same for tc_router_fwd_kernel
 
     // device tables: pointers to FP32 masters / grads per expert
     void* d_tables = nullptr;                // one allocation holding all tables
@@ -127,6 +130,9 @@ struct mgpt_moe_layer {
     mgpt::bf16 *sWg = nullptr, *sWu = nullptr, *sWd = nullptr;      // [E][C][H],[E][C][H],[E][H][C]
     mgpt::bf16 *sWgT = nullptr, *sWuT = nullptr, *sWdT = nullptr;   // [E][H][C],[E][H][C],[E][C][H]
     mgpt::bf16* sWr = nullptr;                                      // router weight [C][E8], E8 = E rounded up to 8
+    mgpt::bf16* sWrT2 = nullptr;     // router weight transposed and split in two BF16 pieces: [2][NE][C], Wr^T ~ hi + mid
+    float* d_rstat = nullptr;        // {max_e ||Wr[:,e]||_2, max_e |br[e]|}, slightly inflated (screened router's error bound)
+    int router_ne = 0;               // NE: experts rounded up to 16, 32, 64 or 128
 
     // last forward (for backward / counts)
     int last_n = 0, last_io = 0;
@@ -143,6 +149,7 @@ struct mgpt_moe_layer {
     // TMA descriptors (opaque, built per workspace pointer)
     void* tc_state = nullptr;
     int sm_budget = 0;                       // > 0: persistent kernels launch at most this many CTAs
+    bool bwd_overwrite = false;              // this backward writes the expert weight gradients instead of adding to them
 
     // expert side of an expert-parallel layer: row buffers owned by the caller (the exchange buffers) and the
     // number of row segments per expert (one per source rank); 0 = one contiguous padded range per expert
@@ -178,7 +185,14 @@ inline char* buf_dXg(const mgpt_moe_layer* L, const Workspace& w, char* ws) { re
 
 // router.cu
 int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, int N, int C, int E, int k,
-                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st);
+                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st,
+                      const int32_t* list = nullptr, const int32_t* list_count = nullptr);
+// router_tc.cu: the router for BF16 tokens -- tensor-core first pass plus exact recompute of the tokens whose
+// routing the first pass cannot prove
+bool tc_router_usable(const mgpt_moe_layer* L, const void* x, int io);
+int tc_router_fwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st);
+int launch_router_pieces(mgpt_moe_layer* L, cudaStream_t st);
+int router_tc_ne(int E);
 int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,
                       void* dx, cudaStream_t st, const void* dXg_rows = nullptr, const int32_t* pos_rows = nullptr);
 
@@ -201,7 +215,7 @@ int combine_rows_backward(const void* dy, int io, const void* rows, const int32_
 int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
              int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
              int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of,
-             int32_t* sticky);
+             int32_t* sticky, int32_t* pairs, int32_t* n_pairs);
 
 // gemm_simt.cu
 int simt_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
@@ -209,8 +223,9 @@ int simt_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaS
 
 // gemm_tc.cu (tcgen05 / TMEM / TMA)
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
-int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st);
+int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st, int phase = 3);
 int tc_init(mgpt_moe_layer* L);
+bool tc_fused_bias_grads(const Dims& d);
 int tc_selftest_bounded_wait(mgpt_moe_layer* L, cudaStream_t st);
 void tc_destroy(mgpt_moe_layer* L);
 int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st);

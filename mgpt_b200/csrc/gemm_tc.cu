@@ -9,7 +9,7 @@
 // expert backward (layers/MoELayer.cpp:94-118, 159-181; layers/SwiGLU.cpp:23-96;
 // layers/LinearLayer.cpp:23-80) becomes seven launches for all experts:
 //
-//   gate/up : [G|U] = Xg * [Wg|Wu] + [bg|bu],  Hh = silu(G)*U      (epilogue)
+//   gate/up : [G|U] = Xg * [Wg|Wu] + [bg|bu],  Hh = silu(G)*U; keeps silu(G) and dHh/dG's factor (epilogue)
 //   down    : Yg = Hh * Wd + bd
 //   dHh     : dHh = dYg * Wd^T -> dG, dU (SwiGLU backward in the epilogue)
 //   dXg     : dXg = dG * Wg^T + dU * Wu^T       (one accumulator, K = 2H)
@@ -22,9 +22,7 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets a bit in the
 // workspace status word and the CTA leaves through its normal teardown
 // (TMEM is released), so a fault in a descriptor cannot hang the device.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace mgpt {
 
@@ -39,127 +37,13 @@ constexpr int EPI_WARPS = 16;                        // four per TMEM lane quart
 constexpr uint32_t STAGING_BYTES = 2048;             // per epilogue warp: 32 rows x 64 B
 constexpr uint32_t TMEM_COLS = 2 * BN;               // two accumulators
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024 /*align slack*/ + 512 /*barriers, work queue*/;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;      // warp0 TMA, warp1 MMA, warps2-17 epilogue
+constexpr int CS_WARPS = 2;                          // weight-gradient kernel only: warps 18-19 sum operand columns (bias gradients)
+constexpr int WG_THREADS = TC_THREADS + 32 * CS_WARPS;
 
-enum { ERR_FULL_WAIT = ST_FULL_WAIT, ERR_EMPTY_WAIT = ST_EMPTY_WAIT, ERR_ACC_WAIT = ST_ACC_WAIT, ERR_SCHED_WAIT = ST_SCHED_WAIT };
 constexpr int SCHED_Q = 8;                           // queue entries: the producer runs up to ~4 items ahead of the slowest epilogue warp
 
-// ---- PTX wrappers ------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: returns false (and records why) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status, int code,
-                                          uint32_t limit = SPIN_LIMIT)
-{
-    for (uint32_t i = 0; i < limit; ++i)
-        if (mbar_try(bar, parity)) return true;
-    atomicOr(status, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
-}
-// grad += x for four consecutive floats, no return value (one L2 reduction per 16 bytes)
-__device__ __forceinline__ void red_add_v4(float* dst, float4 x)
-{
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
-{
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
-{
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum)
-{
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
-}
-// mbarrier arrives once every MMA issued so far by this thread has finished
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 consecutive 32-bit columns: thread = TMEM lane (row), v[j] = column j.
-// Asynchronous: pair with tmem_ld_wait().
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
-{
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-// The registers written by tmem_ld32 may be read only after this (several loads can be in flight).
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version bits.
-//   K-major  operand: rows of 64 bf16 (128 B), 8-row groups SBO apart (LBO unused)
-//   MN-major operand: 64 contiguous MN elements per k, 8-k groups SBO apart,
-//                     next 64 MN elements LBO apart
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;            // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;            // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D=F32, A=B=BF16, dense, M x N, operand majors.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn_major, int b_mn_major)
-{
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
-           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-
-__device__ __forceinline__ float silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+using namespace tcx;
 
 // v[j] += bias[n + j] for 32 consecutive columns; 16-byte loads when the whole piece is inside the row
 __device__ __forceinline__ void add_bias32(float (&v)[32], const float* __restrict__ bias, int n, int n_out)
@@ -226,13 +110,14 @@ __device__ __forceinline__ Pipe carve(uint8_t* raw)
 }
 
 // Common prologue: barriers, TMEM (both accumulators), returns the TMEM base address.
-__device__ __forceinline__ uint32_t cta_setup(const Pipe& pipe, int warp)
+// `extra`: warps besides the MMA thread that read every operand stage and every work item (and release both).
+__device__ __forceinline__ uint32_t cta_setup(const Pipe& pipe, int warp, int extra = 0)
 {
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(pipe.full(s), 1);
-            mbar_init(pipe.empty(s), 1);
+            mbar_init(pipe.empty(s), 1 + extra);
         }
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
@@ -242,7 +127,7 @@ __device__ __forceinline__ uint32_t cta_setup(const Pipe& pipe, int warp)
 #pragma unroll
         for (int i = 0; i < SCHED_Q; ++i) {
             mbar_init(pipe.sched_full(i), 1);
-            mbar_init(pipe.sched_empty(i), 1 + EPI_WARPS);
+            mbar_init(pipe.sched_empty(i), 1 + EPI_WARPS + extra);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -348,7 +233,7 @@ __device__ __forceinline__ void pack32(const float (&a)[32], uint32_t (&out)[16]
         out[i] = *reinterpret_cast<uint32_t*>(&h);
     }
 }
-// The saved pre-activations G and U are private to the gate/up and dHh epilogues, so they are kept in the layout
+// The two saved activation-derivative arrays (buffers "G" and "U") are private to the gate/up and dHh epilogues, so they are kept in the layout
 // both epilogues touch with full-width accesses: [row tile][8-column chunk][128 rows][8 bf16].  A thread owns one
 // row (its TMEM lane); the 32 lanes of a warp then read or write 512 contiguous bytes per instruction.
 // `chunk0` points at this thread's row in the first chunk of its 32 columns; `valid` = columns left in the tensor.
@@ -388,7 +273,7 @@ struct RowsP {
     int n_out;              // output columns (H or C)
     int n_col_tiles;        // column tiles per row tile
     int b_rows_per_expert;  // rows of one expert in the B tensor map (= n_out)
-    bf16 *G, *U;            // saved pre-activations in the blocked layout (written by MODE_GATEUP, read by MODE_DHH)
+    bf16 *G, *U;            // P and Q (see the gate/up epilogue) in the blocked layout (written by MODE_GATEUP, read by MODE_DHH)
     const float* const* bias0;
     const float* const* bias1;
     // MODE_DX only: row tiles are token tiles (no experts); the epilogue adds the expert rows of each token
@@ -528,22 +413,37 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 tmem_ld_wait();
                 release_acc(pipe.acc_empty(buf), lane);
                 if (n < p.n_out) {
-                    uint32_t gp[16], up[16];
+                    // What backward needs of G and U is not the values themselves but
+                    //   Q = silu(G)                       (dU = dHh * Q)
+                    //   P = U * sigmoid(G) * (1 + G * (1 - sigmoid(G)))      (dG = dHh * P)
+                    // (utils/Tensor.cpp:2020-2027), so those are what is kept: the sigmoid is evaluated once, here,
+                    // in FP32 on the unrounded sums, and the dHh epilogue is left with two multiplies per element.
+                    uint32_t pp[16], qp[16], hp[16];
                     add_bias32(a, p.bias0[e], n, p.n_out);
                     add_bias32(b, p.bias1[e], n, p.n_out);
-                    pack32(a, gp);
-                    pack32(b, up);
-                    const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
-                    store_blocked32(reinterpret_cast<uint4*>(p.G) + o, gp, p.n_out - n);
-                    store_blocked32(reinterpret_cast<uint4*>(p.U) + o, up, p.n_out - n);
-                    // Hh from the rounded G and U (backward reads the stored values)
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float h0 = silu(bf_lo(gp[i])) * bf_lo(up[i]), h1 = silu(bf_hi(gp[i])) * bf_hi(up[i]);
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(h0, h1);
-                        gp[i] = *reinterpret_cast<uint32_t*>(&hh);
+                        float pv[2], qv[2], hv[2];
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            const float g = a[2 * i + hh], u = b[2 * i + hh];
+                            const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+                            const float q = g * sig;
+                            qv[hh] = q;
+                            hv[hh] = q * u;
+                            pv[hh] = (u * sig) * (1.0f + (g - q));
+                        }
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(pv[0], pv[1]);
+                        __nv_bfloat162 q2 = __floats2bfloat162_rn(qv[0], qv[1]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(hv[0], hv[1]);
+                        pp[i] = *reinterpret_cast<uint32_t*>(&p2);
+                        qp[i] = *reinterpret_cast<uint32_t*>(&q2);
+                        hp[i] = *reinterpret_cast<uint32_t*>(&h2);
                     }
-                    stage_row_bf16(stage, lane, gp);
+                    const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
+                    store_blocked32(reinterpret_cast<uint4*>(p.G) + o, pp, p.n_out - n);
+                    store_blocked32(reinterpret_cast<uint4*>(p.U) + o, qp, p.n_out - n);
+                    stage_row_bf16(stage, lane, hp);
                     flush_stage(stage, &tmD2, n, row_w, lane);
                 }
             } else {
@@ -560,7 +460,7 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     if (MODE == MODE_DOWN) {
                         add_bias32(v, p.bias0[e], n, p.n_out);
                     } else if (MODE == MODE_DHH) {
-                        // utils/Tensor.cpp:2020-2027 with dd = dHh
+                        // utils/Tensor.cpp:2020-2027 with dd = dHh: dG = dd * P, dU = dd * Q (P, Q saved by the forward epilogue)
                         if (un == 0) {
                             const int n1 = n + 32;
                             const size_t o1 = blocked_index(row_tile, p.n_out, n1, q * 32 + lane);
@@ -571,18 +471,9 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         uint32_t (&uw)[16] = uq[un];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            float dgv[2], duv[2];
-#pragma unroll
-                            for (int hh = 0; hh < 2; ++hh) {
-                                const float g = hh ? bf_hi(gw[i]) : bf_lo(gw[i]);
-                                const float u = hh ? bf_hi(uw[i]) : bf_lo(uw[i]);
-                                const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
-                                const float dd = v[2 * i + hh];
-                                dgv[hh] = (dd * u) * (sig * (1.0f + g * (1.0f - sig)));
-                                duv[hh] = dd * (g * sig);
-                            }
-                            __nv_bfloat162 a2 = __floats2bfloat162_rn(dgv[0], dgv[1]);
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(duv[0], duv[1]);
+                            const float d0 = v[2 * i], d1 = v[2 * i + 1];
+                            __nv_bfloat162 a2 = __floats2bfloat162_rn(d0 * bf_lo(gw[i]), d1 * bf_hi(gw[i]));
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(d0 * bf_lo(uw[i]), d1 * bf_hi(uw[i]));
                             gw[i] = *reinterpret_cast<uint32_t*>(&a2);      // dG, packed in place
                             uw[i] = *reinterpret_cast<uint32_t*>(&b2);      // dU, packed in place
                         }
@@ -640,6 +531,7 @@ struct WgradProb {
     int n_groups;           // experts, or uniform token chunks
     int uniform_rows;       // > 0: group g covers rows [g*uniform_rows, +uniform_rows) instead of an expert's rows
     int item_begin;         // first item index of this problem
+    int transposed;         // the tile is grad^T: element (m, n) of the product belongs at grad[n*M + m]
 };
 struct WgradP {
     const int32_t* padded_offsets;
@@ -649,6 +541,11 @@ struct WgradP {
     int32_t* sched;         // {next item, finished CTAs}, both zero between launches
     WgradProb prob[3];
     int n_probs, total_items;
+    int overwrite;          // grad = product (zeros for experts without rows) instead of grad += product
+    // bias gradients from the same operand tiles (null: none): gb[pr][e][col] += column sums, over the expert's
+    // rows, of the operand of problem pr whose columns are that bias's (the A operand when the problem is
+    // computed transposed, else the B operand)
+    float* const* gb[3];
 };
 struct WgradItem {
     int pr, e, m0, n0, r0, nkb;
@@ -678,7 +575,7 @@ __device__ __forceinline__ WgradItem wgrad_item(const WgradP& p, int item)
 }
 
 // Persistent over items (problem, expert, m tile, n tile); experts without rows are skipped.
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(WG_THREADS, 1)
 tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                 const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const WgradP p)
@@ -692,7 +589,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
     }
 
     const Pipe pipe = carve(smem_raw);
-    const uint32_t tmem_base = cta_setup(pipe, warp);
+    const uint32_t tmem_base = cta_setup(pipe, warp, CS_WARPS);
     constexpr uint32_t BOX = 64 * BK * 2;      // one {64 MN elements, 64 rows} box = 8 KiB
 
     if (warp == 0) {
@@ -769,6 +666,89 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                 ++t;
             }
         }
+    } else if (warp >= 2 + EPI_WARPS) {
+        // Column sums of an operand over the expert's rows = a bias gradient (layers/LinearLayer.cpp:56-57).  The tiles
+        // are in shared memory anyway, so these two warps add rows up while the tensor core works on the same stage.
+        // The operand tile whose columns are the bias's is made of 64-column boxes, and it is loaded once per tile of
+        // the OTHER output dimension: box b is summed by the item whose other-dimension tile index is b modulo the
+        // number of such tiles, so the work is spread over items (at most two boxes each; the host falls back to a
+        // separate kernel for shapes where that does not cover every box).  The two warps split a box's 64 rows.
+        // They take part in every stage and every item (fixed barrier counts), summing or not.
+        const int cw = warp - (2 + EPI_WARPS);
+        const int c8 = lane & 7, rg = lane >> 3;           // 16-byte piece of a 128-byte row; rows rg + 4i
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t nf = 0; ok; ++nf) {
+            const int item = __shfl_sync(0xffffffffu, sched_consume(pipe, nf, p.status), 0);
+            if (item < 0) break;
+            if (lane == 0) sched_release(pipe, nf);
+            const WgradItem w = wgrad_item(p, item);
+            if (w.nkb <= 0) continue;
+            const WgradProb& pb = p.prob[w.pr];
+            float* const* gbt = p.gb[w.pr];
+            // boxes of the operand tile, tiles of the other dimension, this item's index among them
+            const int nbox = pb.transposed ? BM / 64 : BN / 64;
+            const int other_tiles = pb.transposed ? pb.n_tiles_n : pb.n_tiles_m;
+            const int other = pb.transposed ? w.n0 / BN : w.m0 / BM;
+            int box0 = -1, box1 = -1;                       // the (at most two) boxes this item sums
+            if (gbt) {
+                if (other < nbox) box0 = other;
+                if (other + other_tiles < nbox) box1 = other + other_tiles;
+            }
+            float acc[2][8];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[b][i] = 0.0f;
+            for (int kb = 0; kb < w.nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(pipe.full(s), (it / STAGES) & 1, p.status, ERR_FULL_WAIT)) {
+                    ok = false;
+                    break;
+                }
+                if (box0 >= 0) {
+                    const uint32_t tile = smem_u32(pipe.tiles + s * STAGE_BYTES) + (pb.transposed ? 0 : A_BYTES);
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const int bx = b ? box1 : box0;
+                        if (bx >= 0) {
+                            const uint32_t box = tile + (uint32_t)bx * BOX;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const uint32_t r = (uint32_t)(rg + 32 * cw + 4 * i);
+                                uint32_t w0, w1, w2, w3;
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                             : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                                             : "r"(box + r * 128u + ((((uint32_t)c8) ^ (r & 7u)) << 4)));
+                                acc[b][0] += bf_lo(w0); acc[b][1] += bf_hi(w0); acc[b][2] += bf_lo(w1); acc[b][3] += bf_hi(w1);
+                                acc[b][4] += bf_lo(w2); acc[b][5] += bf_hi(w2); acc[b][6] += bf_lo(w3); acc[b][7] += bf_hi(w3);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pipe.empty(s));
+            }
+            if (box0 >= 0 && ok) {
+                float* gbe = gbt[w.e];
+                const int limit = pb.transposed ? pb.M : pb.N;
+                const int col0 = pb.transposed ? w.m0 : w.n0;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const int bx = b ? box1 : box0;
+                    if (bx >= 0) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float v = acc[b][i];
+                            v += __shfl_xor_sync(0xffffffffu, v, 8);
+                            v += __shfl_xor_sync(0xffffffffu, v, 16);
+                            const int col = col0 + bx * 64 + c8 * 8 + i;
+                            if (rg == 0 && col < limit) atomicAdd(gbe + col, v);      // two partial sums per column: one per warp
+                        }
+                    }
+                }
+            }
+        }
     } else {
         const int q = warp & 3, h = (warp - 2) >> 2;
         float* stage = reinterpret_cast<float*>(pipe.staging + (warp - 2) * STAGING_BYTES);   // [32 rows][16 floats]
@@ -778,11 +758,27 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
             if (item < 0) break;
             if (lane == 0) sched_release(pipe, nf);
             const WgradItem w = wgrad_item(p, item);
-            if (w.nkb <= 0) continue;
             const WgradProb& pb = p.prob[w.pr];
+            float* g = pb.single_grad ? pb.single_grad : pb.grad[w.e];
+            const int M = pb.M, N = pb.N;
+            const int m_w = w.m0 + q * 32;             // first product row of this warp
+            const int n_w = w.n0 + h * 64;             // first product column of this warp
+            if (w.nkb <= 0) {
+                // an expert without rows: nothing to add; when gradients are overwritten its tile is zeros
+                if (p.overwrite) {
+                    const int m = m_w + lane;
+                    if (pb.transposed) {
+                        for (int j = 0; j < 64; ++j)
+                            if (m < M && n_w + j < N) g[(size_t)(n_w + j) * M + m] = 0.0f;
+                    } else {
+                        for (int r = 0; r < 32; ++r)
+                            for (int j = lane; j < 64; j += 32)
+                                if (m_w + r < M && n_w + j < N) g[(size_t)(m_w + r) * N + n_w + j] = 0.0f;
+                    }
+                }
+                continue;
+            }
             const uint32_t buf = t & 1u;
-            const int m_w = w.m0 + q * 32;             // first output row of this warp
-            const int n_w = w.n0 + h * 64;             // first output column of this warp
             if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
             const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16) + h * 64;
@@ -791,8 +787,24 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
             tmem_ld32(t_lane + 32, v[1]);
             tmem_ld_wait();
             release_acc(pipe.acc_empty(buf), lane);
-            float* g = pb.single_grad ? pb.single_grad : pb.grad[w.e];
-            const int M = pb.M, N = pb.N;
+            if (pb.transposed) {
+                // this thread's product row m is a COLUMN of grad: for one register the 32 lanes cover 32
+                // consecutive floats of one grad row, so every scalar instruction is one full 128-byte line
+                const int m = m_w + lane;
+                if (m < M) {
+                    float* gm = g + m;
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const int n = n_w + j;
+                        if (n < N) {
+                            if (p.overwrite) gm[(size_t)n * M] = v[j >> 5][j & 31];
+                            else atomicAdd(gm + (size_t)n * M, v[j >> 5][j & 31]);
+                        }
+                    }
+                }
+                ++t;
+                continue;
+            }
             const uint32_t sw_w = ((uint32_t)lane >> 1) & 3u;            // writer: row = lane
             const int sub = lane >> 2, piece = lane & 3;                 // reader: 8 rows x 4 pieces per pass
 #pragma unroll
@@ -814,7 +826,10 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                     const int row = rr * 8 + sub, m = m_w + row;
                     const float4 x = *reinterpret_cast<const float4*>(
                         &stage[row * 16 + (((uint32_t)piece ^ (((uint32_t)row >> 1) & 3u)) << 2)]);
-                    if (m < M && col < N) red_add_v4(g + (size_t)m * N + col, x);
+                    if (m < M && col < N) {
+                        if (p.overwrite) *reinterpret_cast<float4*>(g + (size_t)m * N + col) = x;
+                        else red_add_v4(g + (size_t)m * N + col, x);
+                    }
                 }
                 __syncwarp();
             }
@@ -824,12 +839,14 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
     cta_teardown(tmem_base, warp);
 }
 
+}  // namespace
+
 // ---- host side: tensor maps ------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_fn()
+static EncodeTiledFn encode_fn()
 {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
@@ -846,7 +863,11 @@ EncodeTiledFn encode_fn()
 // OOB reads 0.  Stores (box_rows == 32): box = {32 columns (64 B), 32 rows}, 64-byte swizzle.
 int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows)
 {
-    const bool store = box_rows == 32;
+    return make_map_kind(m, base, rows, cols, box_rows, box_rows == 32);
+}
+
+int make_map_kind(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool store)
+{
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(MGPT_MOE_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {cols, rows};
@@ -860,6 +881,8 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
     if (r != CUDA_SUCCESS) return fail(MGPT_MOE_ECUDA, "cuTensorMapEncodeTiled failed (code " + std::to_string((int)r) + ")");
     return 0;
 }
+
+namespace {
 
 struct TcState {
     const void* ws = nullptr;
@@ -943,6 +966,10 @@ int grid_sms(const mgpt_moe_layer* L, const TcState* s) { return L->sm_budget > 
 
 }  // namespace
 
+// The weight-gradient kernel also sums the bias gradients when every 64-column box of its operand tiles finds an
+// item to sum it: the B tile of gWd has four boxes and is loaded once per 128-row tile of H, two boxes per item.
+bool tc_fused_bias_grads(const Dims& d) { return cdiv(d.H, BM) >= 2; }
+
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
 {
     MGPT_TRY(prepare(L, w, ws));
@@ -975,12 +1002,14 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     return 0;
 }
 
-int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
+// phase: 1 = gradients w.r.t. the rows (dHh, dXg), 2 = gradients w.r.t. the parameters, 3 = both
+int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st, int phase)
 {
     MGPT_TRY(prepare(L, w, ws));
     TcState* s = (TcState*)L->tc_state;
     const Dims& d = L->d;
     RowsP p = {};
+    if (phase & 1) {
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
@@ -1002,23 +1031,29 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
         s->dG, s->dU, s->Wg, s->Wu, s->dXg_s, s->dXg_s, s->dXg_s, p);
     MGPT_LAUNCHED("tc_rows_kernel<dxg>");
     L->stage_end(ST_DXG, st);
-    if (!L->has_grad) return 0;
+    }
+    if (!L->has_grad || !(phase & 2)) return 0;
 
     // all three weight gradients in one launch:
     //   gWg += Xg^T dG, gWu += Xg^T dU   [C,H];   gWd += Hh^T dYg   [H,C]
+    // The first two are computed transposed, (dG^T Xg) [H,C]: H = 1408 splits into eleven 128-row tiles and C into
+    // whole 256-column tiles, where the direct form leaves the last of six 256-column tiles over H half empty.
+    // Writing the tile back transposed costs nothing: a thread's row index runs along a row of the gradient.
     WgradP g = {};
     g.padded_offsets = (const int32_t*)(ws + w.padded_offsets);
     g.seg = (const int32_t*)(ws + w.seg);
     g.n_seg = L->n_seg;
     g.status = L->d_status;
     g.n_probs = 3;
+    g.overwrite = L->bwd_overwrite ? 1 : 0;
     float* const* grads[3] = {L->master.gWg, L->master.gWu, L->master.gWd};
     int items = 0;
     for (int i = 0; i < 3; ++i) {
         WgradProb& q = g.prob[i];
         q.grad = grads[i];
-        q.M = i < 2 ? d.C : d.H;
-        q.N = i < 2 ? d.H : d.C;
+        q.M = d.H;
+        q.N = d.C;
+        q.transposed = i < 2 ? 1 : 0;
         q.n_tiles_m = cdiv(q.M, BM);
         q.n_tiles_n = cdiv(q.N, BN);
         q.n_groups = d.E;
@@ -1028,7 +1063,10 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     g.total_items = items;
     L->stage_begin(ST_WGRAD, st);
     g.sched = s->sched + 8;
-    tc_wgrad_kernel<<<imin(grid_sms(L, s), items), TC_THREADS, SMEM_BYTES, st>>>(s->Xg_t, s->dG_t, s->Xg_t, s->dU_t, s->Hh_t,
+    if (tc_fused_bias_grads(d)) {
+        g.gb[0] = L->master.gbg; g.gb[1] = L->master.gbu; g.gb[2] = L->master.gbd;
+    }
+    tc_wgrad_kernel<<<imin(grid_sms(L, s), items), WG_THREADS, SMEM_BYTES, st>>>(s->dG_t, s->Xg_t, s->dU_t, s->Xg_t, s->Hh_t,
                                                                        s->dYg_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel");
     L->stage_end(ST_WGRAD, st);
@@ -1084,7 +1122,7 @@ int tc_router_wgrad(mgpt_moe_layer* L, const Workspace& w, char* ws, const void*
     q.n_groups = chunks; q.uniform_rows = rows; q.single_grad = L->p_grad[0]; q.item_begin = 0;
     g.total_items = chunks * per_chunk;
     g.sched = s->sched + 12;
-    tc_wgrad_kernel<<<imin(grid_sms(L, s), g.total_items), TC_THREADS, SMEM_BYTES, st>>>(mA, mB, mA, mB, mA, mB, g);
+    tc_wgrad_kernel<<<imin(grid_sms(L, s), g.total_items), WG_THREADS, SMEM_BYTES, st>>>(mA, mB, mA, mB, mA, mB, g);
     MGPT_LAUNCHED("tc_wgrad_kernel<Wr>");
     return 0;
 }

@@ -54,10 +54,11 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
                  int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert,
                  int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ status,
-                 int32_t* __restrict__ sticky)
+                 int32_t* __restrict__ sticky, int32_t* __restrict__ pairs, int32_t* __restrict__ n_pairs)
 {
     __shared__ int tot[MAX_EXPERTS];
     __shared__ int poff[MAX_EXPERTS + 1];
+    __shared__ int pair0[MAX_EXPERTS + 1];
     const int e = threadIdx.x;
     if (e < E) {
         int run = 0;
@@ -83,6 +84,14 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
         padded_offsets[E] = p;
         const int nt = p / ROW_TILE;
         *n_tiles = nt;
+        // pairs of row tiles of one expert, for the kernels in which two CTAs share a tile of the weights
+        int np = 0;
+        for (int i = 0; i < E; ++i) {
+            pair0[i] = np;
+            np += ((poff[i + 1] - poff[i]) / ROW_TILE + 1) / 2;
+        }
+        pair0[E] = np;
+        if (n_pairs) *n_pairs = np;
         *status = nt > max_tiles ? ST_PLAN_OVERFLOW : 0;      // cannot happen: max_tiles bounds sum(ceil); also clears the word
         if (sticky && nt > max_tiles) atomicOr(sticky, ST_PLAN_OVERFLOW);
     }
@@ -90,6 +99,13 @@ plan_scan_kernel(int32_t* __restrict__ blk_cnt, int n_blocks, int E,
     if (e < E) {
         const int t0 = poff[e] / ROW_TILE, t1 = poff[e + 1] / ROW_TILE;
         for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+        if (pairs) {
+            int pi = pair0[e];
+            for (int t = t0; t < t1 && t < max_tiles; t += 2, ++pi) {
+                pairs[2 * pi] = t;
+                pairs[2 * pi + 1] = (t + 1 < t1 && t + 1 < max_tiles) ? t + 1 : -1;     // a lone last tile has no partner
+            }
+        }
     }
 }
 
@@ -346,14 +362,14 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(BiasGradArgs a)
 int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* offsets, int32_t* padded_offsets,
              int32_t* tile_expert, int32_t* n_tiles, int max_tiles, int32_t* map, int32_t* pos,
              int32_t* row_src, int row_cap, int32_t* status, int32_t* blk, cudaStream_t st, int32_t* slot_of,
-             int32_t* sticky)
+             int32_t* sticky, int32_t* pairs, int32_t* n_pairs)
 {
     const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
     (void)row_cap;      // rows beyond the plan's tiles are never read; padding rows are marked by plan_assign_kernel
     plan_count_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
     MGPT_LAUNCHED("plan_count_kernel");
     plan_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(blk, plan_blocks, E, counts, offsets, padded_offsets, tile_expert,
-                                                n_tiles, max_tiles, status, sticky);
+                                                n_tiles, max_tiles, status, sticky, pairs, n_pairs);
     MGPT_LAUNCHED("plan_scan_kernel");
     plan_assign_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk, counts, offsets, padded_offsets, map, pos,
                                                            row_src, slot_of, status, sticky);
@@ -366,7 +382,8 @@ int launch_plan(const Dims& d, const Workspace& w, char* ws, cudaStream_t st, in
     return run_plan((const int32_t*)(ws + w.top_idx), w.R, d.E, (int32_t*)(ws + w.counts), (int32_t*)(ws + w.offsets),
                     (int32_t*)(ws + w.padded_offsets), (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.n_tiles),
                     w.max_tiles, (int32_t*)(ws + w.map), (int32_t*)(ws + w.pos), (int32_t*)(ws + w.row_src),
-                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st, (int32_t*)(ws + w.slot), sticky);
+                    w.row_cap, (int32_t*)(ws + w.status), (int32_t*)(ws + w.blk_cnt), st, (int32_t*)(ws + w.slot), sticky,
+                    (int32_t*)(ws + w.pairs), (int32_t*)(ws + w.n_pairs));
 }
 
 // dst[p,:] = src[row_src[p]/k,:] for p < rows (zero where row_src[p] < 0).  rows < 0: every tile of the plan.
@@ -474,10 +491,13 @@ __global__ void __launch_bounds__(256)
 segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, int32_t* __restrict__ counts,
                      int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_order,
                      int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ seg,
-                     int32_t* __restrict__ status, int32_t* __restrict__ sticky)
+                     int32_t* __restrict__ status, int32_t* __restrict__ sticky,
+                     int32_t* __restrict__ pairs, int32_t* __restrict__ n_pairs)
 {
     __shared__ int first_tile[MAX_SEGMENTS + 1];     // in arrival order (s, e)
     __shared__ int first_item[MAX_SEGMENTS];         // in processing order (e, s)
+    __shared__ int pair0[MAX_EXPERTS + 1];
+    __shared__ int item0[MAX_EXPERTS + 1];           // first position of an expert in the processing order
     const int n = n_src * E;
     if (threadIdx.x == 0) {
         int t = 0;
@@ -489,12 +509,19 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
         *n_tiles = t;
         *status = t > max_tiles ? ST_PLAN_OVERFLOW : 0;
         if (sticky && t > max_tiles) atomicOr(sticky, ST_PLAN_OVERFLOW);
-        int it = 0;
-        for (int e = 0; e < E; ++e)
+        int it = 0, np = 0;
+        for (int e = 0; e < E; ++e) {
+            item0[e] = it;
+            pair0[e] = np;
             for (int s_ = 0; s_ < n_src; ++s_) {
                 first_item[e * n_src + s_] = it;
                 it += (seg_counts[s_ * E + e] + ROW_TILE - 1) / ROW_TILE;
             }
+            np += (it - item0[e] + 1) / 2;
+        }
+        item0[E] = it;
+        pair0[E] = np;
+        *n_pairs = np;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -514,6 +541,15 @@ segment_tiles_kernel(const int32_t* __restrict__ seg_counts, int n_src, int E, i
         for (int s_ = 0; s_ < n_src; ++s_) c += seg_counts[s_ * E + e];
         counts[e] = c;
     }
+    __syncthreads();        // tile_order is complete (written above by this block)
+    // pairs of tiles of one expert, in processing order (the two tiles may have arrived from different sources)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int pi = pair0[e];
+        for (int i = item0[e]; i < item0[e + 1] && i < max_tiles; i += 2, ++pi) {
+            pairs[2 * pi] = tile_order[i];
+            pairs[2 * pi + 1] = (i + 1 < item0[e + 1] && i + 1 < max_tiles) ? tile_order[i + 1] : -1;
+        }
+    }
 }
 
 int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int32_t* seg_counts, int n_src, cudaStream_t st,
@@ -523,7 +559,8 @@ int launch_segment_tiles(const Dims& d, const Workspace& w, char* ws, const int3
     segment_tiles_kernel<<<1, 256, 0, st>>>(seg_counts, n_src, d.E, (int32_t*)(ws + w.counts),
                                             (int32_t*)(ws + w.tile_expert), (int32_t*)(ws + w.tile_order),
                                             (int32_t*)(ws + w.n_tiles), w.max_tiles, (int32_t*)(ws + w.seg),
-                                            (int32_t*)(ws + w.status), sticky);
+                                            (int32_t*)(ws + w.status), sticky, (int32_t*)(ws + w.pairs),
+                                            (int32_t*)(ws + w.n_pairs));
     MGPT_LAUNCHED("segment_tiles_kernel");
     return 0;
 }
@@ -562,7 +599,7 @@ extern "C" int mgpt_moe_op_plan(const int32_t* top_idx, int n_rows, int E, int32
     if (scratch_bytes < mgpt_moe_op_plan_scratch_bytes(n_rows, E))
         return fail(MGPT_MOE_ENOMEM, "scratch smaller than mgpt_moe_op_plan_scratch_bytes()");
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream, nullptr, nullptr);
+                    pos, row_src, row_cap, status, (int32_t*)scratch, (cudaStream_t)stream, nullptr, nullptr, nullptr, nullptr);
 }
 
 // ---- dispatch plan without any allocation ------------------------------------------
@@ -615,5 +652,5 @@ extern "C" int mgpt_moe_op_plan_noalloc(const int32_t* top_idx, int n_rows, int 
     // The array still holds the previous call's block bases.  Nothing has to be cleared:
     // plan_count_kernel writes all plan_blocks*E entries this call reads before they are read.
     return run_plan(top_idx, n_rows, E, counts, offsets, padded_offsets, tile_expert, n_tiles, row_cap / ROW_TILE, map,
-                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream, nullptr, nullptr);
+                    pos, row_src, row_cap, status, scratch, (cudaStream_t)stream, nullptr, nullptr, nullptr, nullptr);
 }

@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(R_WARPS * 32)
 router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ br,
                   int N, int C, int E, int k,
                   float* __restrict__ logits, float* __restrict__ probs,
-                  int32_t* __restrict__ top_idx, float* __restrict__ top_p)
+                  int32_t* __restrict__ top_idx, float* __restrict__ top_p,
+                  const int32_t* __restrict__ list, const int32_t* __restrict__ list_count)
 {
     constexpr int SUB = 32 / EL;                    // tokens per warp pass
     constexpr int TOK_W = TPW * SUB;                // tokens per warp
@@ -49,6 +50,17 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = lane / EL, el = lane % EL;
     const int tok0 = blockIdx.x * TOK;
+
+    // The CTA's tokens: a contiguous range, or -- second pass of the screened router -- entries of a list of
+    // token indices whose length is only known on the device (CTAs beyond it leave at once).
+    __shared__ int stok[TOK];
+    const int n_active = list ? *list_count : N;
+    if (tok0 >= n_active) return;
+    for (int i = tid; i < TOK; i += THREADS) {
+        const int idx = tok0 + i;
+        stok[i] = idx < n_active ? (list ? list[idx] : idx) : -1;
+    }
+    __syncthreads();
 
     float acc[TPW][EPL];
 #pragma unroll
@@ -92,8 +104,8 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
                 const int v = tid + u * THREADS;
                 xr[u] = make_uint4(0, 0, 0, 0);
                 if (v < X_VECS) {
-                    const int tok = tok0 + v / XPT;
-                    if (tok < N) xr[u] = *reinterpret_cast<const uint4*>(x + (size_t)tok * C + c0 + (v % XPT) * XV);
+                    const int tok = stok[v / XPT];
+                    if (tok >= 0) xr[u] = *reinterpret_cast<const uint4*>(x + (size_t)tok * C + c0 + (v % XPT) * XV);
                 }
             }
 #pragma unroll
@@ -144,8 +156,8 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 #pragma unroll 4
             for (int i = tid; i < TOK * R_CK; i += THREADS) {
                 const int t = i / R_CK, j = i % R_CK;
-                const int tok = tok0 + t, c = c0 + j;
-                xs[0][t][j] = (tok < N && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
+                const int tok = stok[t], c = c0 + j;
+                xs[0][t][j] = (tok >= 0 && c < C) ? to_f32(x[(size_t)tok * C + c]) : 0.0f;
             }
 #pragma unroll 4
             for (int i = tid; i < R_CK * WCOLS; i += THREADS) {
@@ -167,8 +179,8 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 #pragma unroll
     for (int t = 0; t < TPW; ++t) {
         // every lane runs the warp-level steps (tokens past N compute on zeros and store nothing)
-        const int tok = tok0 + warp * TOK_W + t * SUB + sub;
-        const bool live = tok < N;
+        const int tok = stok[warp * TOK_W + t * SUB + sub];
+        const bool live = tok >= 0;
         float lg[EPL], p[EPL];
         float mx = -INFINITY;
 #pragma unroll
@@ -492,39 +504,49 @@ router_wgrad_reduce_kernel(const float* __restrict__ part, const float* __restri
 
 template <typename TIn, int EL, int EPL, int TPW>
 int router_fwd_launch(const TIn* x, const float* Wr, const float* br, int N, int C, int E, int k,
-                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
+                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st,
+                      const int32_t* list, const int32_t* list_count)
 {
     constexpr int TOK = R_WARPS * TPW * (32 / EL);
     const int grid = (N + TOK - 1) / TOK;
     const bool fast = C % R_CK == 0 && E == EPL * EL && ((uintptr_t)x & 15) == 0 && ((uintptr_t)Wr & 15) == 0;
     if (fast)
-        router_fwd_kernel<TIn, EL, EPL, TPW, true><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
+        router_fwd_kernel<TIn, EL, EPL, TPW, true><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, list, list_count);
     else
-        router_fwd_kernel<TIn, EL, EPL, TPW, false><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p);
+        router_fwd_kernel<TIn, EL, EPL, TPW, false><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, list, list_count);
     MGPT_LAUNCHED("router_fwd_kernel");
     return 0;
 }
 
 template <typename TIn>
 int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, int C, int E, int k,
-                        float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
+                        float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st,
+                        const int32_t* list, const int32_t* list_count)
 {
-    if (E <= 8) return router_fwd_launch<TIn, 8, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
-    if (E <= 16) return router_fwd_launch<TIn, 16, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
-    if (E <= 32) return router_fwd_launch<TIn, 32, 1, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
-    if (E <= 64) return router_fwd_launch<TIn, 32, 2, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
-    return router_fwd_launch<TIn, 32, 4, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+    // Second pass of the screened router: a fraction of the tokens, how many is only known on the device.  Small
+    // CTAs (16 tokens) so that the few thousand listed tokens still spread over every SM.
+    if (list && E > 32 && E <= 64)
+        return router_fwd_launch<TIn, 32, 2, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    if (list && E > 16 && E <= 32)
+        return router_fwd_launch<TIn, 32, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    if (E <= 8) return router_fwd_launch<TIn, 8, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    if (E <= 16) return router_fwd_launch<TIn, 16, 1, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    if (E <= 32) return router_fwd_launch<TIn, 32, 1, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    if (E <= 64) return router_fwd_launch<TIn, 32, 2, 8>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    return router_fwd_launch<TIn, 32, 4, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
 }
 
 }  // namespace
 
+// list / list_count (device): run only on the tokens list[0 .. *list_count), at most N of them
 int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, int N, int C, int E, int k,
-                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st)
+                      float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st,
+                      const int32_t* list, const int32_t* list_count)
 {
     if (N <= 0) return 0;
     if (io == MGPT_MOE_IO_F32)
-        return router_fwd_dispatch((const float*)x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
-    return router_fwd_dispatch((const bf16*)x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st);
+        return router_fwd_dispatch((const float*)x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    return router_fwd_dispatch((const bf16*)x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
 }
 
 int launch_router_bwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, int io,

@@ -69,9 +69,13 @@ int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void*
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = (char*)workspace;
     const Dims& d = L->d;
-    if (n_tokens > 0)
-        MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k, (float*)(ws + w.logits),
-                                   (float*)(ws + w.probs), (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
+    if (n_tokens > 0) {
+        if (tc_router_usable(L, x, io))
+            MGPT_TRY(tc_router_fwd(L, w, ws, x, st));
+        else
+            MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k, (float*)(ws + w.logits),
+                                       (float*)(ws + w.probs), (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
+    }
     MGPT_TRY(launch_plan(d, w, ws, st, L->d_status));
     // expert-major rows, each expert padded to whole tiles with zero rows; stable within an expert
     MGPT_TRY(gather_rows(x, io, (const int32_t*)(ws + w.row_src), (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, d.C,
@@ -162,8 +166,8 @@ int mgpt_moe_experts_forward(mgpt_moe_layer* L, const void* rows, const int32_t*
     return 0;
 }
 
-int mgpt_moe_experts_backward(mgpt_moe_layer* L, const void* d_out_rows, void* d_in_rows, void* workspace,
-                              size_t ws_bytes, mgpt_stream_t stream)
+static int experts_backward_impl(mgpt_moe_layer* L, const void* d_out_rows, void* d_in_rows, void* workspace,
+                                 size_t ws_bytes, mgpt_stream_t stream, int phase)
 {
     MGPT_TRY(check_expert_layer(L));
     if (!L->fwd_done || workspace != L->last_ws) return fail(MGPT_MOE_ESTATE, "backward needs the workspace of the last forward");
@@ -178,14 +182,36 @@ int mgpt_moe_experts_backward(mgpt_moe_layer* L, const void* d_out_rows, void* d
     const Dims& d = L->d;
     L->ext_dYg = const_cast<void*>(d_out_rows);      // padding rows arrive as zeros from the routing side
     L->ext_dXg = d_in_rows;
-    if (d.mode == MGPT_MOE_BF16 && d.gemm_impl == 0) MGPT_TRY(tc_experts_backward(L, w, ws, st));
-    else MGPT_TRY(simt_experts_backward(L, w, ws, st));
-    if (L->has_grad) {
+    const bool tc = d.mode == MGPT_MOE_BF16 && d.gemm_impl == 0;
+    if (tc) {
+        MGPT_TRY(tc_experts_backward(L, w, ws, st, phase));
+    } else if (phase & 1) {
+        MGPT_TRY(simt_experts_backward(L, w, ws, st));     // the CUDA-core path computes both kinds in one go
+    }
+    if ((phase & 2) && L->has_grad && !(tc && tc_fused_bias_grads(d))) {      // else the tensor-core weight-gradient kernel sums them itself
         L->stage_begin(ST_BIAS_GRAD, st);
         MGPT_TRY(launch_bias_grads(L, w, ws, st));
         L->stage_end(ST_BIAS_GRAD, st);
     }
     return 0;
+}
+
+int mgpt_moe_experts_backward(mgpt_moe_layer* L, const void* d_out_rows, void* d_in_rows, void* workspace,
+                              size_t ws_bytes, mgpt_stream_t stream)
+{
+    return experts_backward_impl(L, d_out_rows, d_in_rows, workspace, ws_bytes, stream, 3);
+}
+
+int mgpt_moe_experts_backward_rows(mgpt_moe_layer* L, const void* d_out_rows, void* d_in_rows, void* workspace,
+                                   size_t ws_bytes, mgpt_stream_t stream)
+{
+    return experts_backward_impl(L, d_out_rows, d_in_rows, workspace, ws_bytes, stream, 1);
+}
+
+int mgpt_moe_experts_backward_params(mgpt_moe_layer* L, const void* d_out_rows, void* d_in_rows, void* workspace,
+                                     size_t ws_bytes, mgpt_stream_t stream)
+{
+    return experts_backward_impl(L, d_out_rows, d_in_rows, workspace, ws_bytes, stream, 2);
 }
 
 }  // extern "C"

@@ -59,6 +59,7 @@ int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st)
         const int E8 = (d.E + 7) / 8 * 8;
         router_shadow_kernel<<<(d.C * E8 + 255) / 256, 256, 0, st>>>(L->p_data[0], d.C, d.E, E8, L->sWr);
         MGPT_LAUNCHED("router_shadow_kernel");
+        MGPT_TRY(launch_router_pieces(L, st));
     }
     L->shadows_fresh = true;
     return 0;
@@ -72,6 +73,7 @@ int launch_sync_weights(mgpt_moe_layer* L, cudaStream_t st)
         const int E8 = (d.E + 7) / 8 * 8;
         router_shadow_kernel<<<(d.C * E8 + 255) / 256, 256, 0, st>>>(L->p_data[0], d.C, d.E, E8, L->sWr);
         MGPT_LAUNCHED("router_shadow_kernel");
+        MGPT_TRY(launch_router_pieces(L, st));
     }
     if (!L->experts_bound) {
         L->shadows_fresh = true;

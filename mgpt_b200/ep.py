@@ -220,6 +220,23 @@ class CudaStages:
             self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
         return d_in
 
+    def experts_backward_rows(self, d_out, chunk=0):
+        """First half of experts_backward: the gradient w.r.t. the received rows (what the other ranks wait for)."""
+        d_in = torch.empty_like(d_out)
+        ws = self._local_ws[chunk]
+        self._lib_mod.check(self.lib.mgpt_moe_experts_backward_rows(
+            self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
+        self._bwd_bufs = getattr(self, "_bwd_bufs", {})
+        self._bwd_bufs[chunk] = (d_out, d_in)
+        return d_in
+
+    def experts_backward_params(self, chunk=0):
+        """Second half: this chunk's expert parameter gradients, from the buffers of experts_backward_rows."""
+        d_out, d_in = self._bwd_bufs.pop(chunk)
+        ws = self._local_ws[chunk]
+        self._lib_mod.check(self.lib.mgpt_moe_experts_backward_params(
+            self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
+
 
 class ExpertParallelMoE:
     """Same role as the reference's MoELayer, with the experts sharded over a process group."""
@@ -375,10 +392,14 @@ class ExpertParallelMoE:
             if pending[c] is not None:
                 pending[c].wait()
             self._mark("grad_rows_all_to_all")
-            d_in = self.stages.experts_backward(d_recv[c], *([c] if nc > 1 else []))
-            self._mark("experts_backward")
+            # the rows' gradients first: they start travelling back while this chunk's parameter gradients
+            # (the larger half of the work) are still being formed
+            d_in = self.stages.experts_backward_rows(d_recv[c], *([c] if nc > 1 else []))
+            self._mark("experts_backward_rows")
             back.append(self._exchange(d_back[starts[c]: starts[c] + int(sum(send_splits[c]))], d_in,
                                        send_splits[c], recv_splits[c]))
+            self.stages.experts_backward_params(*([c] if nc > 1 else []))
+            self._mark("experts_backward_params")
         for wk in back:
             if wk is not None:
                 wk.wait()

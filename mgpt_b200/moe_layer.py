@@ -198,6 +198,11 @@ class MoELayer:
         _lib.check(self.lib.mgpt_moe_expert_counts(self._h, buf))
         return list(buf)
 
+    def set_weight_grad_overwrite(self, enabled: bool) -> None:
+        """Backward stores the expert weight gradients instead of adding to them (see include/mgpt_moe.h): for a
+        caller that would have zeroed them first, e.g. the first micro-batch after ``zero_grad``."""
+        _lib.check(self.lib.mgpt_moe_set_weight_grad_overwrite(self._h, 1 if enabled else 0))
+
     def check_status(self) -> None:
         """Raises MoeError if a kernel of this layer reported an error since the last check (a bounded wait
         that ran out, an expert id out of range); synchronises the stream of the last call."""

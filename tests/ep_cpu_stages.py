@@ -134,3 +134,10 @@ class CpuStages:
             p[2].grad += torch.from_numpy(xe.T @ dU)
             d_in[idx] = dG @ Wg.T + dU @ Wu.T
         return torch.from_numpy(d_in.astype(np.float32))
+
+    # the two-call form (rows first, so that they can travel back while the parameter gradients are formed)
+    def experts_backward_rows(self, d_out, chunk=0):
+        return self.experts_backward(d_out, chunk)
+
+    def experts_backward_params(self, chunk=0):
+        pass

@@ -48,7 +48,11 @@ def test_c4_routing_bit_exact_and_plan_invariants(c4):
     assert np.array_equal(view("counts"), ref["counts"])
     assert np.array_equal(view("offsets"), ref["offsets"])
     assert np.array_equal(view("map"), ref["map"])
-    assert np.array_equal(layer.workspace_view("logits", torch.float32, (N, E)).cpu().numpy(), ref["logits"])
+    # BF16 tokens take the screened router: logits from the tensor-core pass agree to a few 1e-6, indices exactly
+    logits = layer.workspace_view("logits", torch.float32, (N, E)).cpu().numpy()
+    assert np.abs(logits - ref["logits"]).max() <= 2e-5 * (1.0 + np.abs(ref["logits"]).max())
+    redo = int(layer.workspace_view("router_recompute", torch.int32).cpu().numpy()[0])
+    assert 0 <= redo <= N // 2, f"{redo} of {N} tokens took the exact pass"
     # plan: counts add up, padded segments are whole tiles, pos is a bijection onto the non-padding rows
     counts, poff, pos = ref["counts"], view("padded_offsets"), view("pos")
     assert counts.sum() == N * k

@@ -45,15 +45,19 @@ def test_c1_fp32_full_size():
     assert rel_l2(got["dlogits"], ref["dlogits"]) <= 1e-4
 
 
+@pytest.mark.parametrize("impl", [1, 0])
 @pytest.mark.parametrize("name", ["c2", "c3", "c5-256"])
-def test_routing_bit_exact_at_full_size(name):
-    """Router + plan at the benchmark sizes (the oracle's routing pass takes seconds)."""
+def test_routing_bit_exact_at_full_size(name, impl):
+    """Router + plan at the benchmark sizes (the oracle's routing pass takes seconds).  impl 1: the exact
+    CUDA-core router alone; impl 0: tensor-core first pass + exact second pass."""
     w = synth.WORKLOADS[name]
     x, params, dy = synth.make_inputs(w)
     ref = oracle.run(dims_of(w), x, params, route_only=True, threads=16)
-    got = run_layer(w, x, params, None, mode="fp32" if w.dtype == "fp32" else "bf16", gemm_impl=1,
+    got = run_layer(w, x, params, None, mode="fp32" if w.dtype == "fp32" else "bf16", gemm_impl=impl,
                     io=torch.bfloat16)
     assert_routing_exact(got, ref)
+    if impl == 0:
+        assert got["screened"] and got["router_recompute"] <= w.n_tokens // 2
 
 
 def test_gradients_accumulate():

@@ -20,7 +20,7 @@ def _bf16_inputs(w, x, params, dy):
 
 
 def _buffers(got, w, blocked_gu=False):
-    """Activation buffers as [rows, width].  The tcgen05 path keeps G and U as
+    """Activation buffers as [rows, width].  The tcgen05 path keeps the buffers named G and U as
     [row tile][8-column chunk][128 rows][8] (include/mgpt_moe.h); ``blocked_gu`` undoes that."""
     layer = got["layer"]
     rows = int(got["padded_offsets"][-1])
@@ -66,6 +66,11 @@ def test_tc_against_simt_and_oracle(shape, io):
     simt = run_layer(w, x, params, dy, mode="bf16", gemm_impl=1, io=io)
     assert_routing_exact(tc, ref)
     a, b = _buffers(tc, w, blocked_gu=True), _buffers(simt, w)
+    # the tensor-core path keeps, in the buffers named G and U, what backward needs of them:
+    # P = U*sigmoid(G)*(1 + G*(1 - sigmoid(G))) and Q = silu(G)  (include/mgpt_moe.h)
+    g64, u64 = b["G"].astype(np.float64), b["U"].astype(np.float64)
+    sig = 1.0 / (1.0 + np.exp(-g64))
+    b["G"], b["U"] = u64 * sig * (1.0 + g64 * (1.0 - sig)), g64 * sig
     for name in ACT:
         assert rel_l2(a[name], b[name]) < 6e-3, (name, rel_l2(a[name], b[name]))
     for i, (ga, gb) in enumerate(zip(tc["grads"], simt["grads"])):
@@ -92,3 +97,35 @@ def test_tc_decode_shapes_forward_only(n):
     got = run_layer(w, x, params, None, mode="bf16", io=torch.bfloat16)
     assert_routing_exact(got, ref)
     assert rel_l2(got["y"], ref["y"]) <= TOL_BF16
+
+
+def test_weight_gradients_overwritten_equal_accumulated_into_zero():
+    """Stores instead of read-modify-writes: same bits as accumulating into zeroed tensors, stale contents gone,
+    experts without rows get zeros; bias and router gradients keep accumulating."""
+    w = synth.Workload("ow", 900, 128, 200, 16, 2, "bf16", skew=True)
+    x, params, dy = synth.make_inputs(w, seed=13, bias_std=0.02)
+    params[1][0, -3:] = np.float32(-64.0)                               # the last three experts stay empty
+    acc = run_layer(w, x, params, dy, mode="bf16", io=torch.bfloat16)
+    assert (acc["counts"] == 0).any()
+    from mgpt_b200 import MoELayer
+    layer = MoELayer(w.C, w.H, w.E, w.k, mode="bf16", lb_alpha=w.alpha)
+    layer.load_parameters(params)
+    for p in layer.get_parameters():
+        p.grad.fill_(123.0)                                             # what a forgotten zero_grad leaves behind
+    for i in (0, 1):
+        layer.get_parameters()[i].grad.zero_()
+    for e in range(w.E):
+        for j in (1, 3, 5):
+            layer.get_parameters()[2 + 6 * e + j].grad.zero_()          # biases accumulate: zeroed by the caller
+    layer.set_weight_grad_overwrite(True)
+    xt, dyt = torch.from_numpy(x).cuda().bfloat16(), torch.from_numpy(dy).cuda().bfloat16()
+    layer.forward(xt)
+    layer.backward(dyt)
+    torch.cuda.synchronize()
+    layer.check_status()
+    for i, (p, want) in enumerate(zip(layer.get_parameters(), acc["grads"])):
+        got = p.grad.cpu().numpy()
+        if i >= 2 and (i - 2) % 6 in (0, 2, 4):
+            assert np.array_equal(got, want), f"weight gradient {i}"
+        else:
+            assert rel_l2(got, want) < 1e-5, f"gradient {i}"

@@ -26,6 +26,9 @@ def run_layer(w, x, params, dy, *, mode, gemm_impl=0, io=torch.float32):
     y = layer.forward(xt)
     N, E, k = w.n_tokens, w.E, w.k
     out = {"layer": layer, "y": y.float().cpu().numpy()}
+    # BF16 tokens on the tensor-core path take the screened router: indices exact, logits / probabilities close
+    out["screened"] = mode == "bf16" and gemm_impl == 0 and io == torch.bfloat16
+    out["router_recompute"] = int(layer.workspace_view("router_recompute", torch.int32).cpu().numpy()[0]) if out["screened"] else 0
     i32, f32 = torch.int32, torch.float32
     out["logits"] = layer.workspace_view("logits", f32, (N, E)).cpu().numpy()
     out["probs"] = layer.workspace_view("probs", f32, (N, E)).cpu().numpy()
@@ -53,9 +56,15 @@ def assert_routing_exact(got, ref):
     """Routing indices, per-expert counts and the slot permutation must be bit-exact."""
     for key in ("top_idx", "counts", "offsets", "map"):
         assert np.array_equal(got[key], ref[key]), f"{key} differs from the CPU reference"
-    assert np.array_equal(got["logits"], ref["logits"]), "router logits are not bit-exact"
-    # probabilities differ from glibc's expf by at most an ulp or two
-    assert np.allclose(got["top_p"], ref["top_p"], rtol=1e-6, atol=0)
+    if got.get("screened"):
+        # tensor-core first pass: same sums in another order (tokens of the exact second pass are bit-exact)
+        assert np.abs(got["logits"] - ref["logits"]).max() <= 2e-5 * (1.0 + np.abs(ref["logits"]).max())
+        assert np.allclose(got["top_p"], ref["top_p"], rtol=1e-4, atol=0)
+        assert np.allclose(got["probs"], ref["probs"], rtol=1e-4, atol=0)
+    else:
+        assert np.array_equal(got["logits"], ref["logits"]), "router logits are not bit-exact"
+        # probabilities differ from glibc's expf by at most an ulp or two
+        assert np.allclose(got["top_p"], ref["top_p"], rtol=1e-6, atol=0)
     assert got["status"] == 0
 
 
