@@ -148,6 +148,35 @@ const char* mgpt_moe_stage_name(int stage);
 int  mgpt_moe_forward_residual(mgpt_moe_layer* layer, const void* x, const void* residual, void* y, int n_tokens,
                                int io_dtype, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
 
+/* Forward for generation.  The reference's generator runs the whole model forward over the current context for every
+ * new token and throws the activations away (pipeline/Generator.cpp:10-31: model.forward, reset_activations), so the
+ * layer sees forward-only calls of a few to a few hundred tokens.  This entry point is mgpt_moe_forward without
+ * anything kept for a backward pass: a workspace of mgpt_moe_inference_workspace_bytes(n_tokens) (no saved
+ * activation factors, no backward buffers), the same routing and the same y.  Token batches too small to fill the
+ * device take the low-latency form of the exact router.  mgpt_moe_backward cannot follow it (MGPT_MOE_ESTATE);
+ * mgpt_moe_expert_counts can. */
+size_t mgpt_moe_inference_workspace_bytes(const mgpt_moe_layer* layer, int n_tokens);
+int  mgpt_moe_forward_inference(mgpt_moe_layer* layer, const void* x, void* y, int n_tokens, int io_dtype,
+                                void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
+/* The block's glue around the layer, fused (layers/TransformerBlock.cpp:42-46 forward, 80-84 backward):
+ *   block_forward   x2 = x1 + moe(rmsnorm(x1) * rms_scale)   in place of  ln2.forward_into, mlp.forward_into, add_into
+ *   block_backward  d_x1 = dout + rmsnorm_backward(d_moe_in), d_rms_scale += ...
+ *                                                            in place of  mlp.backward_into, ln2.backward_into, add_into
+ * RMSNorm as the reference's (utils/Tensor.cpp:785-800, 1674-1690; r = 1/sqrt(mean(x^2) + eps), rms_scale the
+ * layer's gamma [C], FP32).  The norm writes the layer's input once (the reference also writes x_hat) and one float
+ * per token; the skip connection rides on the combine write; backward recomputes x_hat from x1 and forms d_x1 in
+ * the pass that adds dout.  x1 must still hold its forward values at block_backward.  workspace:
+ * mgpt_moe_block_workspace_bytes(n_tokens, io_dtype) bytes, 256-byte aligned, untouched between the two calls; it
+ * contains the layer's own workspace, which starts at workspace + block_workspace_bytes - mgpt_moe_workspace_bytes.
+ * d_rms_scale may be NULL.  The layer's parameter gradients accumulate as in mgpt_moe_backward. */
+size_t mgpt_moe_block_workspace_bytes(const mgpt_moe_layer* layer, int n_tokens, int io_dtype);
+int  mgpt_moe_block_forward(mgpt_moe_layer* layer, const void* x1, const float* rms_scale, float eps, void* x2,
+                            int n_tokens, int io_dtype, void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+int  mgpt_moe_block_backward(mgpt_moe_layer* layer, const void* x1, const float* rms_scale, float* d_rms_scale,
+                             const void* dout, void* d_x1, int io_dtype, void* workspace, size_t workspace_bytes,
+                             mgpt_stream_t stream);
+
 /* Recompute forward for activation checkpointing. The reference runs every block's
  * forward twice per step (GPT.cpp:79-96: once without keeping activations, once more
  * before that block's backward, the arena rewound in between). The same tokens route
@@ -308,6 +337,48 @@ int  mgpt_moe_experts_backward_rows(mgpt_moe_layer* layer, const void* d_out_row
                                     void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
 int  mgpt_moe_experts_backward_params(mgpt_moe_layer* layer, const void* d_out_rows, void* d_in_rows,
                                       void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+
+/* ---- expert parallelism behind the C ABI ------------------------------------------------------------------------
+ * One process per GPU, one mgpt_moe_ep per process: every rank keeps a replica of the router and E/world experts
+ * (with n_chunks > 1 expert e belongs to chunk e / (E/n_chunks) and, inside it, to rank
+ * (e % (E/n_chunks)) / (E/(world*n_chunks)); n_chunks = 1: rank g owns experts [g*E/world, (g+1)*E/world)), tokens
+ * stay on their GPU.  Forward: route -> exchange of the per-expert counts -> rows to the experts' owners -> experts ->
+ * rows back -> combine; backward the mirror image, the gradients of the received rows travelling back while the
+ * parameter gradients are formed.  The exchange is NCCL point-to-point (ncclSend / ncclRecv in groups) on a stream of
+ * its own; a chunk's exchange overlaps the previous chunk's expert work.  The library loads libnccl.so.2 at the first
+ * call (it does not link it), so single-GPU users need no NCCL.  The reference has no multi-GPU code: these calls
+ * shard the expert loop of MoELayer::forward_into / backward_into (layers/MoELayer.cpp:94-118, 159-181).
+ *
+ * Set-up: rank 0 calls mgpt_moe_ep_unique_id and hands the 128 bytes to every rank by whatever means the engine
+ * has; then every rank calls mgpt_moe_ep_create (a collective: it returns once all ranks have called it).
+ * Parameters: 2 + 6*E/world tensors -- Wr, br, then this rank's experts in local order (chunk by chunk;
+ * mgpt_moe_ep_global_expert gives the global index of local expert i) -- FP32 device buffers owned by the caller, like
+ * mgpt_moe_bind_params.  x, y, dy, dx: device [n_tokens, C].  The layer owns its workspaces and exchange buffers and
+ * grows them on demand (allocation only when n_tokens or the row counts exceed what was seen before).  The
+ * load-balance term uses this rank's own counts; router gradients are this rank's (all-reduce them if the replicas
+ * are to stay identical).  Each forward synchronises the host once (the row counts per peer). */
+typedef struct mgpt_moe_ep mgpt_moe_ep;
+typedef struct {
+    int   embed_dim, hidden_dim, num_experts, top_k;
+    float lb_alpha;
+    int   mode;        /* MGPT_MOE_FP32 | MGPT_MOE_BF16 */
+    int   device;
+    int   rank, world;
+    int   n_chunks;    /* experts per rank are split into this many chunks (1 = no overlap) */
+} mgpt_moe_ep_config;
+#define MGPT_MOE_EP_ID_BYTES 128
+int  mgpt_moe_ep_unique_id(void* id_out);
+int  mgpt_moe_ep_create(const mgpt_moe_ep_config* cfg, const void* id, mgpt_moe_ep** out);
+void mgpt_moe_ep_destroy(mgpt_moe_ep* ep);
+int  mgpt_moe_ep_num_params(const mgpt_moe_ep* ep);
+int  mgpt_moe_ep_global_expert(const mgpt_moe_ep* ep, int local_index);
+int  mgpt_moe_ep_bind_params(mgpt_moe_ep* ep, float* const* data, float* const* grad, int n);
+int  mgpt_moe_ep_sync_weights(mgpt_moe_ep* ep, mgpt_stream_t stream);
+int  mgpt_moe_ep_forward(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, int io_dtype, mgpt_stream_t stream);
+int  mgpt_moe_ep_backward(mgpt_moe_ep* ep, const void* x, const void* dy, void* dx, int io_dtype, mgpt_stream_t stream);
+/* Real rows this rank received per (source rank, local expert) in the last forward: int32 [world * E/world], host. */
+int  mgpt_moe_ep_received_counts(mgpt_moe_ep* ep, int32_t* host_counts);
+int  mgpt_moe_ep_check_status(mgpt_moe_ep* ep);
 
 /* The same plan for callers that can neither pass scratch nor let the library
  * allocate: an engine whose arena already owns all device memory, or a step

@@ -22,7 +22,11 @@ SYMBOLS = [
     "mgpt_moe_stage_workspace_bytes", "mgpt_moe_route", "mgpt_moe_combine", "mgpt_moe_combine_backward",
     "mgpt_moe_route_backward", "mgpt_moe_experts_forward", "mgpt_moe_experts_backward",
     "mgpt_moe_check_status", "mgpt_moe_adamw_step_guarded", "mgpt_moe_selftest_bounded_wait",
-    "mgpt_moe_set_weight_grad_overwrite", "mgpt_moe_experts_backward_rows", "mgpt_moe_experts_backward_params",
+    "mgpt_moe_ep_unique_id", "mgpt_moe_ep_create", "mgpt_moe_ep_destroy", "mgpt_moe_ep_num_params",
+    "mgpt_moe_ep_global_expert", "mgpt_moe_ep_bind_params", "mgpt_moe_ep_sync_weights", "mgpt_moe_ep_forward",
+    "mgpt_moe_ep_backward", "mgpt_moe_ep_received_counts", "mgpt_moe_ep_check_status",
+    "mgpt_moe_block_workspace_bytes", "mgpt_moe_block_forward", "mgpt_moe_block_backward",
+    "mgpt_moe_set_weight_grad_overwrite", "mgpt_moe_inference_workspace_bytes", "mgpt_moe_forward_inference", "mgpt_moe_experts_backward_rows", "mgpt_moe_experts_backward_params",
 ]
 PLAN_NOALLOC_MAX_ROWS = 1048576
 N_STAGES = 12
@@ -32,6 +36,15 @@ class Config(ct.Structure):
     _fields_ = [("embed_dim", ct.c_int), ("hidden_dim", ct.c_int), ("num_experts", ct.c_int),
                 ("top_k", ct.c_int), ("lb_alpha", ct.c_float), ("mode", ct.c_int), ("device", ct.c_int),
                 ("gemm_impl", ct.c_int)]
+
+
+class EpConfig(ct.Structure):
+    _fields_ = [("embed_dim", ct.c_int), ("hidden_dim", ct.c_int), ("num_experts", ct.c_int), ("top_k", ct.c_int),
+                ("lb_alpha", ct.c_float), ("mode", ct.c_int), ("device", ct.c_int), ("rank", ct.c_int),
+                ("world", ct.c_int), ("n_chunks", ct.c_int)]
+
+
+EP_ID_BYTES = 128
 
 
 class MoeError(RuntimeError):
@@ -62,6 +75,9 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_workspace_bytes.argtypes = [vp, i32]
     lib.mgpt_moe_workspace_bytes.restype = sz
     lib.mgpt_moe_forward.argtypes = [vp, vp, vp, i32, i32, vp, sz, vp]
+    lib.mgpt_moe_forward_inference.argtypes = [vp, vp, vp, i32, i32, vp, sz, vp]
+    lib.mgpt_moe_inference_workspace_bytes.argtypes = [vp, i32]
+    lib.mgpt_moe_inference_workspace_bytes.restype = sz
     lib.mgpt_moe_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]
     lib.mgpt_moe_expert_counts.argtypes = [vp, ct.POINTER(ct.c_int32)]
     lib.mgpt_moe_workspace_view.argtypes = [vp, i32, ct.c_char_p, ct.POINTER(sz), ct.POINTER(sz)]
@@ -98,6 +114,22 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_experts_backward.argtypes = [vp, vp, vp, vp, sz, vp]
     lib.mgpt_moe_experts_backward_rows.argtypes = [vp, vp, vp, vp, sz, vp]
     lib.mgpt_moe_experts_backward_params.argtypes = [vp, vp, vp, vp, sz, vp]
+    lib.mgpt_moe_ep_unique_id.argtypes = [vp]
+    lib.mgpt_moe_ep_create.argtypes = [ct.POINTER(EpConfig), vp, ct.POINTER(vp)]
+    lib.mgpt_moe_ep_destroy.argtypes = [vp]
+    lib.mgpt_moe_ep_destroy.restype = None
+    lib.mgpt_moe_ep_num_params.argtypes = [vp]
+    lib.mgpt_moe_ep_global_expert.argtypes = [vp, i32]
+    lib.mgpt_moe_ep_bind_params.argtypes = [vp, ct.POINTER(vp), ct.POINTER(vp), i32]
+    lib.mgpt_moe_ep_sync_weights.argtypes = [vp, vp]
+    lib.mgpt_moe_ep_forward.argtypes = [vp, vp, vp, i32, i32, vp]
+    lib.mgpt_moe_ep_backward.argtypes = [vp, vp, vp, vp, i32, vp]
+    lib.mgpt_moe_ep_received_counts.argtypes = [vp, ct.POINTER(ct.c_int32)]
+    lib.mgpt_moe_ep_check_status.argtypes = [vp]
+    lib.mgpt_moe_block_workspace_bytes.argtypes = [vp, i32, i32]
+    lib.mgpt_moe_block_workspace_bytes.restype = sz
+    lib.mgpt_moe_block_forward.argtypes = [vp, vp, vp, ct.c_float, vp, i32, i32, vp, sz, vp]
+    lib.mgpt_moe_block_backward.argtypes = [vp, vp, vp, vp, vp, vp, i32, vp, sz, vp]
     lib.mgpt_moe_op_plan_noalloc.argtypes = [vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
     _lib = lib
     return lib

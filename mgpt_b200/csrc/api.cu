@@ -2,6 +2,7 @@
 // and the forward / backward schedules.  See include/mgpt_moe.h for the
 // contract and the reference interfaces each entry point stands in for.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -46,7 +47,9 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     };
     const size_t rc = (size_t)w.row_cap, ab = w.act_bytes;
     const size_t big = kind == 1 ? 0 : 1;          // routing-side workspaces carry no activation buffers
-    const size_t rowbuf = kind == 0 ? 1 : 0;       // expert-side row buffers belong to the caller
+    const size_t rowbuf = (kind == 0 || kind == 3) ? 1 : 0;       // expert-side row buffers belong to the caller
+    const size_t bwd = kind == 3 ? 0 : 1;          // inference keeps nothing for backward
+    w.inference = kind == 3;
     w.logits = take(N * E * 4);
     w.probs = take(N * E * 4);
     w.top_idx = take(N * k * 4);
@@ -67,16 +70,16 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
     w.seg = take(E * MAX_SOURCES * 2 * 4);
     w.tile_order = take((size_t)w.max_tiles * 4);
     w.Xg = take(rowbuf * rc * C * ab);
-    w.G = take(big * rc * H * ab);
-    w.U = take(big * rc * H * ab);
+    w.G = take(bwd * big * rc * H * ab);
+    w.U = take(bwd * big * rc * H * ab);
     w.Hh = take(big * rc * H * ab);
     w.Yg = take(rowbuf * rc * C * ab);
-    w.dYg = take(rowbuf * rc * C * ab);
-    w.dG = take(big * rc * H * ab);
-    w.dU = take(big * rc * H * ab);
-    w.dXg = take(rowbuf * rc * C * ab);
-    w.d_top_p = take(N * k * 4);
-    w.dlogits = take(N * E * 4);
+    w.dYg = take(bwd * rowbuf * rc * C * ab);
+    w.dG = take(bwd * big * rc * H * ab);
+    w.dU = take(bwd * big * rc * H * ab);
+    w.dXg = take(bwd * rowbuf * rc * C * ab);
+    w.d_top_p = take(bwd * N * k * 4);
+    w.dlogits = take(bwd * N * E * 4);
     // router weight gradient: per-token-chunk partial sums, reduced in a second pass
     {
         const int e4 = (d.E + 3) / 4, ch_per_cta = (256 / e4) * 4;
@@ -87,8 +90,8 @@ Workspace make_workspace(const Dims& d, int n_tokens, int kind)
         if (chunks < 1) chunks = 1;
         w.rw_chunks = chunks;
     }
-    w.rw_part = take((size_t)w.rw_chunks * (C * E + E) * 4);
-    w.dl16 = take(N * ((E + 7) / 8 * 8) * 2);          // dlogits in bf16 for the tensor-core router backward
+    w.rw_part = take(bwd * (size_t)w.rw_chunks * (C * E + E) * 4);
+    w.dl16 = take(bwd * N * ((E + 7) / 8 * 8) * 2);          // dlogits in bf16 for the tensor-core router backward
     w.rt_list = take(N * 4);                            // screened router: tokens recomputed by the exact pass
     w.rt_count = take(4);
     w.total = off;
@@ -171,6 +174,7 @@ int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
             return cuda_fail(e, "cudaMalloc(router shadow)");
         }
         if (cfg->gemm_impl == 0) {
+            if (const char* env = getenv("MGPT_MOE_ROUTER_TC_MIN_WORK")) L->router_tc_min_work = atof(env);
             L->router_ne = router_tc_ne(E);
             const size_t pieces = (size_t)2 * L->router_ne * C * sizeof(bf16);
             e = cudaMalloc(&L->sWrT2, pieces);
@@ -376,7 +380,7 @@ int mgpt_moe_workspace_view(const mgpt_moe_layer* L, int n_tokens, const char* n
     return fail(MGPT_MOE_EINVAL, std::string("unknown workspace buffer: ") + name);
 }
 
-static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, size_t ws_bytes, Workspace* w)
+static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, size_t ws_bytes, Workspace* w, int kind = 0)
 {
     if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
     if (!L->bound) return fail(MGPT_MOE_ESTATE, "bind_params first (all 2+6E tensors for the whole-layer calls)");
@@ -384,7 +388,7 @@ static int check_call(mgpt_moe_layer* L, int n_tokens, int io, const void* ws, s
     if (io != MGPT_MOE_IO_F32 && io != MGPT_MOE_IO_BF16) return fail(MGPT_MOE_EINVAL, "unknown io dtype");
     if (L->d.mode == MGPT_MOE_FP32 && io != MGPT_MOE_IO_F32) return fail(MGPT_MOE_EINVAL, "FP32 mode takes FP32 tokens");
     if ((long long)n_tokens * L->d.k > (1ll << 30)) return fail(MGPT_MOE_EINVAL, "too many routed rows");
-    *w = make_workspace(L->d, n_tokens);
+    *w = make_workspace(L->d, n_tokens, kind);
     if (!ws || ((uintptr_t)ws & 255)) return fail(MGPT_MOE_EINVAL, "workspace must be 256-byte aligned");
     if (ws_bytes < w->total) return fail(MGPT_MOE_ENOMEM, "workspace smaller than mgpt_moe_workspace_bytes()");
     if (L->d.mode == MGPT_MOE_BF16 && !L->shadows_fresh)
@@ -461,7 +465,8 @@ int mgpt_moe_save_routing(mgpt_moe_layer* L, void* dst, mgpt_stream_t stream)
 }
 
 static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
-                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual = nullptr);
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual = nullptr,
+                        bool inference = false);
 
 int mgpt_moe_forward(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io,
                      void* workspace, size_t ws_bytes, mgpt_stream_t stream)
@@ -483,11 +488,23 @@ int mgpt_moe_forward_residual(mgpt_moe_layer* L, const void* x, const void* resi
     return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, nullptr, residual);
 }
 
+size_t mgpt_moe_inference_workspace_bytes(const mgpt_moe_layer* L, int n_tokens)
+{
+    if (!L || n_tokens < 0) return 0;
+    return make_workspace(L->d, n_tokens, 3).total;
+}
+
+int mgpt_moe_forward_inference(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
+                               size_t ws_bytes, mgpt_stream_t stream)
+{
+    return forward_impl(L, x, y, n_tokens, io, workspace, ws_bytes, stream, nullptr, nullptr, true);
+}
+
 static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens, int io, void* workspace,
-                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual)
+                        size_t ws_bytes, mgpt_stream_t stream, const void* routing, const void* residual, bool inference)
 {
     Workspace w;
-    MGPT_TRY(check_call(L, n_tokens, io, workspace, ws_bytes, &w));
+    MGPT_TRY(check_call(L, n_tokens, io, workspace, ws_bytes, &w, inference ? 3 : 0));
     if (n_tokens > 0 && (!x || !y)) return fail(MGPT_MOE_EINVAL, "null token buffer");
     MGPT_CUDA(cudaSetDevice(L->device));
     cudaStream_t st = (cudaStream_t)stream;
@@ -507,7 +524,7 @@ static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens,
     } else {
         if (n_tokens > 0) {
             L->stage_begin(ST_ROUTER, st);
-            if (tc_router_usable(L, x, io))
+            if (tc_router_usable(L, x, io, n_tokens))
                 MGPT_TRY(tc_router_fwd(L, w, ws, x, st));
             else
                 MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k,
@@ -533,7 +550,8 @@ static int forward_impl(mgpt_moe_layer* L, const void* x, void* y, int n_tokens,
     L->last_io = io;
     L->last_ws = workspace;
     L->last_stream = st;
-    L->fwd_done = true;
+    L->fwd_done = !inference;        // nothing was kept: backward cannot follow an inference forward
+    L->last_inference = inference;
     return 0;
 }
 
@@ -570,9 +588,9 @@ int mgpt_moe_backward(mgpt_moe_layer* L, const void* x, const void* dy, void* dx
 int mgpt_moe_expert_counts(mgpt_moe_layer* L, int32_t* host_counts)
 {
     if (!L || !host_counts) return fail(MGPT_MOE_EINVAL, "null argument");
-    if (!L->fwd_done) return fail(MGPT_MOE_ESTATE, "no forward has run");
+    if (!L->fwd_done && !L->last_inference) return fail(MGPT_MOE_ESTATE, "no forward has run");
     MGPT_CUDA(cudaSetDevice(L->device));
-    const Workspace w = make_workspace(L->d, L->last_n);
+    const Workspace w = make_workspace(L->d, L->last_n, L->last_inference ? 3 : 0);
     MGPT_CUDA(cudaMemcpyAsync(host_counts, (char*)L->last_ws + w.counts, (size_t)L->d.E * sizeof(int32_t),
                               cudaMemcpyDeviceToHost, L->last_stream));
     MGPT_TRY(status_fetch(L, L->last_stream));

@@ -81,6 +81,7 @@ struct Workspace {
     size_t total;
     // derived sizes
     int n_tokens, R, max_tiles, row_cap, plan_blocks, rw_chunks;
+    bool inference;     // forward-only layout: nothing is kept for a backward pass
     size_t act_bytes;   // bytes per activation element (2 or 4)
 };
 
@@ -92,7 +93,7 @@ struct Dims {
 };
 
 // kind 0: whole layer; kind 1: routing side only (no activation buffers; rows are exchanged by the caller);
-// kind 2: expert side (the four [rows, C] buffers belong to the caller)
+// kind 2: expert side (the four [rows, C] buffers belong to the caller); kind 3: whole layer, forward only (inference)
 Workspace make_workspace(const Dims& d, int n_tokens, int kind = 0);
 
 // Device-side tables of per-expert pointers (index = expert).
@@ -133,12 +134,14 @@ struct mgpt_moe_layer {
     mgpt::bf16* sWrT2 = nullptr;     // router weight transposed and split in two BF16 pieces: [2][NE][C], Wr^T ~ hi + mid
     float* d_rstat = nullptr;        // {max_e ||Wr[:,e]||_2, max_e |br[e]|}, slightly inflated (screened router's error bound)
     int router_ne = 0;               // NE: experts rounded up to 16, 32, 64 or 128
+    double router_tc_min_work = 4e8; // tokens*C*E from which the tensor-core first pass is used (MGPT_MOE_ROUTER_TC_MIN_WORK)
 
     // last forward (for backward / counts)
     int last_n = 0, last_io = 0;
     void* last_ws = nullptr;
     cudaStream_t last_stream = 0;
     bool fwd_done = false;
+    bool last_inference = false;             // the last forward was mgpt_moe_forward_inference (counts readable, no backward)
 
     // host staging for mgpt_moe_step_host
     void *h_x = nullptr, *h_dy = nullptr, *h_y = nullptr, *h_dx = nullptr, *h_ws = nullptr;
@@ -189,7 +192,7 @@ int launch_router_fwd(const void* x, int io, const float* Wr, const float* br, i
                       const int32_t* list = nullptr, const int32_t* list_count = nullptr);
 // router_tc.cu: the router for BF16 tokens -- tensor-core first pass plus exact recompute of the tokens whose
 // routing the first pass cannot prove
-bool tc_router_usable(const mgpt_moe_layer* L, const void* x, int io);
+bool tc_router_usable(const mgpt_moe_layer* L, const void* x, int io, int n_tokens);
 int tc_router_fwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st);
 int launch_router_pieces(mgpt_moe_layer* L, cudaStream_t st);
 int router_tc_ne(int E);

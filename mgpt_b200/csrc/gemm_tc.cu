@@ -22,6 +22,9 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets a bit in the
 // workspace status word and the CTA leaves through its normal teardown
 // (TMEM is released), so a fault in a descriptor cannot hang the device.
+#include <cstdio>
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace mgpt {
@@ -181,10 +184,11 @@ __device__ __forceinline__ int sched_consume(const Pipe& pipe, uint32_t n, int32
 }
 __device__ __forceinline__ void sched_release(const Pipe& pipe, uint32_t n) { mbar_arrive(pipe.sched_empty(n % SCHED_Q)); }
 // Once per CTA of the grid, by the producer thread after its last fetch (also CTAs that leave without fetching).
-__device__ __forceinline__ void sched_finish(int32_t* counter)
+// `n`: how many callers there are (every CTA of the grid, or every pair's leader)
+__device__ __forceinline__ void sched_finish(int32_t* counter, int n = -1)
 {
     __threadfence();
-    if (atomicAdd(counter + 1, 1) == (int)gridDim.x - 1) {
+    if (atomicAdd(counter + 1, 1) == (n < 0 ? (int)gridDim.x : n) - 1) {
         counter[0] = 0;
         counter[1] = 0;
         __threadfence();
@@ -192,11 +196,15 @@ __device__ __forceinline__ void sched_finish(int32_t* counter)
 }
 
 // Epilogue warp -> accumulator buffer is free again (all its tcgen05.ld of this tile are done).
-__device__ __forceinline__ void release_acc(uint32_t bar, int lane)
+// bar: a barrier of this CTA, or -- remote -- the shared::cluster address of a barrier of the pair's leader CTA.
+__device__ __forceinline__ void release_acc(uint32_t bar, int lane, bool remote = false)
 {
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
+    if (lane == 0) {
+        if (remote) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+        else mbar_arrive(bar);
+    }
 }
 
 // Writes this thread's row of a [32 rows x 32 bf16] tile into the warp's staging tile in the
@@ -267,6 +275,8 @@ struct RowsP {
     const int32_t* tile_expert;
     const int32_t* tile_order;  // optional: i-th row tile to work on (expert-major order over scattered tiles)
     const int32_t* n_tiles;
+    const int32_t* pairs;       // pair kernel: {first tile, second tile or -1} per pair, in processing order
+    const int32_t* n_pairs;
     int32_t* status;
     int32_t* sched;         // {next item, finished CTAs}, both zero between launches
     int kblocks;            // k-blocks (of 64) per operand pair
@@ -283,6 +293,152 @@ struct RowsP {
     const int32_t* gather_pos;  // [tokens, gather_k] row of dXg for (token, j)
     int gather_k;
 };
+
+// The epilogue of one work item for one of the 16 epilogue warps: TMEM lane quarter q (rows q*32..+31 of the row
+// tile), column group h.  acc_empty_bar is where "this warp has read the accumulator" is signalled: a barrier of
+// this CTA, or (remote) of the leader CTA of a pair.  store = false: the tile is a stand-in (a pair's missing
+// second tile): the accumulator is released and nothing is written.  False: a bounded wait ran out.
+template <int MODE>
+__device__ __forceinline__ bool rows_epilogue(const RowsP& p, uint32_t acc_full_bar, uint32_t acc_empty_bar, bool remote,
+                                              uint32_t tmem_base, uint32_t buf, uint32_t t, int row_tile, int n0, int e,
+                                              int q, int h, int lane, uint8_t* stage, const CUtensorMap* tmD0,
+                                              const CUtensorMap* tmD1, const CUtensorMap* tmD2, bool store)
+{
+    const int row_w = row_tile * BM + q * 32;           // first row of this warp
+    if (!store) {
+        if (!mbar_wait(acc_full_bar, (t >> 1) & 1, p.status, ERR_ACC_WAIT)) return false;
+        tc_fence_after();
+        release_acc(acc_empty_bar, lane, remote);
+        return true;
+    }
+    // MODE_DHH: the saved G and U of this item come from HBM.  Unit 0's pieces are requested before the wait
+    // for the accumulator, unit 1's while unit 0 is worked on, so their latency hides behind other work.
+    uint32_t gq[2][16], uq[2][16];
+    if (MODE == MODE_DHH) {
+        const int n = n0 + h * 64;
+        const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
+        load_blocked32(reinterpret_cast<const uint4*>(p.G) + o, gq[0], p.n_out - n);
+        load_blocked32(reinterpret_cast<const uint4*>(p.U) + o, uq[0], p.n_out - n);
+    }
+    if (!mbar_wait(acc_full_bar, (t >> 1) & 1, p.status, ERR_ACC_WAIT)) return false;
+    tc_fence_after();
+    const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+    if (MODE == MODE_GATEUP) {
+        // this warp: hidden units n0 + h*32 .. +31  (gate columns h*32.., up columns 128 + h*32..)
+        const int n = n0 + h * 32;
+        float a[32], b[32];
+        tmem_ld32(t_lane + h * 32, a);
+        tmem_ld32(t_lane + BN / 2 + h * 32, b);
+        tmem_ld_wait();
+        release_acc(acc_empty_bar, lane, remote);
+        if (n < p.n_out) {
+            // What backward needs of G and U is not the values themselves but
+            //   Q = silu(G)                       (dU = dHh * Q)
+            //   P = U * sigmoid(G) * (1 + G * (1 - sigmoid(G)))      (dG = dHh * P)
+            // (utils/Tensor.cpp:2020-2027), so those are what is kept: the sigmoid is evaluated once, here,
+            // in FP32 on the unrounded sums, and the dHh epilogue is left with two multiplies per element.
+            uint32_t pp[16], qp[16], hp[16];
+            add_bias32(a, p.bias0[e], n, p.n_out);
+            add_bias32(b, p.bias1[e], n, p.n_out);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float pv[2], qv[2], hv[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float g = a[2 * i + hh], u = b[2 * i + hh];
+                    const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+                    const float q = g * sig;
+                    qv[hh] = q;
+                    hv[hh] = q * u;
+                    pv[hh] = (u * sig) * (1.0f + (g - q));
+                }
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(pv[0], pv[1]);
+                __nv_bfloat162 q2 = __floats2bfloat162_rn(qv[0], qv[1]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(hv[0], hv[1]);
+                pp[i] = *reinterpret_cast<uint32_t*>(&p2);
+                qp[i] = *reinterpret_cast<uint32_t*>(&q2);
+                hp[i] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            if (p.G) {                                  // inference keeps nothing for a backward pass
+                const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
+                store_blocked32(reinterpret_cast<uint4*>(p.G) + o, pp, p.n_out - n);
+                store_blocked32(reinterpret_cast<uint4*>(p.U) + o, qp, p.n_out - n);
+            }
+            stage_row_bf16(stage, lane, hp);
+            flush_stage(stage, tmD2, n, row_w, lane);
+        }
+    } else {
+        // this warp: columns n0 + h*64 .. +63, two units of 32
+#pragma unroll
+        for (int un = 0; un < 2; ++un) {
+            const int n = n0 + h * 64 + un * 32;
+            float v[32];
+            tmem_ld32(t_lane + h * 64 + un * 32, v);
+            tmem_ld_wait();
+            if (un == 1) release_acc(acc_empty_bar, lane, remote);
+            if (n >= p.n_out) continue;                      // warp-uniform
+            uint32_t pk[16];
+            if (MODE == MODE_DOWN) {
+                add_bias32(v, p.bias0[e], n, p.n_out);
+            } else if (MODE == MODE_DHH) {
+                // utils/Tensor.cpp:2020-2027 with dd = dHh: dG = dd * P, dU = dd * Q (P, Q saved by the forward epilogue)
+                if (un == 0) {
+                    const int n1 = n + 32;
+                    const size_t o1 = blocked_index(row_tile, p.n_out, n1, q * 32 + lane);
+                    load_blocked32(reinterpret_cast<const uint4*>(p.G) + o1, gq[1], p.n_out - n1);
+                    load_blocked32(reinterpret_cast<const uint4*>(p.U) + o1, uq[1], p.n_out - n1);
+                }
+                uint32_t (&gw)[16] = gq[un];
+                uint32_t (&uw)[16] = uq[un];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float d0 = v[2 * i], d1 = v[2 * i + 1];
+                    __nv_bfloat162 a2 = __floats2bfloat162_rn(d0 * bf_lo(gw[i]), d1 * bf_hi(gw[i]));
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(d0 * bf_lo(uw[i]), d1 * bf_hi(uw[i]));
+                    gw[i] = *reinterpret_cast<uint32_t*>(&a2);      // dG, packed in place
+                    uw[i] = *reinterpret_cast<uint32_t*>(&b2);      // dU, packed in place
+                }
+                stage_row_bf16(stage, lane, uw);
+                flush_stage(stage, tmD1, n, row_w, lane);
+                stage_row_bf16(stage, lane, gw);
+                flush_stage(stage, tmD0, n, row_w, lane);
+                continue;
+            } else if (MODE == MODE_DX) {
+                // dx = (sum of the token's expert rows, ascending row order) + dlogits * Wr^T
+                const int tok = row_w + lane;
+                if (tok < p.n_valid_rows) {
+                    int ps[MAX_TOPK];
+#pragma unroll
+                    for (int j = 0; j < MAX_TOPK; ++j)
+                        ps[j] = j < p.gather_k ? p.gather_pos[(size_t)tok * p.gather_k + j] : 0x7fffffff;
+#pragma unroll
+                    for (int a = 0; a < MAX_TOPK - 1; ++a)
+#pragma unroll
+                        for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
+                            if (ps[b] > ps[b + 1]) {
+                                const int tmp = ps[b];
+                                ps[b] = ps[b + 1];
+                                ps[b + 1] = tmp;
+                            }
+                    const int valid = min(32, p.n_out - n);
+#pragma unroll
+                    for (int j = 0; j < MAX_TOPK; ++j) {
+                        if (j < p.gather_k) {
+                            float g[32];
+                            load_bf16x32(p.gather_src + (size_t)ps[j] * p.n_out + n, g, valid);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += g[i];
+                        }
+                    }
+                }
+            }
+            pack32(v, pk);
+            stage_row_bf16(stage, lane, pk);
+            flush_stage(stage, tmD0, n, row_w, lane);
+        }
+    }
+    return true;
+}
 
 // Persistent: CTA b works on items b, b+grid, ... where item = row_tile * n_col_tiles + col_tile.
 // Two 256-column accumulators in TMEM alternate, so the epilogue of one item runs while the
@@ -391,136 +547,16 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             const int row_i = item / p.n_col_tiles, n0 = (item % p.n_col_tiles) * COLS_PER_ITEM;
             const int row_tile = p.tile_order ? p.tile_order[row_i] : row_i;
             const int e = MODE == MODE_DX ? 0 : p.tile_expert[row_tile];
-            const int row_w = row_tile * BM + q * 32;           // first row of this warp
-            // MODE_DHH: the saved G and U of this item come from HBM.  Unit 0's pieces are requested before the wait
-            // for the accumulator, unit 1's while unit 0 is worked on, so their latency hides behind other work.
-            uint32_t gq[2][16], uq[2][16];
-            if (MODE == MODE_DHH) {
-                const int n = n0 + h * 64;
-                const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
-                load_blocked32(reinterpret_cast<const uint4*>(p.G) + o, gq[0], p.n_out - n);
-                load_blocked32(reinterpret_cast<const uint4*>(p.U) + o, uq[0], p.n_out - n);
-            }
-            if (!mbar_wait(pipe.acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
-            tc_fence_after();
-            const uint32_t t_lane = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
-            if (MODE == MODE_GATEUP) {
-                // this warp: hidden units n0 + h*32 .. +31  (gate columns h*32.., up columns 128 + h*32..)
-                const int n = n0 + h * 32;
-                float a[32], b[32];
-                tmem_ld32(t_lane + h * 32, a);
-                tmem_ld32(t_lane + BN / 2 + h * 32, b);
-                tmem_ld_wait();
-                release_acc(pipe.acc_empty(buf), lane);
-                if (n < p.n_out) {
-                    // What backward needs of G and U is not the values themselves but
-                    //   Q = silu(G)                       (dU = dHh * Q)
-                    //   P = U * sigmoid(G) * (1 + G * (1 - sigmoid(G)))      (dG = dHh * P)
-                    // (utils/Tensor.cpp:2020-2027), so those are what is kept: the sigmoid is evaluated once, here,
-                    // in FP32 on the unrounded sums, and the dHh epilogue is left with two multiplies per element.
-                    uint32_t pp[16], qp[16], hp[16];
-                    add_bias32(a, p.bias0[e], n, p.n_out);
-                    add_bias32(b, p.bias1[e], n, p.n_out);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float pv[2], qv[2], hv[2];
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            const float g = a[2 * i + hh], u = b[2 * i + hh];
-                            const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
-                            const float q = g * sig;
-                            qv[hh] = q;
-                            hv[hh] = q * u;
-                            pv[hh] = (u * sig) * (1.0f + (g - q));
-                        }
-                        __nv_bfloat162 p2 = __floats2bfloat162_rn(pv[0], pv[1]);
-                        __nv_bfloat162 q2 = __floats2bfloat162_rn(qv[0], qv[1]);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(hv[0], hv[1]);
-                        pp[i] = *reinterpret_cast<uint32_t*>(&p2);
-                        qp[i] = *reinterpret_cast<uint32_t*>(&q2);
-                        hp[i] = *reinterpret_cast<uint32_t*>(&h2);
-                    }
-                    const size_t o = blocked_index(row_tile, p.n_out, n, q * 32 + lane);
-                    store_blocked32(reinterpret_cast<uint4*>(p.G) + o, pp, p.n_out - n);
-                    store_blocked32(reinterpret_cast<uint4*>(p.U) + o, qp, p.n_out - n);
-                    stage_row_bf16(stage, lane, hp);
-                    flush_stage(stage, &tmD2, n, row_w, lane);
-                }
-            } else {
-                // this warp: columns n0 + h*64 .. +63, two units of 32
-#pragma unroll
-                for (int un = 0; un < 2; ++un) {
-                    const int n = n0 + h * 64 + un * 32;
-                    float v[32];
-                    tmem_ld32(t_lane + h * 64 + un * 32, v);
-                    tmem_ld_wait();
-                    if (un == 1) release_acc(pipe.acc_empty(buf), lane);
-                    if (n >= p.n_out) continue;                      // warp-uniform
-                    uint32_t pk[16];
-                    if (MODE == MODE_DOWN) {
-                        add_bias32(v, p.bias0[e], n, p.n_out);
-                    } else if (MODE == MODE_DHH) {
-                        // utils/Tensor.cpp:2020-2027 with dd = dHh: dG = dd * P, dU = dd * Q (P, Q saved by the forward epilogue)
-                        if (un == 0) {
-                            const int n1 = n + 32;
-                            const size_t o1 = blocked_index(row_tile, p.n_out, n1, q * 32 + lane);
-                            load_blocked32(reinterpret_cast<const uint4*>(p.G) + o1, gq[1], p.n_out - n1);
-                            load_blocked32(reinterpret_cast<const uint4*>(p.U) + o1, uq[1], p.n_out - n1);
-                        }
-                        uint32_t (&gw)[16] = gq[un];
-                        uint32_t (&uw)[16] = uq[un];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float d0 = v[2 * i], d1 = v[2 * i + 1];
-                            __nv_bfloat162 a2 = __floats2bfloat162_rn(d0 * bf_lo(gw[i]), d1 * bf_hi(gw[i]));
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(d0 * bf_lo(uw[i]), d1 * bf_hi(uw[i]));
-                            gw[i] = *reinterpret_cast<uint32_t*>(&a2);      // dG, packed in place
-                            uw[i] = *reinterpret_cast<uint32_t*>(&b2);      // dU, packed in place
-                        }
-                        stage_row_bf16(stage, lane, uw);
-                        flush_stage(stage, &tmD1, n, row_w, lane);
-                        stage_row_bf16(stage, lane, gw);
-                        flush_stage(stage, &tmD0, n, row_w, lane);
-                        continue;
-                    } else if (MODE == MODE_DX) {
-                        // dx = (sum of the token's expert rows, ascending row order) + dlogits * Wr^T
-                        const int tok = row_w + lane;
-                        if (tok < p.n_valid_rows) {
-                            int ps[MAX_TOPK];
-#pragma unroll
-                            for (int j = 0; j < MAX_TOPK; ++j)
-                                ps[j] = j < p.gather_k ? p.gather_pos[(size_t)tok * p.gather_k + j] : 0x7fffffff;
-#pragma unroll
-                            for (int a = 0; a < MAX_TOPK - 1; ++a)
-#pragma unroll
-                                for (int b = 0; b < MAX_TOPK - 1 - a; ++b)
-                                    if (ps[b] > ps[b + 1]) {
-                                        const int tmp = ps[b];
-                                        ps[b] = ps[b + 1];
-                                        ps[b + 1] = tmp;
-                                    }
-                            const int valid = min(32, p.n_out - n);
-#pragma unroll
-                            for (int j = 0; j < MAX_TOPK; ++j) {
-                                if (j < p.gather_k) {
-                                    float g[32];
-                                    load_bf16x32(p.gather_src + (size_t)ps[j] * p.n_out + n, g, valid);
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i) v[i] += g[i];
-                                }
-                            }
-                        }
-                    }
-                    pack32(v, pk);
-                    stage_row_bf16(stage, lane, pk);
-                    flush_stage(stage, &tmD0, n, row_w, lane);
-                }
-            }
+            if (!rows_epilogue<MODE>(p, pipe.acc_full(buf), pipe.acc_empty(buf), false, tmem_base, buf, t, row_tile, n0, e, q, h,
+                                     lane, stage, &tmD0, &tmD1, &tmD2, true))
+                break;
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores landed before exit
     }
     cta_teardown(tmem_base, warp);
 }
+
+#include "gemm_tc_pair.inl"
 
 // ---- weight gradients: grad[e][M,N] += A_e^T * B_e over the expert's rows ---------
 // One weight-gradient problem: grad[e][M,N] += A_e^T * B_e over the rows of "expert" e.
@@ -890,6 +926,7 @@ struct TcState {
     int n_tokens = -1;
     bool attr_set = false;
     int sms = 0;
+    int max_pairs = 0;           // CTA pairs (clusters of two) that can be resident at once; 0 = pair kernels off
     int32_t* sched = nullptr;    // device: one {next item, finished CTAs} pair per kind of launch, zero between launches
     // K-major operand loads (box 64 x 128 rows)
     CUtensorMap Xg, Hh, dYg, dG, dU, WgT, WuT, WdT, Wg, Wu, Wd;
@@ -948,6 +985,35 @@ int prepare_attrs(mgpt_moe_layer* L)
         MGPT_CUDA(cudaFuncSetAttribute(tc_rows_kernel<MODE_DX>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         MGPT_CUDA(cudaDeviceGetAttribute(&s->sms, cudaDevAttrMultiProcessorCount, L->device));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_pair_kernel<MODE_GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_pair_kernel<MODE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_pair_kernel<MODE_DHH>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        MGPT_CUDA(cudaFuncSetAttribute(tc_rows_pair_kernel<MODE_DXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        {
+            // The CTA-pair kernels (gemm_tc_pair.inl) are opt-in, MGPT_MOE_CTA_PAIRS=1 in the environment: measured on
+            // B200 they match the single-CTA kernels at the 64-expert shapes (both sit at ~82-90 % of what cuBLAS
+            // sustains under the 1 kW power cap) and lose a little on small shapes.  How many clusters of two CTAs
+            // fit on the device at once is asked of the driver (SMs pair up within a GPC).
+            const char* env = getenv("MGPT_MOE_CTA_PAIRS");
+            s->max_pairs = 0;
+            if (env && env[0] == '1') {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(2 * (unsigned)s->sms, 1, 1);
+                cfg.blockDim = dim3(TC_THREADS, 1, 1);
+                cfg.dynamicSmemBytes = SMEM_BYTES;
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+                cfg.attrs = at;
+                cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, tc_rows_pair_kernel<MODE_DOWN>, &cfg) == cudaSuccess && n > 0)
+                    s->max_pairs = n;
+                else
+                    cudaGetLastError();       // no pairs on this device: the single-CTA kernels stay
+            }
+            if (getenv("MGPT_MOE_VERBOSE")) fprintf(stderr, "mgpt_moe: %d SMs, %d resident CTA pairs\n", s->sms, s->max_pairs);
+        }
         // the work-item counters must read zero before the first launch on any stream: allocate and clear them
         // here, at layer creation, and wait for the clear (nothing orders the legacy stream with a caller's
         // non-blocking stream)
@@ -970,6 +1036,25 @@ int grid_sms(const mgpt_moe_layer* L, const TcState* s) { return L->sm_budget > 
 // item to sum it: the B tile of gWd has four boxes and is loaded once per 128-row tile of H, two boxes per item.
 bool tc_fused_bias_grads(const Dims& d) { return cdiv(d.H, BM) >= 2; }
 
+namespace {
+// One of the four token-major products: on CTA pairs where the device takes them, else one CTA per tile.
+template <int MODE>
+int launch_rows(mgpt_moe_layer* L, TcState* s, const Workspace& w, const RowsP& p, const CUtensorMap& a0, const CUtensorMap& a1,
+                const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& d0, const CUtensorMap& d1,
+                const CUtensorMap& d2, cudaStream_t st, const char* what)
+{
+    const int budget = grid_sms(L, s);
+    if (s->max_pairs > 0 && p.pairs) {
+        const int pairs = imin(imin(s->max_pairs, budget / 2), w.max_tiles * p.n_col_tiles);
+        tc_rows_pair_kernel<MODE><<<2 * (pairs > 0 ? pairs : 1), TC_THREADS, SMEM_BYTES, st>>>(a0, a1, b0, b1, d0, d1, d2, p);
+    } else {
+        tc_rows_kernel<MODE><<<imin(budget, w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(a0, a1, b0, b1, d0, d1, d2, p);
+    }
+    MGPT_LAUNCHED(what);
+    return 0;
+}
+}  // namespace
+
 int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStream_t st)
 {
     MGPT_TRY(prepare(L, w, ws));
@@ -979,25 +1064,24 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
+    p.pairs = (const int32_t*)(ws + w.pairs);
+    p.n_pairs = (const int32_t*)(ws + w.n_pairs);
     p.status = L->d_status;
     // gate/up + SwiGLU: K = C, 128 hidden units per item
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN / 2);
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
-    p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
+    p.G = w.inference ? nullptr : (bf16*)(ws + w.G);
+    p.U = w.inference ? nullptr : (bf16*)(ws + w.U);
     L->stage_begin(ST_GATEUP, st);
     p.sched = s->sched + 0;
-    tc_rows_kernel<MODE_GATEUP><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->Xg, s->Xg, s->WgT, s->WuT, s->Hh_s, s->Hh_s, s->Hh_s, p);
-    MGPT_LAUNCHED("tc_rows_kernel<gateup>");
+    MGPT_TRY(launch_rows<MODE_GATEUP>(L, s, w, p, s->Xg, s->Xg, s->WgT, s->WuT, s->Hh_s, s->Hh_s, s->Hh_s, st, "tc_rows<gateup>"));
     L->stage_end(ST_GATEUP, st);
     // down: K = H
     p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
     p.bias0 = L->master.bd; p.bias1 = nullptr;
     L->stage_begin(ST_DOWN, st);
     p.sched = s->sched + 2;
-    tc_rows_kernel<MODE_DOWN><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->Hh, s->Hh, s->WdT, s->WdT, s->Yg_s, s->Yg_s, s->Yg_s, p);
-    MGPT_LAUNCHED("tc_rows_kernel<down>");
+    MGPT_TRY(launch_rows<MODE_DOWN>(L, s, w, p, s->Hh, s->Hh, s->WdT, s->WdT, s->Yg_s, s->Yg_s, s->Yg_s, st, "tc_rows<down>"));
     L->stage_end(ST_DOWN, st);
     return 0;
 }
@@ -1013,23 +1097,21 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     p.tile_expert = (const int32_t*)(ws + w.tile_expert);
     p.tile_order = L->n_seg > 0 ? (const int32_t*)(ws + w.tile_order) : nullptr;
     p.n_tiles = (const int32_t*)(ws + w.n_tiles);
+    p.pairs = (const int32_t*)(ws + w.pairs);
+    p.n_pairs = (const int32_t*)(ws + w.n_pairs);
     p.status = L->d_status;
     // dHh = dYg * Wd^T  (K = C), SwiGLU backward in the epilogue
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN);
     p.G = (bf16*)(ws + w.G); p.U = (bf16*)(ws + w.U);
     L->stage_begin(ST_DHH, st);
     p.sched = s->sched + 4;
-    tc_rows_kernel<MODE_DHH><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->dYg, s->dYg, s->Wd, s->Wd, s->dG_s, s->dU_s, s->dU_s, p);
-    MGPT_LAUNCHED("tc_rows_kernel<dhh>");
+    MGPT_TRY(launch_rows<MODE_DHH>(L, s, w, p, s->dYg, s->dYg, s->Wd, s->Wd, s->dG_s, s->dU_s, s->dU_s, st, "tc_rows<dhh>"));
     L->stage_end(ST_DHH, st);
     // dXg = dG * Wg^T + dU * Wu^T  (K = 2H)
     p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
     L->stage_begin(ST_DXG, st);
     p.sched = s->sched + 6;
-    tc_rows_kernel<MODE_DXG><<<imin(grid_sms(L, s), w.max_tiles * p.n_col_tiles), TC_THREADS, SMEM_BYTES, st>>>(
-        s->dG, s->dU, s->Wg, s->Wu, s->dXg_s, s->dXg_s, s->dXg_s, p);
-    MGPT_LAUNCHED("tc_rows_kernel<dxg>");
+    MGPT_TRY(launch_rows<MODE_DXG>(L, s, w, p, s->dG, s->dU, s->Wg, s->Wu, s->dXg_s, s->dXg_s, s->dXg_s, st, "tc_rows<dxg>"));
     L->stage_end(ST_DXG, st);
     }
     if (!L->has_grad || !(phase & 2)) return 0;

@@ -152,6 +152,82 @@ plan_assign_kernel(const int32_t* __restrict__ top_idx, int R, int E,
     }
 }
 
+// The whole plan in one block, for up to PLAN_BLOCK routed rows (decode-sized batches): histogram, prefix sums, tile
+// and pair lists and the stable slot assignment without leaving the SM -- one launch instead of three.
+__global__ void __launch_bounds__(PLAN_BLOCK)
+plan_small_kernel(const int32_t* __restrict__ top_idx, int R, int E, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets, int32_t* __restrict__ padded_offsets, int32_t* __restrict__ tile_expert,
+                  int32_t* __restrict__ n_tiles, int max_tiles, int32_t* __restrict__ map, int32_t* __restrict__ pos,
+                  int32_t* __restrict__ row_src, int32_t* __restrict__ slot_of, int32_t* __restrict__ status,
+                  int32_t* __restrict__ sticky, int32_t* __restrict__ pairs, int32_t* __restrict__ n_pairs)
+{
+    __shared__ int warp_cnt[PLAN_BLOCK / 32][MAX_EXPERTS];
+    __shared__ int tot[MAX_EXPERTS], off[MAX_EXPERTS + 1], poff[MAX_EXPERTS + 1], pair0[MAX_EXPERTS + 1];
+    __shared__ int bad;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < (PLAN_BLOCK / 32) * MAX_EXPERTS; i += PLAN_BLOCK) (&warp_cnt[0][0])[i] = 0;
+    if (threadIdx.x == 0) bad = 0;
+    __syncthreads();
+    const int i = threadIdx.x;
+    bool valid = i < R;
+    int e = valid ? top_idx[i] : 0;
+    if (valid && (unsigned)e >= (unsigned)E) {
+        bad = 1;
+        valid = false;
+    }
+    if (!valid) e = -1 - lane;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (threadIdx.x < E) {
+        int t = 0;
+        for (int w = 0; w < PLAN_BLOCK / 32; ++w) t += warp_cnt[w][threadIdx.x];
+        tot[threadIdx.x] = t;
+        counts[threadIdx.x] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, p = 0, np = 0;
+        for (int x = 0; x < E; ++x) {
+            off[x] = o; poff[x] = p; pair0[x] = np;
+            offsets[x] = o; padded_offsets[x] = p;
+            const int tiles = (tot[x] + ROW_TILE - 1) / ROW_TILE;
+            o += tot[x]; p += tiles * ROW_TILE; np += (tiles + 1) / 2;
+        }
+        off[E] = o; poff[E] = p; pair0[E] = np;
+        padded_offsets[E] = p;
+        *n_tiles = p / ROW_TILE;
+        if (n_pairs) *n_pairs = np;
+        const int st = (p / ROW_TILE > max_tiles ? ST_PLAN_OVERFLOW : 0) | (bad ? ST_BAD_EXPERT : 0);
+        *status = st;
+        if (sticky && st) atomicOr(sticky, st);
+    }
+    __syncthreads();
+    if (threadIdx.x < E) {
+        const int x = threadIdx.x;
+        const int t0 = poff[x] / ROW_TILE, t1 = poff[x + 1] / ROW_TILE;
+        int pi = pair0[x];
+        for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = x;
+        if (pairs)
+            for (int t = t0; t < t1 && t < max_tiles; t += 2, ++pi) {
+                pairs[2 * pi] = t;
+                pairs[2 * pi + 1] = (t + 1 < t1 && t + 1 < max_tiles) ? t + 1 : -1;
+            }
+        for (int q = poff[x] + tot[x]; q < poff[x + 1]; ++q) row_src[q] = -1;
+    }
+    if (valid) {
+        int base = 0;
+        for (int w = 0; w < warp; ++w) base += warp_cnt[w][e];
+        const int r = base + rank_in_warp;
+        const int slot = off[e] + r, p = poff[e] + r;
+        map[slot] = i;
+        pos[i] = p;
+        row_src[p] = i;
+        if (slot_of) slot_of[i] = slot;
+    }
+}
+
 // Xg[p,:] = x[row_src[p]/k,:]  (zero for padding rows).  One warp per row, 16-byte accesses.
 template <typename TIn, typename TAct>
 __global__ void __launch_bounds__(256)
@@ -365,6 +441,12 @@ int run_plan(const int32_t* top_idx, int R, int E, int32_t* counts, int32_t* off
              int32_t* sticky, int32_t* pairs, int32_t* n_pairs)
 {
     const int plan_blocks = R > 0 ? (R + PLAN_BLOCK - 1) / PLAN_BLOCK : 1;
+    if (R <= PLAN_BLOCK) {
+        plan_small_kernel<<<1, PLAN_BLOCK, 0, st>>>(top_idx, R, E, counts, offsets, padded_offsets, tile_expert, n_tiles,
+                                                    max_tiles, map, pos, row_src, slot_of, status, sticky, pairs, n_pairs);
+        MGPT_LAUNCHED("plan_small_kernel");
+        return 0;
+    }
     (void)row_cap;      // rows beyond the plan's tiles are never read; padding rows are marked by plan_assign_kernel
     plan_count_kernel<<<plan_blocks, PLAN_BLOCK, 0, st>>>(top_idx, R, E, blk);
     MGPT_LAUNCHED("plan_count_kernel");

@@ -523,6 +523,15 @@ int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, i
                         float* logits, float* probs, int32_t* top_idx, float* top_p, cudaStream_t st,
                         const int32_t* list, const int32_t* list_count)
 {
+    // Decode-sized batches: too few tokens to fill the device, what is left is the latency of one CTA, which is the
+    // length of its dependent addition chains: one token per warp pass keeps it shortest.
+    if (!list && N <= 1024) {
+        if (E <= 8) return router_fwd_launch<TIn, 8, 1, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+        if (E <= 16) return router_fwd_launch<TIn, 16, 1, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+        if (E <= 32) return router_fwd_launch<TIn, 32, 1, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+        if (E <= 64) return router_fwd_launch<TIn, 32, 2, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+        return router_fwd_launch<TIn, 32, 4, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
+    }
     // Second pass of the screened router: a fraction of the tokens, how many is only known on the device.  Small
     // CTAs (16 tokens) so that the few thousand listed tokens still spread over every SM.
     if (list && E > 32 && E <= 64)

@@ -346,10 +346,12 @@ int launch_router_pieces(mgpt_moe_layer* L, cudaStream_t st)
     return 0;
 }
 
-bool tc_router_usable(const mgpt_moe_layer* L, const void* x, int io)
+// The two-pass router pays off once the exact kernel's 2*N*C*E multiply-adds take longer than two launches and a
+// first pass over x: below ~4e8 of them (config 2: 6.7e7; decode batches) the exact kernel alone is faster.
+bool tc_router_usable(const mgpt_moe_layer* L, const void* x, int io, int n_tokens)
 {
     return L->d.mode == MGPT_MOE_BF16 && L->d.gemm_impl == 0 && io == MGPT_MOE_IO_BF16 && L->sWrT2 != nullptr &&
-           ((uintptr_t)x & 15) == 0;
+           ((uintptr_t)x & 15) == 0 && (double)n_tokens * L->d.C * L->d.E >= L->router_tc_min_work;
 }
 
 int tc_router_fwd(mgpt_moe_layer* L, const Workspace& w, char* ws, const void* x, cudaStream_t st)

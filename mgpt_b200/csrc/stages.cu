@@ -70,7 +70,7 @@ int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void*
     char* ws = (char*)workspace;
     const Dims& d = L->d;
     if (n_tokens > 0) {
-        if (tc_router_usable(L, x, io))
+        if (tc_router_usable(L, x, io, n_tokens))
             MGPT_TRY(tc_router_fwd(L, w, ws, x, st));
         else
             MGPT_TRY(launch_router_fwd(x, io, L->p_data[0], L->p_data[1], n_tokens, d.C, d.E, d.k, (float*)(ws + w.logits),

@@ -407,3 +407,112 @@ class ExpertParallelMoE:
         dx = self.stages.route_backward(x, d_back)
         self._mark("route_backward")
         return dx
+
+
+class NativeExpertParallelMoE:
+    """The same layer through the C ABI alone (``mgpt_moe_ep_*``): routing, exchange (NCCL point-to-point on the
+    library's own stream) and overlap all happen inside ``libmgpt_moe.so``, which is what an engine written in C++
+    binds.  torch is used here for device memory and, in ``create_id``, to hand rank 0's NCCL id to the other ranks."""
+
+    def __init__(self, embed_dim, hidden_dim, num_experts, top_k, *, rank=0, world=1, nccl_id=None, mode="bf16",
+                 device=0, lb_alpha=0.01, n_chunks=1):
+        from . import _lib
+        self._lib_mod = _lib
+        self.lib = _lib.load()
+        self.C = embed_dim
+        self.H = 4 * embed_dim if hidden_dim == -1 else hidden_dim
+        self.E, self.k, self.rank, self.world, self.n_chunks = num_experts, top_k, rank, world, n_chunks
+        self.E_local = num_experts // world
+        self.device = torch.device("cuda", device)
+        m = {"fp32": _lib.FP32, "bf16": _lib.BF16}[mode]
+        cfg = _lib.EpConfig(embed_dim, hidden_dim, num_experts, top_k, lb_alpha, m, device, rank, world, n_chunks)
+        self._h = ct.c_void_p()
+        idbuf = (ct.c_char * _lib.EP_ID_BYTES).from_buffer_copy(nccl_id) if nccl_id is not None else None
+        _lib.check(self.lib.mgpt_moe_ep_create(ct.byref(cfg), idbuf, ct.byref(self._h)))
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.params = [torch.zeros(self.C, self.E, **f32), torch.zeros(1, self.E, **f32)]
+        for _ in range(self.E_local):
+            self.params += [torch.zeros(self.C, self.H, **f32), torch.zeros(1, self.H, **f32), torch.zeros(self.C, self.H, **f32),
+                            torch.zeros(1, self.H, **f32), torch.zeros(self.H, self.C, **f32), torch.zeros(1, self.C, **f32)]
+        for p in self.params:
+            p.grad = torch.zeros_like(p)
+        n = len(self.params)
+        assert n == self.lib.mgpt_moe_ep_num_params(self._h)
+        data = (ct.c_void_p * n)(*[p.data_ptr() for p in self.params])
+        grad = (ct.c_void_p * n)(*[p.grad.data_ptr() for p in self.params])
+        _lib.check(self.lib.mgpt_moe_ep_bind_params(self._h, data, grad, n))
+        self._x = None
+
+    @staticmethod
+    def create_id(group=None) -> bytes:
+        """Rank 0 asks NCCL for an id; every rank of the torch.distributed group gets it."""
+        from . import _lib
+        lib = _lib.load()
+        buf = torch.zeros(_lib.EP_ID_BYTES, dtype=torch.uint8)
+        if not dist.is_initialized() or dist.get_rank(group) == 0:
+            raw = (ct.c_char * _lib.EP_ID_BYTES)()
+            _lib.check(lib.mgpt_moe_ep_unique_id(raw))
+            buf = torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8).clone()
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dev = buf.cuda() if dist.get_backend(group) == "nccl" else buf
+            dist.broadcast(dev, src=0, group=group)
+            buf = dev.cpu()
+        return bytes(buf.numpy().tobytes())
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            self.lib.mgpt_moe_ep_destroy(self._h)
+            self._h = ct.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _stream():
+        return ct.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def get_parameters(self):
+        return self.params
+
+    def global_expert(self, local_index: int) -> int:
+        return int(self.lib.mgpt_moe_ep_global_expert(self._h, local_index))
+
+    def load_parameters(self, full_params):
+        import numpy as np
+        mine = list(full_params[:2])
+        for l in range(self.E_local):
+            e = self.global_expert(l)
+            mine += list(full_params[2 + 6 * e: 2 + 6 * (e + 1)])
+        for p, a in zip(self.params, mine):
+            t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)) if not torch.is_tensor(a) else a
+            p.copy_(t.reshape(p.shape))
+        self._lib_mod.check(self.lib.mgpt_moe_ep_sync_weights(self._h, self._stream()))
+
+    def zero_grad(self):
+        for p in self.params:
+            p.grad.zero_()
+
+    def _io(self, t):
+        return self._lib_mod.IO_BF16 if t.dtype == torch.bfloat16 else self._lib_mod.IO_F32
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = torch.empty_like(x)
+        self._lib_mod.check(self.lib.mgpt_moe_ep_forward(self._h, x.data_ptr(), y.data_ptr(), x.shape[0], self._io(x),
+                                                         self._stream()))
+        self._x = x
+        buf = (ct.c_int32 * (self.world * self.E_local))()
+        self._lib_mod.check(self.lib.mgpt_moe_ep_received_counts(self._h, buf))
+        self.last_recv_counts = torch.tensor(list(buf), dtype=torch.int32).view(self.world, self.E_local)
+        return y
+
+    def backward(self, dy: torch.Tensor) -> torch.Tensor:
+        dx = torch.empty_like(dy)
+        self._lib_mod.check(self.lib.mgpt_moe_ep_backward(self._h, self._x.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                                          self._io(dy), self._stream()))
+        return dx
+
+    def check_status(self):
+        self._lib_mod.check(self.lib.mgpt_moe_ep_check_status(self._h))

@@ -156,6 +156,56 @@ class MoELayer:
         self.forward_into(x, out)
         return out
 
+    def forward_inference_into(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """Forward for generation (pipeline/Generator.cpp:10-31 runs forward only and drops the activations):
+        same routing and output as ``forward_into``, nothing kept for backward, a smaller workspace."""
+        assert x.is_cuda and x.is_contiguous() and x.shape[-1] == self.C
+        assert out.shape == x.shape and out.dtype == x.dtype and out.is_contiguous()
+        n = x.numel() // self.C
+        need = int(self.lib.mgpt_moe_inference_workspace_bytes(self._h, n))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        ws = self._ws
+        _lib.check(self.lib.mgpt_moe_forward_inference(self._h, x.data_ptr(), out.data_ptr(), n, self._io(x),
+                                                       ws.data_ptr(), ws.numel(), self._stream()))
+        self._x, self._n = None, n
+        self.cached_out = out
+
+    def forward_inference(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(x)
+        self.forward_inference_into(x, out)
+        return out
+
+    # -- the block's glue: x2 = x1 + moe(rmsnorm(x1)*scale) and its backward (TransformerBlock.cpp:42-46, 80-84)
+    def block_forward(self, x1: torch.Tensor, rms_scale: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+        assert x1.is_cuda and x1.is_contiguous() and x1.shape[-1] == self.C
+        assert rms_scale.dtype == torch.float32 and rms_scale.numel() == self.C
+        n = x1.numel() // self.C
+        io = self._io(x1)
+        need = int(self.lib.mgpt_moe_block_workspace_bytes(self._h, n, io))
+        if getattr(self, "_bws", None) is None or self._bws.numel() < need:
+            self._bws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        x2 = torch.empty_like(x1)
+        _lib.check(self.lib.mgpt_moe_block_forward(self._h, x1.data_ptr(), rms_scale.data_ptr(), float(eps), x2.data_ptr(),
+                                                   n, io, self._bws.data_ptr(), self._bws.numel(), self._stream()))
+        moe_ws = int(self.lib.mgpt_moe_workspace_bytes(self._h, n))
+        self._ws = self._bws[need - moe_ws: need]          # the layer's own workspace, for workspace_view()
+        self._x, self._n, self._x1 = None, n, x1
+        return x2
+
+    def block_backward(self, rms_scale: torch.Tensor, dout: torch.Tensor, d_rms_scale: torch.Tensor = None) -> torch.Tensor:
+        d_x1 = torch.empty_like(dout)
+        _lib.check(self.lib.mgpt_moe_block_backward(
+            self._h, self._x1.data_ptr(), rms_scale.data_ptr(), d_rms_scale.data_ptr() if d_rms_scale is not None else None,
+            dout.data_ptr(), d_x1.data_ptr(), self._io(dout), self._bws.data_ptr(), self._bws.numel(), self._stream()))
+        return d_x1
+
+    def block_input(self) -> torch.Tensor:
+        """The normalised rows the layer saw in the last block_forward (its own input), for checks."""
+        n, C = self._n, self.C
+        dt = self._x1.dtype
+        return self._bws[: n * C * self._x1.element_size()].view(dt).view(n, C)
+
     # -- activation checkpointing: keep the routing of a forward, recompute without router and plan
     def save_routing(self) -> torch.Tensor:
         """Routing results and plan of the last forward, in memory of their own (the reference rewinds its

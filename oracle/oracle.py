@@ -212,3 +212,31 @@ def adamw(w, g, m, v, *, lr, beta1, beta2, eps, weight_decay, t, which: str = "o
     if rc != 0:
         raise RuntimeError(f"{which} adamw returned {rc}")
     return w, m, v
+
+
+def rmsnorm(x, scale, dout, eps=1e-5, *, which: str = "numpy"):
+    """RMSNorm forward and backward of the reference (utils/Tensor.cpp:785-800, 1674-1690) on [n, c] float32 arrays:
+    returns (out, rs, dx, dscale).  ``which``: "numpy" (a restatement, float32 arithmetic, sums in float64 rounded
+    once: within 1e-6 of the reference's sequential float32 sums) or "ref" (the reference's own Tensor code)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    scale = np.ascontiguousarray(scale, dtype=np.float32).ravel()
+    dout = np.ascontiguousarray(dout, dtype=np.float32)
+    n, c = x.shape
+    if which == "ref":
+        lib = ct.CDLL(REF_SO)
+        fn = lib.moe_ref_rmsnorm
+        fn.argtypes = [_FP, _FP, _FP, ct.c_int, ct.c_int, ct.c_float, _FP, _FP, _FP, _FP]
+        out, rs = np.zeros((n, c), np.float32), np.zeros(n, np.float32)
+        dx, ds = np.zeros((n, c), np.float32), np.zeros(c, np.float32)
+        if fn(_fp(x), _fp(scale), _fp(dout), n, c, eps, _fp(out), _fp(rs), _fp(dx), _fp(ds)) != 0:
+            raise RuntimeError("moe_ref_rmsnorm failed")
+        return out, rs, dx, ds
+    ms = (x.astype(np.float64) ** 2).sum(1) / c
+    rs = (1.0 / np.sqrt(ms + eps)).astype(np.float32)
+    xh = x * rs[:, None]
+    out = xh * scale[None, :]
+    dxh = dout * scale[None, :]
+    dot = (dxh.astype(np.float64) * xh).sum(1).astype(np.float32)
+    dx = rs[:, None] * (dxh - xh * (dot / np.float32(c))[:, None])
+    ds = (dout.astype(np.float64) * xh).sum(0).astype(np.float32)
+    return out.astype(np.float32), rs, dx.astype(np.float32), ds

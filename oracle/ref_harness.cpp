@@ -151,3 +151,28 @@ extern "C" int moe_ref_adamw(float* w, const float* g, float* m, float* v, long 
         return 1;
     }
 }
+
+/* The reference's own RMSNorm (Tensor::rms_norm_into / rms_norm_backward_into, CPU arm), for pinning the numpy
+ * restatement the block-glue tests use.  x, dout [n, c]; scale [c]; out, dx [n, c]; rs [n]; dscale [c] (accumulated from 0). */
+extern "C" int moe_ref_rmsnorm(const float* x, const float* scale, const float* dout, int n, int c, float eps, float* out,
+                               float* rs, float* dx, float* dscale)
+{
+    try {
+        Tensor xt({n, c}, 0.0f, Device::CPU), st({c}, 0.0f, Device::CPU), dt({n, c}, 0.0f, Device::CPU);
+        std::memcpy(xt.data.data(), x, (size_t)n * c * sizeof(float));
+        std::memcpy(st.data.data(), scale, (size_t)c * sizeof(float));
+        std::memcpy(dt.data.data(), dout, (size_t)n * c * sizeof(float));
+        st.grad.assign((size_t)c, 0.0f);
+        Tensor r, xh, o, dxt;
+        xt.rms_norm_into(c, st, eps, r, xh, o);
+        xt.rms_norm_backward_into(dt, xh, st, r, dxt);
+        std::memcpy(out, o.data.data(), (size_t)n * c * sizeof(float));
+        std::memcpy(rs, r.data.data(), (size_t)n * sizeof(float));
+        std::memcpy(dx, dxt.data.data(), (size_t)n * c * sizeof(float));
+        std::memcpy(dscale, st.grad.data(), (size_t)c * sizeof(float));
+        return 0;
+    } catch (const std::exception& e) {
+        std::cerr << "moe_ref_rmsnorm: " << e.what() << std::endl;
+        return 1;
+    }
+}

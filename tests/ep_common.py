@@ -20,11 +20,13 @@ def shard_inputs(w, rank, seed=77):
     return x, params, dy
 
 
-def run_rank(w, rank, world, make_stages, device, tol, io=torch.float32):
+def run_rank(w, rank, world, make_stages, device, tol, io=torch.float32, make_layer=None):
     x, params, dy = shard_inputs(w, rank)
     E_local = w.E // world
-    stages = make_stages(w, E_local)
-    layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, stages=stages)
+    if make_layer is not None:
+        layer = make_layer(w)                      # e.g. the C-ABI form of the layer
+    else:
+        layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, stages=make_stages(w, E_local))
     layer.load_parameters(params)
     layer.zero_grad()
     xt = torch.from_numpy(x).to(device).to(io)

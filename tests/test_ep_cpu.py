@@ -64,3 +64,77 @@ def test_single_rank_needs_no_process_group(chunks):
 def test_experts_must_divide_evenly():
     from mgpt_b200.ep import ExpertParallelMoE
     ExpertParallelMoE(16, 24, 4, 2, stages=CpuStages(16, 24, 4, 2, 4))     # world 1: fine
+
+
+# ---- failures, made on the host: no GPU is involved, nothing is killed mid-collective ----------------------
+def _spawn(target, world, args, timeout=120):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q) + tuple(args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=timeout) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    return results
+
+
+def _uneven_worker(rank, world, port, q):
+    try:
+        torch.set_num_threads(1)
+        init_pg(rank, world, "gloo", port)
+        from mgpt_b200.ep import ExpertParallelMoE
+        try:
+            ExpertParallelMoE(16, 24, 5, 2, stages=CpuStages(16, 24, 5, 2, 2))      # 5 experts over 2 ranks
+            q.put((rank, "no error"))
+        except ValueError as e:
+            q.put((rank, f"ValueError: {e}"))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, traceback.format_exc()))
+
+
+def test_experts_that_do_not_divide_over_the_ranks_are_refused():
+    for rank, msg in _spawn(_uneven_worker, 2, ()).items():
+        assert msg.startswith("ValueError") and "not divisible" in msg, f"rank {rank}: {msg}"
+
+
+def _absent_worker(rank, world, port, q):
+    """Rank 1 never joins the step (it raises before its forward, as a rank does whose data loader failed).  Rank 0
+    must come back with an error from the count exchange -- the first collective of the step, before any row has
+    moved and before any expert kernel was enqueued -- once the group's timeout has passed, not hang."""
+    import datetime
+    import time
+    try:
+        torch.set_num_threads(1)
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=4))
+        from mgpt_b200.ep import ExpertParallelMoE
+        w = synth.Workload("ep", 24, 16, 16, 4, 2, "fp32")
+        stages = CpuStages(w.C, w.H, w.E, w.k, w.E // world, w.alpha)
+        layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, stages=stages)
+        calls = {"experts": 0}
+        real = stages.experts_forward
+        stages.experts_forward = lambda *a, **k: (calls.__setitem__("experts", calls["experts"] + 1), real(*a, **k))[1]
+        if rank == 1:
+            time.sleep(8)                  # stays alive past the others' timeout, takes no part in the step
+            q.put((rank, "absent"))
+            return
+        t0 = time.time()
+        try:
+            layer.forward(torch.zeros(w.n_tokens, w.C))
+            q.put((rank, "no error"))
+        except Exception as e:
+            q.put((rank, f"error after {time.time() - t0:.1f}s, expert calls {calls['experts']}: {type(e).__name__}"))
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, traceback.format_exc()))
+
+
+def test_a_rank_that_never_posts_its_counts_times_the_others_out():
+    res = _spawn(_absent_worker, 2, (), timeout=60)
+    assert res[1] == "absent"
+    assert res[0].startswith("error after") and "expert calls 0" in res[0], res[0]

@@ -41,6 +41,24 @@ def test_stage_entry_points_one_gpu(mode, tol, chunks):
     assert torch.isfinite(y2.float()).all()
 
 
+def _native(mode, rank, world, chunks=1, nccl_id=None):
+    from mgpt_b200.ep import NativeExpertParallelMoE
+    return lambda w: NativeExpertParallelMoE(w.C, w.H, w.E, w.k, rank=rank, world=world, nccl_id=nccl_id, mode=mode,
+                                             device=rank, lb_alpha=w.alpha, n_chunks=chunks)
+
+
+@pytest.mark.parametrize("chunks", [1, 2])
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-5), ("bf16", 2e-2)])
+def test_c_abi_expert_parallel_layer_one_gpu(mode, tol, chunks):
+    """mgpt_moe_ep_* with one rank (no NCCL needed): route, self-exchange, experts in chunks, combine and the
+    mirror-image backward, all inside the library."""
+    w = synth.Workload("epc", 700, 128, 192, 8, 2, mode)
+    io = torch.bfloat16 if mode == "bf16" else torch.float32
+    layer = run_rank(w, 0, 1, None, "cuda:0", tol, io=io, make_layer=_native(mode, 0, 1, chunks))
+    layer.check_status()
+    layer.close()
+
+
 def _worker(rank, world, port, q):
     try:
         os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -54,6 +72,14 @@ def _worker(rank, world, port, q):
         run_rank(w, rank, world, _stages("bf16", rank, chunks=2, sm_budget=120), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
         w = synth.Workload("epchunks", 2000, 256, 192, 16, 2, "bf16")
         run_rank(w, rank, world, _stages("bf16", rank, chunks=4), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        # the same through the C ABI alone (the library's own NCCL communicator and exchange stream)
+        from mgpt_b200.ep import NativeExpertParallelMoE
+        for chunks in (1, 2):
+            nid = NativeExpertParallelMoE.create_id()
+            layer = run_rank(w, rank, world, None, f"cuda:{rank}", 2e-2, io=torch.bfloat16,
+                             make_layer=_native("bf16", rank, world, chunks, nid))
+            layer.check_status()
+            layer.close()
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok"))

@@ -145,3 +145,16 @@ def test_seeded_tokens_have_the_prefix_property():
         assert np.array_equal(params[i], synth.make_param(w, i))
     w3 = synth.WORKLOADS["c3"].scaled(16)
     assert np.array_equal(synth.make_inputs(w3)[1][1], synth.make_param(w3, 1))
+
+
+def test_rmsnorm_restatement_matches_reference_live():
+    """The numpy RMSNorm the block-glue tests use, against the reference's own Tensor code."""
+    if not oracle.have_ref():
+        pytest.skip("reference build not present")
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((37, 96)) * 1.5 + 0.2).astype(np.float32)
+    g = (1.0 + 0.1 * rng.standard_normal(96)).astype(np.float32)
+    d = rng.standard_normal((37, 96)).astype(np.float32)
+    a, b = oracle.rmsnorm(x, g, d), oracle.rmsnorm(x, g, d, which="ref")
+    for u, v in zip(a, b):
+        assert np.allclose(u, v, rtol=2e-6, atol=1e-6)

@@ -16,6 +16,13 @@ from tests.util import assert_routing_exact, assert_values, dims_of, run_layer
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _always_take_the_tensor_core_router(monkeypatch):
+    """The library keeps small problems on the exact kernel alone (it is faster there); these tests are about the
+    two-pass router, whatever the size."""
+    monkeypatch.setenv("MGPT_MOE_ROUTER_TC_MIN_WORK", "0")
+
+
 def _route(w, x, params):
     ref = oracle.run(dims_of(w), x, params, route_only=True, threads=16)
     got = run_layer(w, x, params, None, mode="bf16", io=torch.bfloat16)

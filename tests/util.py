@@ -27,7 +27,10 @@ def run_layer(w, x, params, dy, *, mode, gemm_impl=0, io=torch.float32):
     N, E, k = w.n_tokens, w.E, w.k
     out = {"layer": layer, "y": y.float().cpu().numpy()}
     # BF16 tokens on the tensor-core path take the screened router: indices exact, logits / probabilities close
-    out["screened"] = mode == "bf16" and gemm_impl == 0 and io == torch.bfloat16
+    import os
+    min_work = float(os.environ.get("MGPT_MOE_ROUTER_TC_MIN_WORK", "4e8"))      # the library's own rule
+    out["screened"] = (mode == "bf16" and gemm_impl == 0 and io == torch.bfloat16
+                       and float(w.n_tokens) * w.C * w.E >= min_work)
     out["router_recompute"] = int(layer.workspace_view("router_recompute", torch.int32).cpu().numpy()[0]) if out["screened"] else 0
     i32, f32 = torch.int32, torch.float32
     out["logits"] = layer.workspace_view("logits", f32, (N, E)).cpu().numpy()
