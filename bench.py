@@ -332,9 +332,11 @@ def single_gpu_pass(args, w, rank, dev, *, light=False):
     y, dx = torch.empty_like(x), torch.empty_like(x)
 
     def step():
-        layer.forward_into(x, y)
         if w.backward:
+            layer.forward_into(x, y)
             layer.backward_into(dy, dx)
+        else:
+            layer.forward_inference_into(x, y)         # the generator's call: forward only, nothing kept
 
     def step_host():
         layer.step_host(x_host, dy_host if w.backward else None, y_host, dx_host if w.backward else None)
