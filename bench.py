@@ -28,12 +28,12 @@ METRIC = "moe_layer_fwd_bwd_tokens_per_sec"
 # c4 is too large to capture with many passes: its figures are those of c4q (a quarter of the tokens and of the
 # experts, same rows per expert) times four -- every term of the traffic is proportional to the number of experts.
 TRAFFIC = {
-    ("c2", "wgrad_gemm"): 415.8e6, ("c2", "gateup_gemm"): 154.8e6, ("c2", "dhh_gemm"): 204.2e6,
-    ("c2", "down_gemm"): 73.9e6, ("c2", "dxg_gemm"): 149.5e6,
-    ("c4q", "wgrad_gemm"): 1420.1e6, ("c4q", "gateup_gemm"): 374.8e6, ("c4q", "dhh_gemm"): 350.2e6,
-    ("c4q", "down_gemm"): 189.1e6, ("c4q", "dxg_gemm"): 342.2e6,
-    ("c4", "wgrad_gemm"): 4 * 1420.1e6, ("c4", "gateup_gemm"): 4 * 374.8e6, ("c4", "dhh_gemm"): 4 * 350.2e6,
-    ("c4", "down_gemm"): 4 * 189.1e6, ("c4", "dxg_gemm"): 4 * 342.2e6,
+    ("c3", "wgrad_gemm"): 827.5e6, ("c3", "gateup_gemm"): 337.8e6, ("c3", "dhh_gemm"): 397.0e6,
+    ("c3", "down_gemm"): 177.2e6, ("c3", "dxg_gemm"): 282.2e6,
+    ("c4q", "wgrad_gemm"): 1413.9e6, ("c4q", "gateup_gemm"): 373.7e6, ("c4q", "dhh_gemm"): 344.1e6,
+    ("c4q", "down_gemm"): 188.5e6, ("c4q", "dxg_gemm"): 339.5e6,
+    ("c4", "wgrad_gemm"): 4 * 1413.9e6, ("c4", "gateup_gemm"): 4 * 373.7e6, ("c4", "dhh_gemm"): 4 * 344.1e6,
+    ("c4", "down_gemm"): 4 * 188.5e6, ("c4", "dxg_gemm"): 4 * 339.5e6,
 }
 UNIT = "tokens/s"
 

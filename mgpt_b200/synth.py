@@ -36,6 +36,9 @@ WORKLOADS = {
     "c4": Workload("c4", 32768, 2048, 1408, 64, 2, "bf16"),
     # a quarter of c4 (same rows per expert, so the same tiles per expert): small enough for multi-pass profiling
     "c4q": Workload("c4q", 8192, 2048, 1408, 16, 2, "bf16"),
+    # c4's tokens, router and permutation with token experts of 64 hidden units: the router, dispatch and combine
+    # kernels at their full-size shapes in ~1.5 GB, for multi-pass profiling
+    "c4r": Workload("c4r", 32768, 2048, 64, 64, 2, "bf16"),
     "c5-8": Workload("c5-8", 8, 1024, 2816, 32, 2, "bf16", backward=False),
     "c5-64": Workload("c5-64", 64, 1024, 2816, 32, 2, "bf16", backward=False),
     "c5-256": Workload("c5-256", 256, 1024, 2816, 32, 2, "bf16", backward=False),
