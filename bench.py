@@ -534,7 +534,14 @@ def run_ours(args, w):
         from mgpt_b200.ep import ExpertParallelMoE
 
         bind_to_gpu_numa_node(local)        # before any pinned allocation: host buffers land next to this rank's GPU
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL's stream at high priority: an exchange that becomes ready together with a persistent compute kernel is
+        # placed first (the compute CTAs that find their SM taken start late and take fewer work items)
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.is_high_priority_stream = True
+            dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+        except Exception:
+            dist.init_process_group("nccl", device_id=dev)
         if w.E % world:
             raise SystemExit(f"workload {w.name}: {w.E} experts do not divide over {world} GPUs")
         if rank == 0 and not args.no_single:
@@ -548,12 +555,24 @@ def run_ours(args, w):
         dist.barrier()
         E_local = w.E // world
         chunks = args.ep_chunks if E_local % max(1, args.ep_chunks) == 0 else 1
-        layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha,
-                                  n_chunks=chunks, sm_budget=args.ep_sm_budget)
+        native = args.ep_impl == "native"
+        if native:
+            # the whole exchange behind the C ABI (mgpt_moe_ep_*: the library's own NCCL communicator and stream)
+            from mgpt_b200.ep import NativeExpertParallelMoE
+            layer = NativeExpertParallelMoE(w.C, w.H, w.E, w.k, rank=rank, world=world,
+                                            nccl_id=NativeExpertParallelMoE.create_id(), mode=w.dtype, device=local,
+                                            lb_alpha=w.alpha, n_chunks=chunks)
+        else:
+            layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha,
+                                      n_chunks=chunks, sm_budget=args.ep_sm_budget)
         # router: the same tensors on every rank; experts: those this rank owns, by their global index
         load_synth_params(layer.get_parameters(), w, dev,
                           lambda i: i if i < 2 else 2 + 6 * layer.global_expert((i - 2) // 6) + (i - 2) % 6)
-        layer.stages.sync_weights()
+        if native:
+            # parameters are bound in place; only the BF16 copies need building
+            layer._lib_mod.check(layer.lib.mgpt_moe_ep_sync_weights(layer._h, layer._stream()))
+        else:
+            layer.stages.sync_weights()
         x_host, dy_host, y_host, dx_host = host_tokens(w, rank)
         x, dy = x_host.to(dev), dy_host.to(dev)
         last = {}
@@ -595,26 +614,35 @@ def run_ours(args, w):
             torch.cuda.synchronize()
 
         layer.zero_grad()
-        res = measure(args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms,
-                      layer.stages.set_profiling, barrier, N, x_host.numel() * x_host.element_size())
-        # one more step with CUDA events around every phase (exchange vs compute), outside the timed region
-        layer.phase_events = {}
-        step()
-        torch.cuda.synchronize()
-        ep_phases = {k: round(v, 3) for k, v in layer.phase_ms().items()}
-        layer.phase_events = None
-        layer.stages.check_status()
+        if native:
+            res = measure(args, w, world, rank, dev, step, step_host, host_checksum, lambda: {}, lambda on: None, barrier, N,
+                          x_host.numel() * x_host.element_size())
+            layer.check_status()
+        else:
+            res = measure(args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms,
+                          layer.stages.set_profiling, barrier, N, x_host.numel() * x_host.element_size())
+            # one more step with CUDA events around every phase (exchange vs compute), outside the timed region
+            layer.phase_events = {}
+            step()
+            torch.cuda.synchronize()
+            ep_phases = {k: round(v, 3) for k, v in layer.phase_ms().items()}
+            layer.phase_events = None
+            layer.stages.check_status()
         if rank == 0 and single is not None:
             # rank 0's tokens through the expert-parallel layer against the same tokens through the one-GPU layer
             # (same weights; the load-balance term uses this rank's own counts in both)
-            counts_ep = layer.stages.routing_view("counts", torch.int32).cpu().tolist()
+            if native:      # rows received per local expert, summed over the sources = this rank's experts' global counts
+                counts_ep = None
+            else:
+                counts_ep = layer.stages.routing_view("counts", torch.int32).cpu().tolist()
             ep_check = {"y_rel_l2": rel_l2(last["y"], single["y"]),
                         "dx_rel_l2": rel_l2(last["dx"], single["dx"]) if w.backward else None,
-                        "counts_equal": counts_ep == [int(c) for c in single["counts"]],
+                        "counts_equal": None if counts_ep is None else counts_ep == [int(c) for c in single["counts"]],
                         "note": "rank 0: expert-parallel result vs the one-GPU layer on the same seeded tokens and weights"}
         dist.barrier()
         parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
-                       f"NCCL all-to-all for dispatch and combine, experts in {chunks} chunk(s) "
+                       + ("NCCL point-to-point groups inside the library (mgpt_moe_ep_*)" if native else "NCCL all-to-all (torch.distributed)")
+                       + f" for dispatch and combine, experts in {chunks} chunk(s) "
                        "(a chunk's exchange overlaps the previous chunk's expert work)")
 
     ms_per_step = res["ms_per_step"]
@@ -688,6 +716,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c1 c2 c3 c4 c5-8 c5-64 c5-256 (default c4)")
     ap.add_argument("--ep-chunks", type=int, default=2, help="N>1: expert chunks whose exchange overlaps compute")
+    ap.add_argument("--ep-impl", default="python", choices=["python", "native"],
+                    help="N>1: exchange driven from Python over torch.distributed, or entirely inside the C library")
     ap.add_argument("--ep-sm-budget", type=int, default=0,
                     help="N>1: CTAs of the persistent expert kernels (0 = every SM); leaves SMs to the exchange kernels")
     ap.add_argument("--cpu-sample", type=int, default=0, help="tokens per CPU-baseline step")

@@ -572,16 +572,21 @@ int mgpt_moe_backward(mgpt_moe_layer* L, const void* x, const void* dy, void* dx
     L->stage_begin(ST_COMBINE_BWD, st);
     MGPT_TRY(launch_combine_bwd(L->d, w, ws, dy, io, st));
     L->stage_end(ST_COMBINE_BWD, st);
-    if (use_tc(L)) MGPT_TRY(tc_experts_backward(L, w, ws, st));
+    // Tensor-core path: the gradients of the rows first, then dx, then the parameter gradients -- dx is what a
+    // caller further up the model (or the host, mgpt_moe_step_host) is waiting for, and nothing in the parameter
+    // gradients depends on it, so its consumer can start while the largest kernel of the step still runs.
+    if (use_tc(L)) MGPT_TRY(tc_experts_backward(L, w, ws, st, 1));
     else MGPT_TRY(simt_experts_backward(L, w, ws, st));
-    if (L->has_grad && !(use_tc(L) && tc_fused_bias_grads(L->d))) {      // the tensor-core weight-gradient kernel sums the bias gradients itself
+    L->stage_begin(ST_ROUTER_BWD, st);
+    MGPT_TRY(launch_router_bwd(L, w, ws, x, io, dx, st));
+    L->stage_end(ST_ROUTER_BWD, st);
+    if (L->dx_ready_event) MGPT_CUDA(cudaEventRecord(L->dx_ready_event, st));
+    if (use_tc(L)) MGPT_TRY(tc_experts_backward(L, w, ws, st, 2));
+    if (L->has_grad && !(use_tc(L) && tc_fused_bias_grads(L->d))) {      // else the tensor-core weight-gradient kernel sums the bias gradients itself
         L->stage_begin(ST_BIAS_GRAD, st);
         MGPT_TRY(launch_bias_grads(L, w, ws, st));
         L->stage_end(ST_BIAS_GRAD, st);
     }
-    L->stage_begin(ST_ROUTER_BWD, st);
-    MGPT_TRY(launch_router_bwd(L, w, ws, x, io, dx, st));
-    L->stage_end(ST_ROUTER_BWD, st);
     return 0;
 }
 
@@ -648,9 +653,15 @@ int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_hos
         MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, cs));
         MGPT_CUDA(cudaEventRecord(L->copy_ev[3], cs));
         MGPT_CUDA(cudaStreamWaitEvent(st, L->copy_ev[1], 0));       // backward needs dy
-        MGPT_TRY(mgpt_moe_backward(L, L->h_x, L->h_dy, L->h_dx, io, L->h_ws, L->h_ws_bytes, stream));
-        MGPT_CUDA(cudaMemcpyAsync(dx_host, L->h_dx, io_bytes, cudaMemcpyDeviceToHost, st));
-        MGPT_CUDA(cudaStreamWaitEvent(st, L->copy_ev[3], 0));       // the caller's stream also covers the y copy
+        L->dx_ready_event = L->copy_ev[4];                          // recorded inside backward, right after dx is written
+        const int brc = mgpt_moe_backward(L, L->h_x, L->h_dy, L->h_dx, io, L->h_ws, L->h_ws_bytes, stream);
+        L->dx_ready_event = nullptr;
+        MGPT_TRY(brc);
+        // dx goes down (after y, same direction) while the parameter gradients are still being formed
+        MGPT_CUDA(cudaStreamWaitEvent(cs, L->copy_ev[4], 0));
+        MGPT_CUDA(cudaMemcpyAsync(dx_host, L->h_dx, io_bytes, cudaMemcpyDeviceToHost, cs));
+        MGPT_CUDA(cudaEventRecord(L->copy_ev[3], cs));
+        MGPT_CUDA(cudaStreamWaitEvent(st, L->copy_ev[3], 0));       // the caller's stream also covers both copies
     } else {
         MGPT_CUDA(cudaMemcpyAsync(y_host, L->h_y, io_bytes, cudaMemcpyDeviceToHost, st));
     }

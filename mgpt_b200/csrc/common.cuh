@@ -147,7 +147,8 @@ struct mgpt_moe_layer {
     void *h_x = nullptr, *h_dy = nullptr, *h_y = nullptr, *h_dx = nullptr, *h_ws = nullptr;
     size_t h_io_bytes = 0, h_ws_bytes = 0;
     cudaStream_t copy_stream = nullptr;      // second stream of mgpt_moe_step_host (copies that overlap compute)
-    cudaEvent_t copy_ev[4] = {};
+    cudaEvent_t copy_ev[5] = {};
+    cudaEvent_t dx_ready_event = nullptr;    // when set, backward records it as soon as dx is complete
 
     // TMA descriptors (opaque, built per workspace pointer)
     void* tc_state = nullptr;

@@ -224,7 +224,12 @@ int mgpt_moe_ep_create(const mgpt_moe_ep_config* cfg, const void* id, mgpt_moe_e
         if (rc) return bail(rc);
         ep->locals.push_back(l);
     }
-    cudaError_t e = cudaStreamCreateWithFlags(&ep->cs, cudaStreamNonBlocking);
+    // The exchange stream gets the highest priority: when an exchange and a persistent compute kernel become ready at
+    // the same moment, the exchange's few CTAs are placed first and the compute CTAs that find their SM taken start
+    // late and simply take fewer work items; the other way round the exchange would wait for the whole kernel.
+    int prio_lo = 0, prio_hi = 0;
+    cudaError_t e = cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ep->cs, cudaStreamNonBlocking, prio_hi);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ep->ev_main, cudaEventDisableTiming);
     for (auto* v : {&ep->ev_in, &ep->ev_out, &ep->ev_back})
         for (int c = 0; c < nc && e == cudaSuccess; ++c) {

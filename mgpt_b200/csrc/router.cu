@@ -61,6 +61,16 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
         stok[i] = idx < n_active ? (list ? list[idx] : idx) : -1;
     }
     __syncthreads();
+    if (list) {
+        // Listed tokens are scattered rows the first pass read a while ago: ask for all of each row now, so that the
+        // per-chunk loads below find it in L2 instead of paying a DRAM round trip per 32 channels.
+        const int lines = (C * (int)sizeof(TIn) + 127) / 128;
+        for (int i = tid; i < TOK * lines; i += THREADS) {
+            const int tok = stok[i / lines];
+            if (tok >= 0)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)(x + (size_t)tok * C) + (size_t)(i % lines) * 128));
+        }
+    }
 
     float acc[TPW][EPL];
 #pragma unroll

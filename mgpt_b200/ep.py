@@ -338,8 +338,9 @@ class ExpertParallelMoE:
             recv_counts.copy_(send_counts)
         else:
             dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        both = torch.stack([self._pad128(send_counts).sum(2).t(), self._pad128(recv_counts).sum(2).t()]).cpu()   # the one host sync
-        send_splits, recv_splits = both[0].tolist(), both[1].tolist()          # [chunk][rank] padded rows
+        both = torch.stack([send_counts, recv_counts]).cpu().numpy()           # the one host sync; the rest is host arithmetic
+        padded = (both + 127) // 128 * 128                                     # [2][rank][chunk][j]
+        send_splits, recv_splits = padded[0].sum(2).T.tolist(), padded[1].sum(2).T.tolist()      # [chunk][rank] padded rows
         starts, n_send = [], 0
         for c in range(nc):
             starts.append(n_send)
