@@ -357,13 +357,35 @@ def single_gpu_pass(args, w, rank, dev, *, light=False):
     res["experts_touched"] = sum(1 for c in counts if c > 0)
     if w.dtype == "bf16":
         # tokens whose routing the tensor-core pass of the router could not prove and the exact pass recomputed
-        res["router_recomputed"] = int(layer.workspace_view("router_recompute", torch.int32).cpu()[0])
+        rc = layer.workspace_view("router_recompute", torch.int32)       # absent from the inference workspace
+        res["router_recomputed"] = int(rc.cpu()[0]) if rc.numel() else None
     res["counts"] = counts
     res["y"], res["dx"] = y, (dx if w.backward else None)          # of the last timed step (device tensors)
+    res["overwrite"] = time_overwrite(layer, w, step) if w.backward and not light and w.dtype == "bf16" else None
     res["recompute"] = time_recompute(layer, x, torch.empty_like(y)) if w.backward and not args.no_optimizer and not light else None
     res["optimizer"] = time_optimizer(layer, w) if w.backward and not args.no_optimizer and not light else None
     layer.close()
     return res
+
+
+def time_overwrite(layer, w, step):
+    """Outside the timed steps: the weight-gradient stage when the caller has said its gradient tensors are freshly
+    zeroed (first backward after the trainer's zero fill), so that the library stores instead of read-modify-writes."""
+    import torch
+    layer.set_weight_grad_overwrite(True)
+    layer.set_profiling(True)
+    ms = []
+    for _ in range(4):
+        step()
+        torch.cuda.synchronize()
+        ms.append(layer.stage_ms().get("wgrad_gemm", 0.0))
+    layer.set_profiling(False)
+    layer.set_weight_grad_overwrite(False)
+    best = min(ms[1:])
+    flop = 6.0 * w.n_tokens * w.k * w.C * w.H
+    return {"wgrad_ms": round(best, 4), "wgrad_tflops": round(flop / (best * 1e-3) / 1e12, 1),
+            "note": "not part of the timed step: weight gradients stored instead of accumulated "
+                    "(mgpt_moe_set_weight_grad_overwrite; equals accumulation into zeroed tensors bit for bit)"}
 
 
 def time_recompute(layer, x, y):
@@ -677,6 +699,8 @@ def run_ours(args, w):
     line["cpu_baseline"] = cpu
     if world == 1 and single.get("optimizer"):
         line["optimizer"] = single["optimizer"]
+    if world == 1 and single.get("overwrite"):
+        line["weight_gradients_stored"] = single["overwrite"]
     if world == 1 and single.get("recompute"):
         line["checkpointing"] = single["recompute"]
     if reference_1gpu:

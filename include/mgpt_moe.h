@@ -305,6 +305,12 @@ size_t mgpt_moe_stage_workspace_bytes(const mgpt_moe_layer* layer, int n, int ro
  * reference's slot order (Tensor.cpp:1368-1381). */
 int  mgpt_moe_route(mgpt_moe_layer* layer, const void* x, int n_tokens, int io_dtype,
                     void* workspace, size_t workspace_bytes, void* send_rows, mgpt_stream_t stream);
+/* mgpt_moe_route in two calls: _plan (router + plan; the counts are then final and their exchange can start) and
+ * _rows (the permutation into send_rows, which can run while the counts travel). */
+int  mgpt_moe_route_plan(mgpt_moe_layer* layer, const void* x, int n_tokens, int io_dtype,
+                         void* workspace, size_t workspace_bytes, mgpt_stream_t stream);
+int  mgpt_moe_route_rows(mgpt_moe_layer* layer, const void* x, int io_dtype, void* workspace, size_t workspace_bytes,
+                         void* send_rows, mgpt_stream_t stream);
 /* y[tok,:] = sum_j p[tok,j] * rows_back[row(tok,j),:]   (Tensor.cpp:1398-1406); rows_back in the send layout */
 int  mgpt_moe_combine(mgpt_moe_layer* layer, const void* rows_back, void* y, int io_dtype,
                       void* workspace, size_t workspace_bytes, mgpt_stream_t stream);

@@ -25,6 +25,7 @@ SYMBOLS = [
     "mgpt_moe_ep_unique_id", "mgpt_moe_ep_create", "mgpt_moe_ep_destroy", "mgpt_moe_ep_num_params",
     "mgpt_moe_ep_global_expert", "mgpt_moe_ep_bind_params", "mgpt_moe_ep_sync_weights", "mgpt_moe_ep_forward",
     "mgpt_moe_ep_backward", "mgpt_moe_ep_received_counts", "mgpt_moe_ep_check_status",
+    "mgpt_moe_route_plan", "mgpt_moe_route_rows",
     "mgpt_moe_block_workspace_bytes", "mgpt_moe_block_forward", "mgpt_moe_block_backward",
     "mgpt_moe_set_weight_grad_overwrite", "mgpt_moe_inference_workspace_bytes", "mgpt_moe_forward_inference", "mgpt_moe_experts_backward_rows", "mgpt_moe_experts_backward_params",
 ]
@@ -107,6 +108,8 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_stage_workspace_bytes.argtypes = [vp, i32, i32]
     lib.mgpt_moe_stage_workspace_bytes.restype = sz
     lib.mgpt_moe_route.argtypes = [vp, vp, i32, i32, vp, sz, vp, vp]
+    lib.mgpt_moe_route_plan.argtypes = [vp, vp, i32, i32, vp, sz, vp]
+    lib.mgpt_moe_route_rows.argtypes = [vp, vp, i32, vp, sz, vp, vp]
     lib.mgpt_moe_combine.argtypes = [vp, vp, vp, i32, vp, sz, vp]
     lib.mgpt_moe_combine_backward.argtypes = [vp, vp, vp, i32, vp, vp, sz, vp]
     lib.mgpt_moe_route_backward.argtypes = [vp, vp, vp, vp, i32, vp, sz, vp]

@@ -333,7 +333,7 @@ int mgpt_moe_ep_forward(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, i
     const size_t row_cap = nb / sizeof(int32_t);
     MGPT_TRY(ep->rows.ensure(row_cap * rb));
     MGPT_TRY(ep->rows_back.ensure(row_cap * rb));
-    MGPT_TRY(mgpt_moe_route(ep->home, x, n_tokens, io, ep->home_ws.p, ep->home_ws.bytes, ep->rows.p, stream));
+    MGPT_TRY(mgpt_moe_route_plan(ep->home, x, n_tokens, io, ep->home_ws.p, ep->home_ws.bytes, stream));
     MGPT_TRY(mgpt_moe_workspace_view(ep->home, n_tokens, "counts", &off, &nb));
     const int32_t* d_counts = (const int32_t*)((char*)ep->home_ws.p + off);
 
@@ -341,6 +341,8 @@ int mgpt_moe_ep_forward(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, i
     MGPT_TRY(ep->recv_counts.ensure((size_t)G * nc * Ec * sizeof(int32_t)));
     int32_t* d_recv = (int32_t*)ep->recv_counts.p;          // [source][chunk][j]
     MGPT_TRY(follow(ep, st));
+    // the rows are permuted while the counts travel and the host reads them
+    MGPT_TRY(mgpt_moe_route_rows(ep->home, x, io, ep->home_ws.p, ep->home_ws.bytes, ep->rows.p, stream));
     if (G > 1) MGPT_NCCL(g_nccl.GroupStart());
     for (int c = 0; c < nc; ++c)
         for (int g = 0; g < G; ++g) {
@@ -384,6 +386,7 @@ int mgpt_moe_ep_forward(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, i
                                     Ec * sizeof(int32_t), G, cudaMemcpyDeviceToDevice, ep->cs));
     }
     // every chunk's rows set off at once (they travel in this order); chunk c is computed while c+1 is arriving
+    MGPT_TRY(follow(ep, st));                       // the permuted rows are complete
     for (int c = 0; c < nc; ++c) {
         MGPT_TRY(exchange_rows(ep, (char*)ep->recv_rows[c].p, ep->recv_split[c], (const char*)ep->rows.p + (size_t)ep->starts[c] * rb,
                                ep->send_split[c]));

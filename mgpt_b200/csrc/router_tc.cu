@@ -9,9 +9,11 @@
 //   pass 1 (this file): logits ~= x * Wr on the tensor cores.  x is BF16; Wr^T is kept as two BF16 pieces
 //     (Wr = hi + mid up to 2^-16 relative), so every product is exact and only the accumulation order differs
 //     from the reference.  For token t and every expert
-//         |logit_ref - logit_tc| <= B_t = (2.5*C*u + 2^-16) * ||x_t||_2 * max_e ||Wr[:,e]||_2 + (bias roundings)
-//     (u = 2^-24; C*u*sum|x w| bounds the reference's sequential FP32 sum, the same again with margin the
-//     tensor core's, and sum|x w| <= ||x|| ||w|| by Cauchy-Schwarz).  ||x_t||_2 comes from the same shared-memory
+//         |logit_ref - logit_tc| <= B_t = (1.5*C*u + 2^-16) * ||x_t||_2 * max_e ||Wr[:,e]||_2 + (bias roundings)
+//     (u = 2^-24.  C*u*sum|x w| bounds the reference's sequential FP32 sum of C exact products.  The tensor core
+//     adds 16 exact products to the FP32 accumulator per instruction and rounds once, at worst by truncation:
+//     2*(C/16)*2u*sum|x w| = C*u/4*sum|x w| over the two pieces; it is given twice that.  sum|x w| <= ||x|| ||w||
+//     by Cauchy-Schwarz).  ||x_t||_2 comes from the same shared-memory
 //     tile the tensor core reads.  If the token's top-(k+1) logits are pairwise more than 2*B_t apart and its
 //     k-th probability is clear of the clamp floor, the reference's order of those experts is the same, whatever
 //     its rounding did: indices are final.  Probabilities are written from the pass-1 logits (they differ from
@@ -199,7 +201,7 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             const float u = 5.9604645e-8f;
             const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
             const float xn = sqrtf(ss) * 1.001f;
-            const float bound = (2.5f * (float)p.C * u + 1.52587890625e-5f) * xn * wmax * 1.01f + 4.0f * u * (xn * wmax + bmax);
+            const float bound = (1.5f * (float)p.C * u + 1.52587890625e-5f) * xn * wmax * 1.01f + 4.0f * u * (xn * wmax + bmax);
             const float tau = 2.0f * bound;
 
             float mx = -INFINITY;

@@ -58,17 +58,19 @@ size_t mgpt_moe_stage_workspace_bytes(const mgpt_moe_layer* L, int n, int routin
     return make_workspace(L->d, n, routing_side ? 1 : 2).total;
 }
 
-int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void* workspace, size_t ws_bytes,
-                   void* send_rows, mgpt_stream_t stream)
+// router + plan: after this the per-expert counts are final (workspace view "counts")
+int mgpt_moe_route_plan(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void* workspace, size_t ws_bytes,
+                        mgpt_stream_t stream)
 {
     MGPT_TRY(check_route_layer(L, io));
-    if (n_tokens < 0 || (n_tokens > 0 && (!x || !send_rows))) return fail(MGPT_MOE_EINVAL, "bad token buffer");
+    if (n_tokens < 0 || (n_tokens > 0 && !x)) return fail(MGPT_MOE_EINVAL, "bad token buffer");
     const Workspace w = make_workspace(L->d, n_tokens, 1);
     MGPT_TRY(check_ws(L, workspace, ws_bytes, w));
     MGPT_CUDA(cudaSetDevice(L->device));
     cudaStream_t st = (cudaStream_t)stream;
     char* ws = (char*)workspace;
     const Dims& d = L->d;
+    L->fwd_done = false;
     if (n_tokens > 0) {
         if (tc_router_usable(L, x, io, n_tokens))
             MGPT_TRY(tc_router_fwd(L, w, ws, x, st));
@@ -77,15 +79,38 @@ int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void*
                                        (float*)(ws + w.probs), (int32_t*)(ws + w.top_idx), (float*)(ws + w.top_p), st));
     }
     MGPT_TRY(launch_plan(d, w, ws, st, L->d_status));
-    // expert-major rows, each expert padded to whole tiles with zero rows; stable within an expert
-    MGPT_TRY(gather_rows(x, io, (const int32_t*)(ws + w.row_src), (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, d.C,
-                         d.k, send_rows, w.act_bytes, st));
     L->last_n = n_tokens;
     L->last_io = io;
     L->last_ws = workspace;
     L->last_stream = st;
+    return 0;
+}
+
+// the permutation of the tokens into send_rows, for the plan mgpt_moe_route_plan left in the workspace
+int mgpt_moe_route_rows(mgpt_moe_layer* L, const void* x, int io, void* workspace, size_t ws_bytes, void* send_rows,
+                        mgpt_stream_t stream)
+{
+    MGPT_TRY(check_route_layer(L, io));
+    if (workspace != L->last_ws || io != L->last_io) return fail(MGPT_MOE_ESTATE, "route_rows follows route_plan on the same workspace");
+    const int n_tokens = L->last_n;
+    if (n_tokens > 0 && (!x || !send_rows)) return fail(MGPT_MOE_EINVAL, "bad token buffer");
+    const Workspace w = make_workspace(L->d, n_tokens, 1);
+    MGPT_TRY(check_ws(L, workspace, ws_bytes, w));
+    MGPT_CUDA(cudaSetDevice(L->device));
+    char* ws = (char*)workspace;
+    // expert-major rows, each expert padded to whole tiles with zero rows; stable within an expert
+    MGPT_TRY(gather_rows(x, io, (const int32_t*)(ws + w.row_src), (const int32_t*)(ws + w.n_tiles), -1, w.row_cap, L->d.C,
+                         L->d.k, send_rows, w.act_bytes, (cudaStream_t)stream));
     L->fwd_done = true;
     return 0;
+}
+
+int mgpt_moe_route(mgpt_moe_layer* L, const void* x, int n_tokens, int io, void* workspace, size_t ws_bytes,
+                   void* send_rows, mgpt_stream_t stream)
+{
+    if (n_tokens > 0 && !send_rows) return fail(MGPT_MOE_EINVAL, "bad token buffer");
+    MGPT_TRY(mgpt_moe_route_plan(L, x, n_tokens, io, workspace, ws_bytes, stream));
+    return mgpt_moe_route_rows(L, x, io, workspace, ws_bytes, send_rows, stream);
 }
 
 int mgpt_moe_combine(mgpt_moe_layer* L, const void* rows_back, void* y, int io, void* workspace, size_t ws_bytes,
