@@ -219,7 +219,7 @@ def host_tokens(w, rank):
 
 
 def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms, set_profiling, barrier, N, io_bytes,
-            graph_ok=False, steps=None, warmup=None, sample_clocks=True):
+            graph_ok=False, steps=None, warmup=None, sample_clocks=True, pipe=None):
     """Warm-up, K timed steps (CUDA events, L2 flushed between steps, max over ranks), then the host-buffer path."""
     import torch
     import torch.distributed as dist
@@ -311,7 +311,31 @@ def measure(args, w, world, rank, dev, step, step_host, host_checksum, stage_ms,
     n_dir = 2 if w.backward else 1
     checksum = host_checksum()             # of the last step's output, computed outside the timed region
     e2e = {"value": world * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": io_bytes * n_dir, "d2h_bytes_per_step": io_bytes * n_dir, "checksum": checksum}
+           "h2d_bytes_per_step": io_bytes * n_dir, "d2h_bytes_per_step": io_bytes * n_dir, "checksum": checksum,
+           "steps_in_flight": 1}
+    if pipe is not None:
+        # The same K steps through the pipelined call: every step still uploads its x and dy from pinned host memory
+        # and downloads its y and dx inside the timed region, but one step's copies overlap another's kernels (two
+        # steps in flight).  Inputs (134 MB at c4) exceed L2, so consecutive steps do not find them cached.
+        enqueue, wait = pipe
+        for i in range(3):
+            enqueue(i)
+        wait()
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            enqueue(i)
+        wait()
+        pms = (time.perf_counter() - t0) * 1e3
+        t = torch.tensor([pms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pms = float(t.item()) / steps
+        e2e.update({"value": world * N / (pms * 1e-3), "ms_per_step": pms, "steps_in_flight": 2,
+                    "call": ("mgpt_moe_step_host_async" if world == 1 else "the same pipeline around the expert-parallel layer")
+                            + " (the next step's uploads and the previous step's downloads overlap this step's "
+                              "kernels), timed over all K steps and the final wait",
+                    "one_step_alone_ms": e2e_ms, "checksum": host_checksum()})
     return {"ms_per_step": ms_per_step, "stage_sum": stage_sum, "steps": steps, "launches": int(launches),
             "clocks": clocks, "e2e": e2e, "launch_mode": launch_mode, "stream_ms": stream_ms}
 
@@ -347,12 +371,20 @@ def single_gpu_pass(args, w, rank, dev, *, light=False):
     def barrier():
         torch.cuda.synchronize()
 
+    # second set of pinned outputs: with two steps in flight, consecutive steps must not share their y / dx
+    y_host2, dx_host2 = (torch.empty_like(y_host).pin_memory(), torch.empty_like(dx_host).pin_memory()) if not light else (None, None)
+
+    def enqueue(i):
+        yo, dxo = (y_host, dx_host) if i % 2 == 0 else (y_host2, dx_host2)
+        layer.step_host_async(x_host, dy_host if w.backward else None, yo, dxo if w.backward else None)
+
     layer.zero_grad()
     step()
     counts = layer.get_expert_counts()                 # also reads the layer's error word
     res = measure(args, w, 1, 0, dev, step, step_host, host_checksum, layer.stage_ms, layer.set_profiling, barrier, N,
                   x_host.numel() * x_host.element_size(), graph_ok=not args.no_graph,
-                  steps=min(args.steps, 10) if light else None, warmup=3 if light else None, sample_clocks=not light)
+                  steps=min(args.steps, 10) if light else None, warmup=3 if light else None, sample_clocks=not light,
+                  pipe=None if light else (enqueue, layer.step_host_wait))
     layer.check_status()
     res["experts_touched"] = sum(1 for c in counts if c > 0)
     if w.dtype == "bf16":
@@ -627,6 +659,46 @@ def run_ours(args, w):
                 dx_host.copy_(layer.backward(dyd), non_blocking=True)
             torch.cuda.synchronize()
 
+        # The pipelined form of the same step (what mgpt_moe_step_host_async does for the one-GPU layer): two slots
+        # of device staging, uploads and downloads on streams of their own, compute in call order.
+        slots = [{"xd": xd, "dyd": dyd}, {"xd": torch.empty_like(x), "dyd": torch.empty_like(dy)}]
+        outs = [(y_host, dx_host), (torch.empty_like(y_host).pin_memory(), torch.empty_like(dx_host).pin_memory())]
+        up_stream, down_stream = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+        def enqueue(i):
+            sl, (yo, dxo) = slots[i % 2], outs[i % 2]
+            cur = torch.cuda.current_stream()
+            if sl.get("out_done") is not None:
+                sl["out_done"].synchronize()           # the step before last: its results are in host memory
+                up_stream.wait_event(sl["compute_done"])
+            in_x, in_dy = torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(up_stream):
+                sl["xd"].copy_(x_host, non_blocking=True)
+                in_x.record()
+                if w.backward:
+                    sl["dyd"].copy_(dy_host, non_blocking=True)
+                    in_dy.record()
+            cur.wait_event(in_x)
+            y = layer.forward(sl["xd"])
+            down_stream.wait_stream(cur)
+            with torch.cuda.stream(down_stream):
+                yo.copy_(y, non_blocking=True)
+            y.record_stream(down_stream)
+            if w.backward:
+                cur.wait_event(in_dy)
+                dxd = layer.backward(sl["dyd"])
+                down_stream.wait_stream(cur)
+                with torch.cuda.stream(down_stream):
+                    dxo.copy_(dxd, non_blocking=True)
+                dxd.record_stream(down_stream)
+            sl["compute_done"] = torch.cuda.Event()
+            sl["compute_done"].record(cur)
+            sl["out_done"] = torch.cuda.Event()
+            sl["out_done"].record(down_stream)
+
+        def wait_all():
+            torch.cuda.synchronize()
+
         def host_checksum():
             return float(y_host[:4096].float().abs().mean())
 
@@ -638,11 +710,12 @@ def run_ours(args, w):
         layer.zero_grad()
         if native:
             res = measure(args, w, world, rank, dev, step, step_host, host_checksum, lambda: {}, lambda on: None, barrier, N,
-                          x_host.numel() * x_host.element_size())
+                          x_host.numel() * x_host.element_size(), pipe=(enqueue, wait_all))
             layer.check_status()
         else:
             res = measure(args, w, world, rank, dev, step, step_host, host_checksum, layer.stages.stage_ms,
-                          layer.stages.set_profiling, barrier, N, x_host.numel() * x_host.element_size())
+                          layer.stages.set_profiling, barrier, N, x_host.numel() * x_host.element_size(),
+                          pipe=(enqueue, wait_all))
             # one more step with CUDA events around every phase (exchange vs compute), outside the timed region
             layer.phase_events = {}
             step()

@@ -127,6 +127,23 @@ int  mgpt_moe_workspace_view(const mgpt_moe_layer* layer, int n_tokens, const ch
 int  mgpt_moe_step_host(mgpt_moe_layer* layer, const void* x_host, const void* dy_host,
                         void* y_host, void* dx_host, int n_tokens, int io_dtype, mgpt_stream_t stream);
 
+/* The same step, pipelined: the call enqueues the uploads, the kernels and
+ * the downloads and returns without waiting, so that the next step's x and
+ * dy go up, and the previous step's y and dx come down, beside this step's
+ * kernels (one upload stream, one download stream, compute on `stream` in
+ * call order; two slots of device staging inside the layer). At most two
+ * steps are in flight: a third call first waits until the results of the
+ * step before last are in host memory. A step's y_host / dx_host are valid
+ * after the call after next has returned, or after mgpt_moe_step_host_wait,
+ * which waits for every step in flight and returns the layer's status
+ * (MGPT_MOE_ESTATE style errors of the kernels, as mgpt_moe_check_status).
+ * The host buffers must stay valid (and pinned, for the copies to overlap)
+ * until then. No reference counterpart: the reference's CPU layer works on
+ * host memory in place (layers/MoELayer.cpp:58-135). */
+int  mgpt_moe_step_host_async(mgpt_moe_layer* layer, const void* x_host, const void* dy_host,
+                              void* y_host, void* dx_host, int n_tokens, int io_dtype, mgpt_stream_t stream);
+int  mgpt_moe_step_host_wait(mgpt_moe_layer* layer);
+
 /* Per-stage device timing for benchmarks. When enabled, forward and backward
  * bracket each stage with CUDA events on the caller's stream;
  * mgpt_moe_stage_ms synchronises those events and writes the milliseconds of

@@ -15,7 +15,7 @@ SYMBOLS = [
     "mgpt_moe_create", "mgpt_moe_destroy", "mgpt_moe_last_error", "mgpt_moe_num_params",
     "mgpt_moe_param_shape", "mgpt_moe_bind_params", "mgpt_moe_sync_weights", "mgpt_moe_workspace_bytes",
     "mgpt_moe_forward", "mgpt_moe_backward", "mgpt_moe_expert_counts", "mgpt_moe_workspace_view",
-    "mgpt_moe_step_host", "mgpt_moe_launch_count", "mgpt_moe_op_router",
+    "mgpt_moe_step_host", "mgpt_moe_step_host_async", "mgpt_moe_step_host_wait", "mgpt_moe_launch_count", "mgpt_moe_op_router",
     "mgpt_moe_set_profiling", "mgpt_moe_stage_ms", "mgpt_moe_stage_name", "mgpt_moe_set_sm_budget", "mgpt_moe_bind_optimizer_state", "mgpt_moe_adamw_step",
     "mgpt_moe_forward_residual", "mgpt_moe_routing_bytes", "mgpt_moe_save_routing", "mgpt_moe_forward_with_routing",
     "mgpt_moe_op_plan", "mgpt_moe_op_plan_scratch_bytes", "mgpt_moe_op_plan_noalloc",
@@ -83,6 +83,8 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_expert_counts.argtypes = [vp, ct.POINTER(ct.c_int32)]
     lib.mgpt_moe_workspace_view.argtypes = [vp, i32, ct.c_char_p, ct.POINTER(sz), ct.POINTER(sz)]
     lib.mgpt_moe_step_host.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp]
+    lib.mgpt_moe_step_host_async.argtypes = [vp, vp, vp, vp, vp, i32, i32, vp]
+    lib.mgpt_moe_step_host_wait.argtypes = [vp]
     lib.mgpt_moe_launch_count.argtypes = [i32]
     lib.mgpt_moe_launch_count.restype = ct.c_long
     lib.mgpt_moe_set_profiling.argtypes = [vp, i32]

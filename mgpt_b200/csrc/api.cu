@@ -224,6 +224,7 @@ void mgpt_moe_destroy(mgpt_moe_layer* L)
         cudaStreamDestroy(L->copy_stream);
         for (auto& e : L->copy_ev) cudaEventDestroy(e);
     }
+    host_pipe_destroy(L);
     delete L;
 }
 
@@ -668,6 +669,167 @@ int mgpt_moe_step_host(mgpt_moe_layer* L, const void* x_host, const void* dy_hos
     MGPT_TRY(status_fetch(L, st));
     MGPT_CUDA(cudaStreamSynchronize(st));
     return status_result(L, st, nullptr);
+}
+
+// ---- pipelined steps with host buffers ------------------------------------------------------
+// One step alone is bound by the PCIe link three times over (x up, y down, dx down; dy goes up beside the forward).
+// Consecutive steps do not depend on each other's tokens, so the next step's uploads and the previous step's
+// downloads can ride beside this step's kernels: two slots of device staging, one upload stream, one download
+// stream, compute on the caller's stream in call order.
+}  // extern "C"
+
+namespace {
+
+struct HostSlot {
+    void *x = nullptr, *dy = nullptr, *y = nullptr, *dx = nullptr;
+    cudaEvent_t in_x = nullptr, in_dy = nullptr, y_ready = nullptr, dx_ready = nullptr, compute_done = nullptr,
+                out_done = nullptr;
+    bool used = false;                        // a step has been enqueued on this slot and not waited for
+};
+struct HostPipe {
+    HostSlot slot[2];
+    size_t io_bytes = 0;
+    cudaStream_t up = nullptr, down = nullptr;
+    uint64_t n_enqueued = 0;
+    cudaStream_t compute = nullptr;           // the stream of the steps in flight
+};
+
+void host_pipe_free_slots(HostPipe* hp)
+{
+    for (auto& s : hp->slot) {
+        cudaFree(s.x); cudaFree(s.dy); cudaFree(s.y); cudaFree(s.dx);
+        s.x = s.dy = s.y = s.dx = nullptr;
+    }
+    hp->io_bytes = 0;
+}
+
+int host_pipe_drain(mgpt_moe_layer* L, HostPipe* hp)
+{
+    for (auto& s : hp->slot)
+        if (s.used) {
+            MGPT_CUDA(cudaEventSynchronize(s.out_done));
+            MGPT_CUDA(cudaEventSynchronize(s.compute_done));
+            s.used = false;
+        }
+    (void)L;
+    return 0;
+}
+
+}  // namespace
+
+void mgpt::host_pipe_destroy(mgpt_moe_layer* L)
+{
+    HostPipe* hp = (HostPipe*)L->host_pipe;
+    if (!hp) return;
+    for (auto& s : hp->slot) {
+        if (s.used) {
+            cudaEventSynchronize(s.out_done);
+            cudaEventSynchronize(s.compute_done);
+        }
+        for (cudaEvent_t e : {s.in_x, s.in_dy, s.y_ready, s.dx_ready, s.compute_done, s.out_done})
+            if (e) cudaEventDestroy(e);
+    }
+    host_pipe_free_slots(hp);
+    if (hp->up) cudaStreamDestroy(hp->up);
+    if (hp->down) cudaStreamDestroy(hp->down);
+    delete hp;
+    L->host_pipe = nullptr;
+}
+
+extern "C" {
+
+int mgpt_moe_step_host_async(mgpt_moe_layer* L, const void* x_host, const void* dy_host, void* y_host, void* dx_host,
+                             int n_tokens, int io, mgpt_stream_t stream)
+{
+    if (!L || !x_host || !y_host) return fail(MGPT_MOE_EINVAL, "null argument");
+    if (dy_host && !dx_host) return fail(MGPT_MOE_EINVAL, "dx_host is required with dy_host");
+    if (n_tokens <= 0) return fail(MGPT_MOE_EINVAL, "n_tokens must be positive");
+    if (io != MGPT_MOE_IO_F32 && io != MGPT_MOE_IO_BF16) return fail(MGPT_MOE_EINVAL, "unknown io dtype");
+    MGPT_CUDA(cudaSetDevice(L->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    HostPipe* hp = (HostPipe*)L->host_pipe;
+    if (!hp) {
+        hp = new HostPipe();
+        L->host_pipe = hp;
+        int lo = 0, hi = 0;
+        MGPT_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        MGPT_CUDA(cudaStreamCreateWithPriority(&hp->up, cudaStreamNonBlocking, hi));
+        MGPT_CUDA(cudaStreamCreateWithPriority(&hp->down, cudaStreamNonBlocking, hi));
+        for (auto& s : hp->slot)
+            for (cudaEvent_t* e : {&s.in_x, &s.in_dy, &s.y_ready, &s.dx_ready, &s.compute_done, &s.out_done})
+                MGPT_CUDA(cudaEventCreateWithFlags(e, cudaEventDisableTiming));
+    }
+    const size_t io_bytes = (size_t)n_tokens * L->d.C * (io == MGPT_MOE_IO_BF16 ? 2 : 4);
+    const size_t ws_bytes = mgpt_moe_workspace_bytes(L, n_tokens);
+    if (hp->compute != st || io_bytes > hp->io_bytes || ws_bytes > L->h_ws_bytes) {
+        // a new stream or larger buffers: finish what is in flight first (never inside a steady-state loop)
+        MGPT_TRY(host_pipe_drain(L, hp));
+        hp->compute = st;
+    }
+    if (io_bytes > hp->io_bytes) {
+        host_pipe_free_slots(hp);
+        for (auto& s : hp->slot) {
+            MGPT_CUDA(cudaMalloc(&s.x, io_bytes));
+            MGPT_CUDA(cudaMalloc(&s.dy, io_bytes));
+            MGPT_CUDA(cudaMalloc(&s.y, io_bytes));
+            MGPT_CUDA(cudaMalloc(&s.dx, io_bytes));
+        }
+        hp->io_bytes = io_bytes;
+    }
+    if (ws_bytes > L->h_ws_bytes) {
+        MGPT_CUDA(cudaStreamSynchronize(st));
+        cudaFree(L->h_ws);
+        L->h_ws = nullptr;
+        L->h_ws_bytes = 0;
+        MGPT_CUDA(cudaMalloc(&L->h_ws, ws_bytes));
+        L->h_ws_bytes = ws_bytes;
+    }
+    HostSlot& s = hp->slot[hp->n_enqueued & 1];
+    if (s.used) {
+        // the step before last used this slot: its results must be in host memory before its staging is reused
+        MGPT_CUDA(cudaEventSynchronize(s.out_done));
+        MGPT_CUDA(cudaStreamWaitEvent(hp->up, s.compute_done, 0));       // its backward read x until the end
+    }
+    ++hp->n_enqueued;
+    s.used = true;
+    // up: x, then dy, behind the previous step's dy
+    MGPT_CUDA(cudaMemcpyAsync(s.x, x_host, io_bytes, cudaMemcpyHostToDevice, hp->up));
+    MGPT_CUDA(cudaEventRecord(s.in_x, hp->up));
+    if (dy_host) {
+        MGPT_CUDA(cudaMemcpyAsync(s.dy, dy_host, io_bytes, cudaMemcpyHostToDevice, hp->up));
+        MGPT_CUDA(cudaEventRecord(s.in_dy, hp->up));
+    }
+    // compute, in call order on the caller's stream
+    MGPT_CUDA(cudaStreamWaitEvent(st, s.in_x, 0));
+    MGPT_TRY(mgpt_moe_forward(L, s.x, s.y, n_tokens, io, L->h_ws, L->h_ws_bytes, stream));
+    MGPT_CUDA(cudaEventRecord(s.y_ready, st));
+    // down: y as soon as forward is done, dx as soon as backward has written it (before the weight gradients)
+    MGPT_CUDA(cudaStreamWaitEvent(hp->down, s.y_ready, 0));
+    MGPT_CUDA(cudaMemcpyAsync(y_host, s.y, io_bytes, cudaMemcpyDeviceToHost, hp->down));
+    if (dy_host) {
+        MGPT_CUDA(cudaStreamWaitEvent(st, s.in_dy, 0));
+        L->dx_ready_event = s.dx_ready;
+        const int brc = mgpt_moe_backward(L, s.x, s.dy, s.dx, io, L->h_ws, L->h_ws_bytes, stream);
+        L->dx_ready_event = nullptr;
+        MGPT_TRY(brc);
+        MGPT_CUDA(cudaStreamWaitEvent(hp->down, s.dx_ready, 0));
+        MGPT_CUDA(cudaMemcpyAsync(dx_host, s.dx, io_bytes, cudaMemcpyDeviceToHost, hp->down));
+    }
+    MGPT_CUDA(cudaEventRecord(s.compute_done, st));
+    MGPT_CUDA(cudaEventRecord(s.out_done, hp->down));
+    return 0;
+}
+
+int mgpt_moe_step_host_wait(mgpt_moe_layer* L)
+{
+    if (!L) return fail(MGPT_MOE_EINVAL, "null layer");
+    HostPipe* hp = (HostPipe*)L->host_pipe;
+    if (!hp || hp->n_enqueued == 0) return 0;
+    MGPT_CUDA(cudaSetDevice(L->device));
+    MGPT_TRY(host_pipe_drain(L, hp));
+    MGPT_TRY(status_fetch(L, hp->compute));
+    MGPT_CUDA(cudaStreamSynchronize(hp->compute));
+    return status_result(L, hp->compute, nullptr);
 }
 
 static const char* const kStageNames[ST_COUNT] = {

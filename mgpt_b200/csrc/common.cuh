@@ -149,6 +149,7 @@ struct mgpt_moe_layer {
     cudaStream_t copy_stream = nullptr;      // second stream of mgpt_moe_step_host (copies that overlap compute)
     cudaEvent_t copy_ev[5] = {};
     cudaEvent_t dx_ready_event = nullptr;    // when set, backward records it as soon as dx is complete
+    void* host_pipe = nullptr;               // mgpt_moe_step_host_async: two slots of device staging, copy streams, events
 
     // TMA descriptors (opaque, built per workspace pointer)
     void* tc_state = nullptr;
@@ -232,6 +233,7 @@ int tc_init(mgpt_moe_layer* L);
 bool tc_fused_bias_grads(const Dims& d);
 int tc_selftest_bounded_wait(mgpt_moe_layer* L, cudaStream_t st);
 void tc_destroy(mgpt_moe_layer* L);
+void host_pipe_destroy(mgpt_moe_layer* L);          // frees the staging of mgpt_moe_step_host_async (waits for steps in flight)
 int launch_sync_router_only(mgpt_moe_layer* L, cudaStream_t st);
 int launch_adamw(mgpt_moe_layer* L, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
                  cudaStream_t st, float grad_clip = 0.0f, int skip_nonfinite = 0);

@@ -24,6 +24,92 @@ constexpr int R_XPAD = 36;     // padded row of the staged x tile (floats): rows
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 
+// Bias, softmax with the reference's summation order, clamp and top-k for the TPW token groups of a warp whose
+// logit sums are in acc (layers/MoELayer.cpp:96-131).
+template <int EL, int EPL, int TPW>
+__device__ __forceinline__ void router_finish(const float (&acc)[TPW][EPL], const int* stok, int warp, int sub, int el,
+                                              int E, int k, const float* __restrict__ br, float* __restrict__ logits,
+                                              float* __restrict__ probs, int32_t* __restrict__ top_idx,
+                                              float* __restrict__ top_p)
+{
+    constexpr int SUB = 32 / EL;
+    constexpr int TOK_W = TPW * SUB;
+    float bias[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) bias[i] = (el + 32 * i < E) ? br[el + 32 * i] : 0.0f;
+
+    const unsigned full = 0xffffffffu;
+#pragma unroll
+    for (int t = 0; t < TPW; ++t) {
+        // every lane runs the warp-level steps (tokens past N compute on zeros and store nothing)
+        const int tok = stok[warp * TOK_W + t * SUB + sub];
+        const bool live = tok >= 0;
+        float lg[EPL], p[EPL];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            lg[i] = __fadd_rn(acc[t][i], bias[i]);
+            if (el + 32 * i < E) mx = fmaxf(mx, lg[i]);
+        }
+#pragma unroll
+        for (int o = EL / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
+        // exp through double and one rounding: agrees with a correctly rounded expf
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) p[i] = (el + 32 * i < E) ? (float)exp((double)__fsub_rn(lg[i], mx)) : 0.0f;
+        // the reference adds the E terms in index order
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int lim = min(EL, E - 32 * i);
+            for (int l = 0; l < lim; ++l) sum = __fadd_rn(sum, __shfl_sync(full, p[i], l, EL));
+        }
+        const float inv = __fdiv_rn(1.0f, fmaxf(sum, 1e-15f));
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            p[i] = fminf(fmaxf(__fmul_rn(p[i], inv), 1e-7f), 1.0f);
+            const int e = el + 32 * i;
+            if (live && e < E) {
+                probs[(size_t)tok * E + e] = p[i];
+                if (logits) logits[(size_t)tok * E + e] = lg[i];
+            }
+        }
+        // k rounds of (value desc, index asc) arg-max == the reference's stable insertion
+        unsigned taken = 0;
+        int my_idx = -1;
+        float my_val = 0.0f;
+        for (int r = 0; r < k; ++r) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const int e = el + 32 * i;
+                if (e < E && !(taken & (1u << i)) && p[i] > bv) {
+                    bv = p[i];
+                    bi = e;
+                }
+            }
+#pragma unroll
+            for (int o = EL / 2; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(full, bv, o);
+                const int oi = __shfl_xor_sync(full, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) {
+                    bv = ov;
+                    bi = oi;
+                }
+            }
+            if ((bi & 31) == el && bi != 0x7fffffff) taken |= 1u << (bi >> 5);
+            if (el == r) {
+                my_idx = bi;
+                my_val = bv;
+            }
+        }
+        if (live && el < k) {
+            top_idx[(size_t)tok * k + el] = my_idx;
+            top_p[(size_t)tok * k + el] = my_val;
+        }
+    }
+}
+
 // EL lanes share one token (lane % EL owns experts el, el+32, ...: EPL of them, EPL > 1 only
 // with EL = 32); a warp therefore works on 32/EL tokens at once and on TPW such groups in
 // sequence, which gives every lane TPW*EPL independent accumulation chains.
@@ -181,80 +267,105 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
         }
     }
 
-    float bias[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) bias[i] = (el + 32 * i < E) ? br[el + 32 * i] : 0.0f;
+    router_finish<EL, EPL, TPW>(acc, stok, warp, sub, el, E, k, br, logits, probs, top_idx, top_p);
+}
 
-    const unsigned full = 0xffffffffu;
-#pragma unroll
-    for (int t = 0; t < TPW; ++t) {
-        // every lane runs the warp-level steps (tokens past N compute on zeros and store nothing)
-        const int tok = stok[warp * TOK_W + t * SUB + sub];
-        const bool live = tok >= 0;
-        float lg[EPL], p[EPL];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            lg[i] = __fadd_rn(acc[t][i], bias[i]);
-            if (el + 32 * i < E) mx = fmaxf(mx, lg[i]);
+// The exact pass over a LIST of tokens (second pass of the screened router): a few thousand tokens, so only a CTA or
+// two per SM, and what decides the time is the latency of one CTA's 64 chunk steps.  The chunks therefore come
+// through a ring of shared-memory stages filled by cp.async three chunks ahead (the kernel above loads one chunk
+// ahead through registers, which is enough only when a dozen CTAs per SM hide each other's waits).  Same arithmetic:
+// one warp pass per token, lane el owns experts el, el+32, ..., acc = fadd(acc, fmul(x, w)) in channel order.
+// Needs C % 32 == 0, E == 32*EPL and 16-byte aligned x and Wr.
+template <typename TIn, int EPL>
+__global__ void __launch_bounds__(R_WARPS * 32)
+router_list_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ br,
+                   int C, int E, int k, float* __restrict__ logits, float* __restrict__ probs,
+                   int32_t* __restrict__ top_idx, float* __restrict__ top_p,
+                   const int32_t* __restrict__ list, const int32_t* __restrict__ list_count)
+{
+    constexpr int TPW = 4, TOK = R_WARPS * TPW, WCOLS = 32 * EPL, THREADS = R_WARPS * 32;
+    constexpr int ST = EPL <= 2 ? 4 : 2;            // stages: 36 KiB of static shared memory at most
+    constexpr int XV = 16 / sizeof(TIn);            // elements per 16-byte piece
+    constexpr int XPT = R_CK / XV;                  // pieces per token per chunk
+    constexpr int W_VECS = R_CK * WCOLS / 4;
+    __shared__ __align__(16) TIn xs[ST][TOK][R_CK];
+    __shared__ __align__(16) float wsm[ST][R_CK][WCOLS];
+    __shared__ int stok[TOK];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_active = *list_count;
+    const int tok0 = blockIdx.x * TOK;
+    if (tok0 >= n_active) return;
+    for (int i = tid; i < TOK; i += THREADS) stok[i] = tok0 + i < n_active ? list[tok0 + i] : -1;
+    __syncthreads();
+
+    auto issue = [&](int ci, int buf) {
+        const int c0 = ci * R_CK;
+        for (int v = tid; v < W_VECS; v += THREADS) {
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&wsm[buf][0][0] + v * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(Wr + (size_t)c0 * E + v * 4) : "memory");
         }
-#pragma unroll
-        for (int o = EL / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
-        // exp through double and one rounding: agrees with a correctly rounded expf
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) p[i] = (el + 32 * i < E) ? (float)exp((double)__fsub_rn(lg[i], mx)) : 0.0f;
-        // the reference adds the E terms in index order
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            const int lim = min(EL, E - 32 * i);
-            for (int l = 0; l < lim; ++l) sum = __fadd_rn(sum, __shfl_sync(full, p[i], l, EL));
-        }
-        const float inv = __fdiv_rn(1.0f, fmaxf(sum, 1e-15f));
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            p[i] = fminf(fmaxf(__fmul_rn(p[i], inv), 1e-7f), 1.0f);
-            const int e = el + 32 * i;
-            if (live && e < E) {
-                probs[(size_t)tok * E + e] = p[i];
-                if (logits) logits[(size_t)tok * E + e] = lg[i];
+        for (int v = tid; v < TOK * XPT; v += THREADS) {
+            const int tok = stok[v / XPT];
+            TIn* d = &xs[buf][v / XPT][(v % XPT) * XV];
+            if (tok >= 0) {
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(d);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(x + (size_t)tok * C + c0 + (v % XPT) * XV) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);      // adding 0*w is exact
             }
         }
-        // k rounds of (value desc, index asc) arg-max == the reference's stable insertion
-        unsigned taken = 0;
-        int my_idx = -1;
-        float my_val = 0.0f;
-        for (int r = 0; r < k; ++r) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
+    };
+
+    float acc[TPW][EPL];
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) {
-                const int e = el + 32 * i;
-                if (e < E && !(taken & (1u << i)) && p[i] > bv) {
-                    bv = p[i];
-                    bi = e;
+    for (int t = 0; t < TPW; ++t)
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) acc[t][i] = 0.0f;
+
+    auto compute = [&](int buf) {
+#pragma unroll 2
+        for (int j = 0; j < R_CK; j += 4) {
+            float xv[TPW][4];
+#pragma unroll
+            for (int t = 0; t < TPW; ++t) {
+                if constexpr (sizeof(TIn) == 2) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(&xs[buf][warp * TPW + t][j]);
+                    xv[t][0] = __uint_as_float(u.x << 16); xv[t][1] = __uint_as_float(u.x & 0xffff0000u);
+                    xv[t][2] = __uint_as_float(u.y << 16); xv[t][3] = __uint_as_float(u.y & 0xffff0000u);
+                } else {
+                    const float4 f = *reinterpret_cast<const float4*>(&xs[buf][warp * TPW + t][j]);
+                    xv[t][0] = f.x; xv[t][1] = f.y; xv[t][2] = f.z; xv[t][3] = f.w;
                 }
             }
 #pragma unroll
-            for (int o = EL / 2; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(full, bv, o);
-                const int oi = __shfl_xor_sync(full, bi, o);
-                if (ov > bv || (ov == bv && oi < bi)) {
-                    bv = ov;
-                    bi = oi;
-                }
-            }
-            if ((bi & 31) == el && bi != 0x7fffffff) taken |= 1u << (bi >> 5);
-            if (el == r) {
-                my_idx = bi;
-                my_val = bv;
+            for (int jj = 0; jj < 4; ++jj) {
+                float w[EPL];
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) w[i] = wsm[buf][j + jj][lane + 32 * i];
+#pragma unroll
+                for (int t = 0; t < TPW; ++t)
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) acc[t][i] = __fadd_rn(acc[t][i], __fmul_rn(xv[t][jj], w[i]));
             }
         }
-        if (live && el < k) {
-            top_idx[(size_t)tok * k + el] = my_idx;
-            top_p[(size_t)tok * k + el] = my_val;
-        }
+    };
+
+    const int nchunks = C / R_CK;
+#pragma unroll
+    for (int s = 0; s < ST - 1; ++s) {
+        if (s < nchunks) issue(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    for (int ci = 0; ci < nchunks; ++ci) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(ST - 2) : "memory");
+        __syncthreads();                               // chunk ci has landed for everyone; chunk ci-1's stage is free
+        const int nxt = ci + ST - 1;
+        if (nxt < nchunks) issue(nxt, nxt % ST);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        compute(ci % ST);
+    }
+    router_finish<32, EPL, TPW>(acc, stok, warp, 0, lane, E, k, br, logits, probs, top_idx, top_p);
 }
 
 // dlogits = P * (dP - <dP,P>),  dP = scatter(d_top_p) + alpha*E*f_e/N
@@ -544,6 +655,14 @@ int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, i
     }
     // Second pass of the screened router: a fraction of the tokens, how many is only known on the device.  Small
     // CTAs (16 tokens) so that the few thousand listed tokens still spread over every SM.
+    if (list && C % R_CK == 0 && E % 32 == 0 && E <= 128 && E != 96 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)Wr & 15) == 0) {
+        const int grid = (N + 15) / 16;
+        if (E == 32) router_list_kernel<TIn, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        else if (E == 64) router_list_kernel<TIn, 2><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        else router_list_kernel<TIn, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        MGPT_LAUNCHED("router_list_kernel");
+        return 0;
+    }
     if (list && E > 32 && E <= 64)
         return router_fwd_launch<TIn, 32, 2, 4>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
     if (list && E > 16 && E <= 32)

@@ -282,5 +282,20 @@ class MoELayer:
             n, self._io(x_host), self._stream()))
 
 
+    def step_host_async(self, x_host: torch.Tensor, dy_host, y_host: torch.Tensor, dx_host) -> None:
+        """The same step, enqueued without waiting: consecutive calls overlap one step's copies with another's
+        kernels (two steps in flight at most).  ``y_host`` / ``dx_host`` are valid after the call after next, or
+        after :meth:`step_host_wait`; all four buffers must stay alive (pinned) until then."""
+        n = x_host.numel() // self.C
+        _lib.check(self.lib.mgpt_moe_step_host_async(
+            self._h, x_host.data_ptr(), dy_host.data_ptr() if dy_host is not None else None,
+            y_host.data_ptr(), dx_host.data_ptr() if dx_host is not None else None,
+            n, self._io(x_host), self._stream()))
+
+    def step_host_wait(self) -> None:
+        """Waits for every step enqueued by :meth:`step_host_async`; raises if a kernel recorded an error."""
+        _lib.check(self.lib.mgpt_moe_step_host_wait(self._h))
+
+
 def launch_count(reset: bool = False) -> int:
     return int(_lib.load().mgpt_moe_launch_count(1 if reset else 0))
