@@ -610,6 +610,9 @@ def run_ours(args, w):
         E_local = w.E // world
         chunks = args.ep_chunks if E_local % max(1, args.ep_chunks) == 0 else 1
         native = args.ep_impl == "native"
+        if args.ep_transport == "peer" and not all(torch.cuda.can_device_access_peer(local, o)
+                                                   for o in range(world) if o != local):
+            args.ep_transport = "collective"       # no peer access between these GPUs (same answer on every rank of a node)
         if native:
             # the whole exchange behind the C ABI (mgpt_moe_ep_*: the library's own NCCL communicator and stream)
             from mgpt_b200.ep import NativeExpertParallelMoE
@@ -618,7 +621,7 @@ def run_ours(args, w):
                                             lb_alpha=w.alpha, n_chunks=chunks)
         else:
             layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha,
-                                      n_chunks=chunks, sm_budget=args.ep_sm_budget)
+                                      n_chunks=chunks, sm_budget=args.ep_sm_budget, transport=args.ep_transport)
         # router: the same tensors on every rank; experts: those this rank owns, by their global index
         load_synth_params(layer.get_parameters(), w, dev,
                           lambda i: i if i < 2 else 2 + 6 * layer.global_expert((i - 2) // 6) + (i - 2) % 6)
@@ -734,9 +737,14 @@ def run_ours(args, w):
                         "dx_rel_l2": rel_l2(last["dx"], single["dx"]) if w.backward else None,
                         "counts_equal": None if counts_ep is None else counts_ep == [int(c) for c in single["counts"]],
                         "note": "rank 0: expert-parallel result vs the one-GPU layer on the same seeded tokens and weights"}
+        if not native:
+            layer.close_peer()
         dist.barrier()
         parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
-                       + ("NCCL point-to-point groups inside the library (mgpt_moe_ep_*)" if native else "NCCL all-to-all (torch.distributed)")
+                       + ("NCCL point-to-point groups inside the library (mgpt_moe_ep_*)" if native else
+                          "rows pulled from the producers' buffers by copy engines over NVLink (CUDA IPC, mgpt_moe_peer_*), "
+                          "NCCL for the counts and the barriers" if args.ep_transport == "peer" else
+                          "NCCL all-to-all (torch.distributed)")
                        + f" for dispatch and combine, experts in {chunks} chunk(s) "
                        "(a chunk's exchange overlaps the previous chunk's expert work)")
 
@@ -815,6 +823,8 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=2, help="N>1: expert chunks whose exchange overlaps compute")
     ap.add_argument("--ep-impl", default="python", choices=["python", "native"],
                     help="N>1: exchange driven from Python over torch.distributed, or entirely inside the C library")
+    ap.add_argument("--ep-transport", default="peer", choices=["collective", "peer"],
+                    help="N>1, --ep-impl python: rows by all_to_all_single, or pulled by copy engines from peer buffers")
     ap.add_argument("--ep-sm-budget", type=int, default=0,
                     help="N>1: CTAs of the persistent expert kernels (0 = every SM); leaves SMs to the exchange kernels")
     ap.add_argument("--cpu-sample", type=int, default=0, help="tokens per CPU-baseline step")

@@ -403,6 +403,25 @@ int  mgpt_moe_ep_backward(mgpt_moe_ep* ep, const void* x, const void* dy, void* 
 int  mgpt_moe_ep_received_counts(mgpt_moe_ep* ep, int32_t* host_counts);
 int  mgpt_moe_ep_check_status(mgpt_moe_ep* ep);
 
+/* Row buffers that the other GPUs of the node read directly, for expert-
+ * parallel callers that compose the stage calls themselves (mgpt_b200/ep.py).
+ * A collective's copy kernels need SMs, and this library's persistent kernels
+ * hold all of them; a copy engine needs none. So each rank allocates the
+ * buffers it produces rows into with mgpt_moe_peer_alloc, hands the 64-byte
+ * handle to the other processes of the node by its own transport, and the
+ * rank that needs a block pulls it with mgpt_moe_peer_copy from the pointer
+ * mgpt_moe_peer_open gave it (cudaMemcpyAsync over NVLink, beside the
+ * kernels). Ordering between producer and reader is the caller's (a barrier of
+ * its process group between "rows written" and "rows pulled"). A handle can
+ * be opened once per process; close every mapping before the owner frees the
+ * buffer. No reference counterpart (the reference has one device). */
+#define MGPT_MOE_PEER_HANDLE_BYTES 64
+int  mgpt_moe_peer_alloc(int device, size_t bytes, void** ptr, void* handle /* [MGPT_MOE_PEER_HANDLE_BYTES] out */);
+int  mgpt_moe_peer_open(int device, const void* handle, void** ptr);
+int  mgpt_moe_peer_close(int device, void* ptr);
+int  mgpt_moe_peer_free(int device, void* ptr);
+int  mgpt_moe_peer_copy(void* dst, const void* src, size_t bytes, mgpt_stream_t stream);
+
 /* The same plan for callers that can neither pass scratch nor let the library
  * allocate: an engine whose arena already owns all device memory, or a step
  * loop that must never run into cudaMalloc (it synchronises the whole device).

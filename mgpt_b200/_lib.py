@@ -26,10 +26,12 @@ SYMBOLS = [
     "mgpt_moe_ep_global_expert", "mgpt_moe_ep_bind_params", "mgpt_moe_ep_sync_weights", "mgpt_moe_ep_forward",
     "mgpt_moe_ep_backward", "mgpt_moe_ep_received_counts", "mgpt_moe_ep_check_status",
     "mgpt_moe_route_plan", "mgpt_moe_route_rows",
+    "mgpt_moe_peer_alloc", "mgpt_moe_peer_open", "mgpt_moe_peer_close", "mgpt_moe_peer_free", "mgpt_moe_peer_copy",
     "mgpt_moe_block_workspace_bytes", "mgpt_moe_block_forward", "mgpt_moe_block_backward",
     "mgpt_moe_set_weight_grad_overwrite", "mgpt_moe_inference_workspace_bytes", "mgpt_moe_forward_inference", "mgpt_moe_experts_backward_rows", "mgpt_moe_experts_backward_params",
 ]
 PLAN_NOALLOC_MAX_ROWS = 1048576
+PEER_HANDLE_BYTES = 64
 N_STAGES = 12
 
 
@@ -131,6 +133,11 @@ def load() -> ct.CDLL:
     lib.mgpt_moe_ep_backward.argtypes = [vp, vp, vp, vp, i32, vp]
     lib.mgpt_moe_ep_received_counts.argtypes = [vp, ct.POINTER(ct.c_int32)]
     lib.mgpt_moe_ep_check_status.argtypes = [vp]
+    lib.mgpt_moe_peer_alloc.argtypes = [i32, sz, ct.POINTER(vp), vp]
+    lib.mgpt_moe_peer_open.argtypes = [i32, vp, ct.POINTER(vp)]
+    lib.mgpt_moe_peer_close.argtypes = [i32, vp]
+    lib.mgpt_moe_peer_free.argtypes = [i32, vp]
+    lib.mgpt_moe_peer_copy.argtypes = [vp, vp, sz, vp]
     lib.mgpt_moe_block_workspace_bytes.argtypes = [vp, i32, i32]
     lib.mgpt_moe_block_workspace_bytes.restype = sz
     lib.mgpt_moe_block_forward.argtypes = [vp, vp, vp, ct.c_float, vp, i32, i32, vp, sz, vp]

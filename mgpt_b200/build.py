@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libmgpt_moe.so")
 
-SOURCES = ["api.cu", "router.cu", "plan.cu", "gemm_simt.cu", "gemm_tc.cu", "router_tc.cu", "weights.cu", "stages.cu", "adamw.cu", "ep.cu", "block.cu"]
+SOURCES = ["api.cu", "router.cu", "plan.cu", "gemm_simt.cu", "gemm_tc.cu", "router_tc.cu", "weights.cu", "stages.cu", "adamw.cu", "ep.cu", "block.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

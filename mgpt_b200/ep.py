@@ -159,13 +159,19 @@ class CudaStages:
         return out
 
     # ---- routing side
-    def route(self, x):
-        """Returns (rows [row_cap, C] in the padded expert-major layout, counts[E] real rows per expert)."""
+    def row_capacity(self, n):
+        """Rows of the padded expert-major layout for n tokens (every expert's segment a multiple of 128)."""
+        self._home_ws = self._home_ws_for(n)
+        return self._view(self.home, self._home_ws, n, "row_src", torch.int32).numel()
+
+    def route(self, x, out=None):
+        """Returns (rows [row_cap, C] in the padded expert-major layout, counts[E] real rows per expert).
+        ``out``: a buffer of at least row_cap rows to write the rows into (else a new tensor)."""
         n = x.shape[0]
         self._home_ws = self._home_ws_for(n)
         self._n = n
         row_cap = self._view(self.home, self._home_ws, n, "row_src", torch.int32).numel()
-        rows = torch.empty(row_cap, self.C, dtype=self.act_dtype, device=self.device)
+        rows = out[:row_cap] if out is not None else torch.empty(row_cap, self.C, dtype=self.act_dtype, device=self.device)
         self._lib_mod.check(self.lib.mgpt_moe_route(self.home, x.data_ptr(), n, self._io(x), self._home_ws.data_ptr(),
                                                     self._home_ws.numel(), rows.data_ptr(), self._stream()))
         counts = self._view(self.home, self._home_ws, n, "counts", torch.int32)
@@ -183,8 +189,8 @@ class CudaStages:
                                                       self._home_ws.data_ptr(), self._home_ws.numel(), self._stream()))
         return y
 
-    def combine_backward(self, rows_back, dy):
-        d_rows = torch.empty_like(rows_back)
+    def combine_backward(self, rows_back, dy, out=None):
+        d_rows = out[:rows_back.shape[0]] if out is not None else torch.empty_like(rows_back)
         self._lib_mod.check(self.lib.mgpt_moe_combine_backward(
             self.home, rows_back.data_ptr(), dy.data_ptr(), self._io(dy), d_rows.data_ptr(),
             self._home_ws.data_ptr(), self._home_ws.numel(), self._stream()))
@@ -198,14 +204,14 @@ class CudaStages:
         return dx
 
     # ---- expert side
-    def experts_forward(self, rows, seg_counts, n_src, chunk=0):
+    def experts_forward(self, rows, seg_counts, n_src, chunk=0, out=None):
         """rows: n_src blocks of padded per-expert segments of chunk ``chunk``;
         seg_counts: int32 [n_src, E_chunk] real counts."""
         n = rows.shape[0]
         h = self.locals[chunk]
         self._local_ws[chunk] = self._ws(h, n, False, self._local_ws[chunk])
         ws = self._local_ws[chunk]
-        out = torch.empty_like(rows)
+        out = torch.empty_like(rows) if out is None else out
         self._seg_counts[chunk] = seg_counts.contiguous()
         self._lib_mod.check(self.lib.mgpt_moe_experts_forward(
             h, rows.data_ptr(), self._seg_counts[chunk].data_ptr(), n_src, n, out.data_ptr(),
@@ -220,9 +226,9 @@ class CudaStages:
             self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
         return d_in
 
-    def experts_backward_rows(self, d_out, chunk=0):
+    def experts_backward_rows(self, d_out, chunk=0, out=None):
         """First half of experts_backward: the gradient w.r.t. the received rows (what the other ranks wait for)."""
-        d_in = torch.empty_like(d_out)
+        d_in = torch.empty_like(d_out) if out is None else out
         ws = self._local_ws[chunk]
         self._lib_mod.check(self.lib.mgpt_moe_experts_backward_rows(
             self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
@@ -238,11 +244,63 @@ class CudaStages:
             self.locals[chunk], d_out.data_ptr(), d_in.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()))
 
 
+class _RawCuda:
+    """A device pointer dressed up for torch.as_tensor (bytes; the caller views it in its own dtype)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerRows:
+    """One row buffer per rank that the other ranks of the node read directly (``mgpt_moe_peer_*``: cudaMalloc +
+    CUDA IPC).  ``tensor`` is this rank's buffer [rows, C]; ``peer[s]`` the device address of rank s's buffer as
+    mapped into this process.  Collective over the group (the handles are all-gathered)."""
+
+    def __init__(self, lib_mod, lib, group, rank, world, device, rows, C, dtype):
+        self.lib_mod, self.lib, self.device_index = lib_mod, lib, device.index
+        self.row_bytes = C * torch.empty((), dtype=dtype).element_size()
+        nbytes = max(1, rows) * self.row_bytes
+        ptr, handle = ct.c_void_p(), ct.create_string_buffer(lib_mod.PEER_HANDLE_BYTES)
+        lib_mod.check(lib.mgpt_moe_peer_alloc(self.device_index, nbytes, ct.byref(ptr), handle))
+        self.ptr = ptr.value
+        self.tensor = torch.as_tensor(_RawCuda(self.ptr, nbytes), device=device).view(dtype).view(max(1, rows), C)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.peer, self._opened = [], []
+        for s in range(world):
+            if s == rank:
+                self.peer.append(self.ptr)
+                continue
+            p = ct.c_void_p()
+            lib_mod.check(lib.mgpt_moe_peer_open(self.device_index, handles[s], ct.byref(p)))
+            self.peer.append(p.value)
+            self._opened.append(p.value)
+
+    def close(self, group=None):
+        """Collective: every rank closes its mappings before any rank frees its buffer."""
+        for p in self._opened:
+            self.lib.mgpt_moe_peer_close(self.device_index, ct.c_void_p(p))
+        self._opened = []
+        if dist.is_initialized():
+            dist.barrier(group=group)
+        if self.ptr:
+            self.tensor = None
+            self.lib.mgpt_moe_peer_free(self.device_index, ct.c_void_p(self.ptr))
+            self.ptr = None
+
+
 class ExpertParallelMoE:
     """Same role as the reference's MoELayer, with the experts sharded over a process group."""
 
     def __init__(self, embed_dim, hidden_dim, num_experts, top_k, *, group=None, stages=None, mode="bf16",
-                 device=0, lb_alpha=0.01, n_chunks=1, sm_budget=0):
+                 device=0, lb_alpha=0.01, n_chunks=1, sm_budget=0, transport="collective"):
+        """``transport``: "collective" moves the rows with ``all_to_all_single`` (NCCL's copy kernels; gloo on CPU);
+        "peer" lets the rank that needs a block pull it from the producer's buffer with a copy engine
+        (one node, GPUs with peer access; see ``PeerRows``), so that the exchange needs no SM."""
+        if transport not in ("collective", "peer"):
+            raise ValueError(f"unknown transport {transport!r}")
+        self.transport = transport
+        self._peer = None
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -325,11 +383,172 @@ class ExpertParallelMoE:
     def _pad128(t):
         return (t + 127) // 128 * 128
 
+    # ---- "peer" transport: persistent buffers, pulled by copy engines
+    def _peer_setup(self, n):
+        """Buffers for up to n tokens per rank (collective on first use or growth).  Four are readable by the peers:
+        the rows this rank routes (A), its experts' outputs (B), and the two gradient mirrors (Cg, D)."""
+        pb = self._peer
+        if pb is not None and n <= pb["n"]:
+            return pb
+        st = self.stages
+        t = torch.tensor([n], device=st.device, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        n_max = int(t.item())
+        if pb is not None:
+            self.close_peer()
+        cap_send = st.row_capacity(n_max)
+        cap_recv = self.world * cap_send              # worst case: every rank routes all of its rows to this one
+        mk = lambda rows: PeerRows(st._lib_mod, st.lib, self.group, self.rank, self.world, st.device, rows, self.C,
+                                   st.act_dtype)
+        loc = lambda rows: torch.empty(rows, self.C, dtype=st.act_dtype, device=st.device)
+        pb = {"n": n_max, "A": mk(cap_send), "B": mk(cap_recv), "Cg": mk(cap_send), "D": mk(cap_recv),
+              "recv": loc(cap_recv), "rows_back": loc(cap_send), "d_recv": loc(cap_recv), "d_back": loc(cap_send),
+              "stream": torch.cuda.Stream(device=st.device, priority=-1),
+              "flag": torch.zeros(1, device=st.device)}
+        self._peer = pb
+        return pb
+
+    def close_peer(self):
+        """Collective: releases the peer-readable buffers."""
+        if self._peer is not None:
+            torch.cuda.synchronize()
+            for k in ("A", "B", "Cg", "D"):
+                self._peer[k].close(self.group)
+            self._peer = None
+
+    def _barrier_then(self, X):
+        """Every rank's kernels queued on the current stream so far are complete on every rank before anything
+        queued on X from here on starts.  The barrier (a one-element all-reduce) is queued in the order of the
+        compute stream, not beside it: its kernel needs an SM, the persistent kernels hold them all, and queued
+        beside them it would start only when the NEXT compute kernel ends, which is when the copies it releases
+        should already be done."""
+        cur = torch.cuda.current_stream()
+        dist.all_reduce(self._peer["flag"], group=self.group)
+        e = torch.cuda.Event()
+        e.record(cur)
+        X.wait_event(e)
+
+    def _pull(self, dst, dst_row, src_ptr, src_row, rows, row_bytes, stream):
+        if rows > 0:
+            st = self.stages
+            st._lib_mod.check(st.lib.mgpt_moe_peer_copy(
+                ct.c_void_p(dst.data_ptr() + dst_row * row_bytes), ct.c_void_p(src_ptr + src_row * row_bytes),
+                rows * row_bytes, ct.c_void_p(stream.cuda_stream)))
+
+    def _peer_layout(self, counts):
+        """All-gathers the per-destination counts and derives, for every (source, destination, chunk), the rows of
+        the block and where it sits in the source's send layout ([chunk][destination]) and in the destination's
+        receive layout ([chunk][source]).  One host synchronisation."""
+        import numpy as np
+        G, nc, Ec = self.world, self.n_chunks, self.E_chunk
+        send_counts = counts.view(nc, G, Ec).permute(1, 0, 2).contiguous()             # [destination, chunk, j]
+        every = torch.empty((G,) + tuple(send_counts.shape), dtype=send_counts.dtype, device=send_counts.device)
+        dist.all_gather_into_tensor(every, send_counts, group=self.group)               # [source, destination, chunk, j]
+        M = every.cpu().numpy().astype(np.int64)
+        blk = ((M + 127) // 128 * 128).sum(3)                                           # [source, destination, chunk]
+        send_off = np.zeros((G, nc, G), dtype=np.int64)                                 # [source][chunk][destination]
+        recv_off = np.zeros((G, nc, G), dtype=np.int64)                                 # [destination][chunk][source]
+        for r in range(G):
+            a = blk[r].T.reshape(-1)                                                    # [chunk][destination] of source r
+            send_off[r] = (np.cumsum(a) - a).reshape(nc, G)
+            b = blk[:, r, :].T.reshape(-1)                                              # [chunk][source] into destination r
+            recv_off[r] = (np.cumsum(b) - b).reshape(nc, G)
+        return every, blk, send_off, recv_off
+
+    def _forward_peer(self, x):
+        G, nc, me = self.world, self.n_chunks, self.rank
+        pb = self._peer_setup(x.shape[0])
+        X, cur = pb["stream"], torch.cuda.current_stream()
+        rb = pb["A"].row_bytes
+        rows, counts = self.stages.route(x, out=pb["A"].tensor)
+        ev_rows = torch.cuda.Event()
+        ev_rows.record(cur)
+        self._mark("route")
+        every, blk, send_off, recv_off = self._peer_layout(counts)
+        self._mark("counts_exchange_and_host_sync")
+        order = [(me + i) % G for i in range(G)]          # every rank starts at a different peer
+        n_send = int(blk[me].sum())
+        recv_rows_c = [int(blk[:, me, c].sum()) for c in range(nc)]
+        recv_base = [int(recv_off[me][c][0]) for c in range(nc)]
+        # the all-gather of the counts was queued behind the routing kernels on every rank and has completed (the host
+        # has read its result): every rank's rows are written
+        X.wait_event(ev_rows)
+        ev_recv = []
+        for c in range(nc):
+            for s in order:
+                self._pull(pb["recv"], int(recv_off[me][c][s]), pb["A"].peer[s], int(send_off[s][c][me]),
+                           int(blk[s][me][c]), rb, X)
+            e = torch.cuda.Event()
+            e.record(X)
+            ev_recv.append(e)
+        rows_back = pb["rows_back"][:n_send]
+        for c in range(nc):
+            cur.wait_event(ev_recv[c])
+            self._mark("rows_all_to_all")
+            lo, hi = recv_base[c], recv_base[c] + recv_rows_c[c]
+            self.stages.experts_forward(pb["recv"][lo:hi], every[:, me, c, :], G, *([c] if nc > 1 else []),
+                                        out=pb["B"].tensor[lo:hi])
+            self._mark("experts_forward")
+            self._barrier_then(X)                         # chunk c's outputs are written on every rank
+            for o in order:
+                self._pull(rows_back, int(send_off[me][c][o]), pb["B"].peer[o], int(recv_off[o][c][me]),
+                           int(blk[me][o][c]), rb, X)
+        ev_back = torch.cuda.Event()
+        ev_back.record(X)
+        cur.wait_event(ev_back)
+        self._mark("rows_back_all_to_all")
+        y = self.stages.combine(rows_back, x)
+        self._mark("combine")
+        self._saved = (x, rows_back, (blk, send_off, recv_off, recv_base, recv_rows_c, order), None, None)
+        self.last_recv_counts = every[:, me].reshape(G, nc * self.E_chunk)      # [source rank, local expert]
+        return y
+
+    def _backward_peer(self, dy):
+        G, nc, me = self.world, self.n_chunks, self.rank
+        pb = self._peer
+        X, cur = pb["stream"], torch.cuda.current_stream()
+        rb = pb["A"].row_bytes
+        x, rows_back, (blk, send_off, recv_off, recv_base, recv_rows_c, order), _, _ = self._saved
+        n_send = rows_back.shape[0]
+        self.stages.combine_backward(rows_back, dy, out=pb["Cg"].tensor)
+        self._mark("combine_backward")
+        self._barrier_then(X)                             # every rank's row gradients are written
+        ev_recv = []
+        for c in range(nc):
+            for s in order:
+                self._pull(pb["d_recv"], int(recv_off[me][c][s]), pb["Cg"].peer[s], int(send_off[s][c][me]),
+                           int(blk[s][me][c]), rb, X)
+            e = torch.cuda.Event()
+            e.record(X)
+            ev_recv.append(e)
+        d_back = pb["d_back"][:n_send]
+        for c in range(nc):
+            cur.wait_event(ev_recv[c])
+            self._mark("grad_rows_all_to_all")
+            lo, hi = recv_base[c], recv_base[c] + recv_rows_c[c]
+            self.stages.experts_backward_rows(pb["d_recv"][lo:hi], *([c] if nc > 1 else []), out=pb["D"].tensor[lo:hi])
+            self._mark("experts_backward_rows")
+            self._barrier_then(X)                         # chunk c's input gradients are written on every rank
+            for o in order:
+                self._pull(d_back, int(send_off[me][c][o]), pb["D"].peer[o], int(recv_off[o][c][me]),
+                           int(blk[me][o][c]), rb, X)
+            self.stages.experts_backward_params(*([c] if nc > 1 else []))
+            self._mark("experts_backward_params")
+        ev_back = torch.cuda.Event()
+        ev_back.record(X)
+        cur.wait_event(ev_back)
+        self._mark("grad_rows_back_all_to_all")
+        dx = self.stages.route_backward(x, d_back)
+        self._mark("route_backward")
+        return dx
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         G, nc, Ec = self.world, self.n_chunks, self.E_chunk
         if self.phase_events is not None:
             self.phase_events["order"] = []
         self._mark("start")
+        if self.transport == "peer" and G > 1:
+            return self._forward_peer(x)
         rows, counts = self.stages.route(x)              # padded expert-major rows, counts[E] in (chunk, rank, j) order
         self._mark("route")
         send_counts = counts.view(nc, G, Ec).permute(1, 0, 2).contiguous()      # [destination, chunk, j]
@@ -378,6 +597,8 @@ class ExpertParallelMoE:
         if self._saved is None:
             raise RuntimeError("backward before forward")
         nc = self.n_chunks
+        if self.transport == "peer" and self.world > 1:
+            return self._backward_peer(dy)
         x, rows_back, send_splits, recv_splits, starts = self._saved
         d_rows = self.stages.combine_backward(rows_back, dy)
         self._mark("combine_backward")

@@ -72,6 +72,18 @@ def _worker(rank, world, port, q):
         run_rank(w, rank, world, _stages("bf16", rank, chunks=2, sm_budget=120), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
         w = synth.Workload("epchunks", 2000, 256, 192, 16, 2, "bf16")
         run_rank(w, rank, world, _stages("bf16", rank, chunks=4), f"cuda:{rank}", 2e-2, io=torch.bfloat16)
+        # rows pulled by copy engines from the producers' buffers (CUDA IPC) instead of the collective's copy kernels
+        from mgpt_b200.ep import ExpertParallelMoE
+        for wl, chunks in ((w, 1), (w, 2), (synth.Workload("eppeer", 900, 128, 128, 16, 4, "bf16", skew=True), 2)):
+            mk = lambda ww: ExpertParallelMoE(ww.C, ww.H, ww.E, ww.k, transport="peer",
+                                              stages=_stages("bf16", rank, chunks=chunks)(ww, ww.E // world))
+            layer = run_rank(wl, rank, world, None, f"cuda:{rank}", 2e-2, io=torch.bfloat16, make_layer=mk)
+            # a second step through the same buffers, with fewer tokens
+            y1 = layer.forward(torch.ones(64, wl.C, dtype=torch.bfloat16, device=f"cuda:{rank}"))
+            dx1 = layer.backward(torch.ones(64, wl.C, dtype=torch.bfloat16, device=f"cuda:{rank}"))
+            assert torch.isfinite(y1.float()).all() and torch.isfinite(dx1.float()).all()
+            layer.stages.check_status()
+            layer.close_peer()
         # the same through the C ABI alone (the library's own NCCL communicator and exchange stream)
         from mgpt_b200.ep import NativeExpertParallelMoE
         for chunks in (1, 2):
