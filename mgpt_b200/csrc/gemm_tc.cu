@@ -578,6 +578,7 @@ struct WgradP {
     WgradProb prob[3];
     int n_probs, total_items;
     int overwrite;          // grad = product (zeros for experts without rows) instead of grad += product
+    int block_loads;        // the tensor maps are the column-block form: one load per operand tile and stage
     // bias gradients from the same operand tiles (null: none): gb[pr][e][col] += column sums, over the expert's
     // rows, of the operand of problem pr whose columns are that bias's (the A operand when the problem is
     // computed transposed, else the B operand)
@@ -652,6 +653,13 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant_
                         const uint32_t a_dst = smem_u32(pipe.tiles + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
                         mbar_expect_tx(pipe.full(s), STAGE_BYTES);
                         const int row = seg_r0 + kb * BK;
+                        if (p.block_loads) {
+                            // two loads per stage instead of six: with 64-row stages this kernel waits for the
+                            // producer thread's issue rate as much as for the bytes (measured: 1.44 -> 1.39 ms)
+                            tma_load_3d(a_dst, mA, 0, row, w.m0 / 64, pipe.full(s));
+                            tma_load_3d(b_dst, mB, 0, row, w.n0 / 64, pipe.full(s));
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < BM / 64; ++i) tma_load_2d(a_dst + i * BOX, mA, w.m0 + 64 * i, row, pipe.full(s));
 #pragma unroll
@@ -918,6 +926,20 @@ int make_map_kind(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols
     return 0;
 }
 
+bool make_map_blocks(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t n_blocks)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || cols % 64 != 0) return false;
+    cuuint64_t dims[3] = {64, rows, cols / 64};
+    cuuint64_t strides[2] = {cols * sizeof(bf16), 64 * sizeof(bf16)};
+    cuuint32_t box[3] = {64, box_rows, n_blocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 namespace {
 
 struct TcState {
@@ -932,6 +954,9 @@ struct TcState {
     CUtensorMap Xg, Hh, dYg, dG, dU, WgT, WuT, WdT, Wg, Wu, Wd;
     // reduction-over-rows operand loads (box 64 x 64 rows)
     CUtensorMap Xg_t, Hh_t, dYg_t, dG_t, dU_t;
+    // the same operands by column blocks (one load per operand tile): A side {64, 64 rows, 2}, B side {64, 64 rows, 4}
+    CUtensorMap Xg_b4, dYg_b4, dG_b2, dU_b2, Hh_b2;
+    bool blocks_ok = false;      // the driver took the block maps (else six 2-D loads per stage)
     // epilogue stores (box 32 x 32 rows, 64-byte swizzle)
     CUtensorMap Hh_s, Yg_s, dG_s, dU_s, dXg_s;
 };
@@ -962,6 +987,9 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->dYg_t, dyg, rc, C, 64));
     MGPT_TRY(make_map(&s->dG_t, ws + w.dG, rc, H, 64));
     MGPT_TRY(make_map(&s->dU_t, ws + w.dU, rc, H, 64));
+    s->blocks_ok = make_map_blocks(&s->Xg_b4, xg, rc, C, 64, BN / 64) && make_map_blocks(&s->dYg_b4, dyg, rc, C, 64, BN / 64) &&
+                   make_map_blocks(&s->dG_b2, ws + w.dG, rc, H, 64, BM / 64) && make_map_blocks(&s->dU_b2, ws + w.dU, rc, H, 64, BM / 64) &&
+                   make_map_blocks(&s->Hh_b2, ws + w.Hh, rc, H, 64, BM / 64);
     MGPT_TRY(make_map(&s->Hh_s, ws + w.Hh, rc, H, 32));
     MGPT_TRY(make_map(&s->Yg_s, yg, rc, C, 32));
     MGPT_TRY(make_map(&s->dG_s, ws + w.dG, rc, H, 32));
@@ -1148,8 +1176,13 @@ int tc_experts_backward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStr
     if (tc_fused_bias_grads(d)) {
         g.gb[0] = L->master.gbg; g.gb[1] = L->master.gbu; g.gb[2] = L->master.gbd;
     }
-    tc_wgrad_kernel<<<imin(grid_sms(L, s), items), WG_THREADS, SMEM_BYTES, st>>>(s->dG_t, s->Xg_t, s->dU_t, s->Xg_t, s->Hh_t,
-                                                                       s->dYg_t, g);
+    g.block_loads = s->blocks_ok ? 1 : 0;
+    if (g.block_loads)
+        tc_wgrad_kernel<<<imin(grid_sms(L, s), items), WG_THREADS, SMEM_BYTES, st>>>(s->dG_b2, s->Xg_b4, s->dU_b2, s->Xg_b4,
+                                                                           s->Hh_b2, s->dYg_b4, g);
+    else
+        tc_wgrad_kernel<<<imin(grid_sms(L, s), items), WG_THREADS, SMEM_BYTES, st>>>(s->dG_t, s->Xg_t, s->dU_t, s->Xg_t, s->Hh_t,
+                                                                           s->dYg_t, g);
     MGPT_LAUNCHED("tc_wgrad_kernel");
     L->stage_end(ST_WGRAD, st);
     return 0;

@@ -51,6 +51,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
 {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
@@ -211,5 +217,9 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster)
 int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 // The same with the kind stated: store = false gives a load map (64-column box, 128-byte swizzle) of any box height.
 int make_map_kind(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool store);
+// A [rows, cols] BF16 matrix (cols a multiple of 64) seen as {64 columns, rows, cols/64 column blocks}: one load of
+// a {64, box_rows, n_blocks} box lands as n_blocks consecutive [box_rows][64] tiles in the 128-byte swizzle, the
+// layout the tensor core reads an operand in whose reduction runs over the rows.  False: the driver refused the map.
+bool make_map_blocks(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t n_blocks);
 
 }  // namespace mgpt
