@@ -251,6 +251,34 @@ class _RawCuda:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+class _CopyLanes:
+    """A few streams used as one for copy-engine transfers: blocks from different peers go out on different lanes
+    (one copy at a time does not fill the NVLink ports when the blocks are small), waits and records apply to all."""
+
+    def __init__(self, device, n):
+        self.streams = [torch.cuda.Stream(device=device, priority=-1) for _ in range(n)]
+
+    def wait_event(self, ev):
+        for st in self.streams:
+            st.wait_event(ev)
+
+    def lane(self, i):
+        return self.streams[i % len(self.streams)]
+
+    def record(self):
+        evs = []
+        for st in self.streams:
+            e = torch.cuda.Event()
+            e.record(st)
+            evs.append(e)
+        return evs
+
+
+def _wait_all(stream, events):
+    for e in events:
+        stream.wait_event(e)
+
+
 class PeerRows:
     """One row buffer per rank that the other ranks of the node read directly (``mgpt_moe_peer_*``: cudaMalloc +
     CUDA IPC).  ``tensor`` is this rank's buffer [rows, C]; ``peer[s]`` the device address of rank s's buffer as
@@ -300,6 +328,7 @@ class ExpertParallelMoE:
         if transport not in ("collective", "peer"):
             raise ValueError(f"unknown transport {transport!r}")
         self.transport = transport
+        self.copy_lanes = 1      # streams the pulls are spread over; more than one lets a later chunk's copies compete with the chunk the compute stream is waiting for (8 GPUs: 5.44 ms with three against 5.07 with one)
         self._peer = None
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -403,7 +432,7 @@ class ExpertParallelMoE:
         loc = lambda rows: torch.empty(rows, self.C, dtype=st.act_dtype, device=st.device)
         pb = {"n": n_max, "A": mk(cap_send), "B": mk(cap_recv), "Cg": mk(cap_send), "D": mk(cap_recv),
               "recv": loc(cap_recv), "rows_back": loc(cap_send), "d_recv": loc(cap_recv), "d_back": loc(cap_send),
-              "stream": torch.cuda.Stream(device=st.device, priority=-1),
+              "stream": _CopyLanes(st.device, self.copy_lanes),
               "flag": torch.zeros(1, device=st.device)}
         self._peer = pb
         return pb
@@ -475,27 +504,23 @@ class ExpertParallelMoE:
         X.wait_event(ev_rows)
         ev_recv = []
         for c in range(nc):
-            for s in order:
+            for i, s in enumerate(order):
                 self._pull(pb["recv"], int(recv_off[me][c][s]), pb["A"].peer[s], int(send_off[s][c][me]),
-                           int(blk[s][me][c]), rb, X)
-            e = torch.cuda.Event()
-            e.record(X)
-            ev_recv.append(e)
+                           int(blk[s][me][c]), rb, X.lane(i))
+            ev_recv.append(X.record())
         rows_back = pb["rows_back"][:n_send]
         for c in range(nc):
-            cur.wait_event(ev_recv[c])
+            _wait_all(cur, ev_recv[c])
             self._mark("rows_all_to_all")
             lo, hi = recv_base[c], recv_base[c] + recv_rows_c[c]
             self.stages.experts_forward(pb["recv"][lo:hi], every[:, me, c, :], G, *([c] if nc > 1 else []),
                                         out=pb["B"].tensor[lo:hi])
             self._mark("experts_forward")
             self._barrier_then(X)                         # chunk c's outputs are written on every rank
-            for o in order:
+            for i, o in enumerate(order):
                 self._pull(rows_back, int(send_off[me][c][o]), pb["B"].peer[o], int(recv_off[o][c][me]),
-                           int(blk[me][o][c]), rb, X)
-        ev_back = torch.cuda.Event()
-        ev_back.record(X)
-        cur.wait_event(ev_back)
+                           int(blk[me][o][c]), rb, X.lane(i))
+        _wait_all(cur, X.record())
         self._mark("rows_back_all_to_all")
         y = self.stages.combine(rows_back, x)
         self._mark("combine")
@@ -515,28 +540,24 @@ class ExpertParallelMoE:
         self._barrier_then(X)                             # every rank's row gradients are written
         ev_recv = []
         for c in range(nc):
-            for s in order:
+            for i, s in enumerate(order):
                 self._pull(pb["d_recv"], int(recv_off[me][c][s]), pb["Cg"].peer[s], int(send_off[s][c][me]),
-                           int(blk[s][me][c]), rb, X)
-            e = torch.cuda.Event()
-            e.record(X)
-            ev_recv.append(e)
+                           int(blk[s][me][c]), rb, X.lane(i))
+            ev_recv.append(X.record())
         d_back = pb["d_back"][:n_send]
         for c in range(nc):
-            cur.wait_event(ev_recv[c])
+            _wait_all(cur, ev_recv[c])
             self._mark("grad_rows_all_to_all")
             lo, hi = recv_base[c], recv_base[c] + recv_rows_c[c]
             self.stages.experts_backward_rows(pb["d_recv"][lo:hi], *([c] if nc > 1 else []), out=pb["D"].tensor[lo:hi])
             self._mark("experts_backward_rows")
             self._barrier_then(X)                         # chunk c's input gradients are written on every rank
-            for o in order:
+            for i, o in enumerate(order):
                 self._pull(d_back, int(send_off[me][c][o]), pb["D"].peer[o], int(recv_off[o][c][me]),
-                           int(blk[me][o][c]), rb, X)
+                           int(blk[me][o][c]), rb, X.lane(i))
             self.stages.experts_backward_params(*([c] if nc > 1 else []))
             self._mark("experts_backward_params")
-        ev_back = torch.cuda.Event()
-        ev_back.record(X)
-        cur.wait_event(ev_back)
+        _wait_all(cur, X.record())
         self._mark("grad_rows_back_all_to_all")
         dx = self.stages.route_backward(x, d_back)
         self._mark("route_backward")
