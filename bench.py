@@ -618,7 +618,8 @@ def run_ours(args, w):
             from mgpt_b200.ep import NativeExpertParallelMoE
             layer = NativeExpertParallelMoE(w.C, w.H, w.E, w.k, rank=rank, world=world,
                                             nccl_id=NativeExpertParallelMoE.create_id(), mode=w.dtype, device=local,
-                                            lb_alpha=w.alpha, n_chunks=chunks)
+                                            lb_alpha=w.alpha, n_chunks=chunks,
+                                            max_tokens=N if args.ep_transport == "peer" else 0)
         else:
             layer = ExpertParallelMoE(w.C, w.H, w.E, w.k, mode=w.dtype, device=local, lb_alpha=w.alpha,
                                       n_chunks=chunks, sm_budget=args.ep_sm_budget, transport=args.ep_transport)
@@ -741,7 +742,8 @@ def run_ours(args, w):
             layer.close_peer()
         dist.barrier()
         parallelism = (f"expert parallel: {E_local} of {w.E} experts per GPU, {N} tokens per GPU, "
-                       + ("NCCL point-to-point groups inside the library (mgpt_moe_ep_*)" if native else
+                       + (("copy-engine pulls from peer buffers" if args.ep_transport == "peer" else "NCCL point-to-point groups")
+                          + " inside the library (mgpt_moe_ep_*)" if native else
                           "rows pulled from the producers' buffers by copy engines over NVLink (CUDA IPC, mgpt_moe_peer_*), "
                           "NCCL for the counts and the barriers" if args.ep_transport == "peer" else
                           "NCCL all-to-all (torch.distributed)")
@@ -821,7 +823,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, help="c1 c2 c3 c4 c5-8 c5-64 c5-256 (default c4)")
     ap.add_argument("--ep-chunks", type=int, default=2, help="N>1: expert chunks whose exchange overlaps compute")
-    ap.add_argument("--ep-impl", default="python", choices=["python", "native"],
+    ap.add_argument("--ep-impl", default="native", choices=["python", "native"],
                     help="N>1: exchange driven from Python over torch.distributed, or entirely inside the C library")
     ap.add_argument("--ep-transport", default="peer", choices=["collective", "peer"],
                     help="N>1, --ep-impl python: rows by all_to_all_single, or pulled by copy engines from peer buffers")

@@ -388,6 +388,12 @@ typedef struct {
     int   device;
     int   rank, world;
     int   n_chunks;    /* experts per rank are split into this many chunks (1 = no overlap) */
+    int   max_tokens;  /* > 0 (all ranks in one node with peer access, world > 1): the rows do not travel through
+                          NCCL; every rank keeps its row buffers, sized for this many tokens per call, readable by
+                          the others (CUDA IPC), and the rank that needs a block pulls it with a copy engine, which
+                          takes no SM from the tensor-core kernels.  NCCL then carries the counts (an all-gather)
+                          and the barriers.  Calls with more tokens fail with MGPT_MOE_EINVAL.  0: NCCL
+                          point-to-point for the rows, buffers grown on demand */
 } mgpt_moe_ep_config;
 #define MGPT_MOE_EP_ID_BYTES 128
 int  mgpt_moe_ep_unique_id(void* id_out);

@@ -44,7 +44,7 @@ class Config(ct.Structure):
 class EpConfig(ct.Structure):
     _fields_ = [("embed_dim", ct.c_int), ("hidden_dim", ct.c_int), ("num_experts", ct.c_int), ("top_k", ct.c_int),
                 ("lb_alpha", ct.c_float), ("mode", ct.c_int), ("device", ct.c_int), ("rank", ct.c_int),
-                ("world", ct.c_int), ("n_chunks", ct.c_int)]
+                ("world", ct.c_int), ("n_chunks", ct.c_int), ("max_tokens", ct.c_int)]
 
 
 EP_ID_BYTES = 128

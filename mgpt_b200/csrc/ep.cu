@@ -34,6 +34,8 @@ struct Nccl {
     int (*Recv)(void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
     int (*GroupEnd)() = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     bool ok = false;
 };
@@ -55,6 +57,8 @@ int load_nccl()
     MGPT_SYM(Recv, "ncclRecv");
     MGPT_SYM(GroupStart, "ncclGroupStart");
     MGPT_SYM(GroupEnd, "ncclGroupEnd");
+    MGPT_SYM(AllGather, "ncclAllGather");
+    MGPT_SYM(AllReduce, "ncclAllReduce");
     MGPT_SYM(GetErrorString, "ncclGetErrorString");
 #undef MGPT_SYM
     g_nccl.ok = true;
@@ -72,6 +76,8 @@ int nccl_fail(int rc, const char* what)
     } while (0)
 
 constexpr int NCCL_BYTES = 0;      // ncclInt8: every message is sent as bytes
+constexpr int NCCL_INT32 = 2, NCCL_SUM = 0;
+constexpr int IPC_BYTES = 64;      // cudaIpcMemHandle_t
 
 inline int pad128(int v) { return (v + ROW_TILE - 1) / ROW_TILE * ROW_TILE; }
 
@@ -117,6 +123,16 @@ struct mgpt_moe_ep {
     std::vector<int> starts, n_recv;                          // first send row / received rows of a chunk
     int n_send = 0, last_n = 0, last_io = 0;
     bool fwd_done = false;
+    // copy-engine transport (cfg.max_tokens > 0): four buffers of this rank that the peers read (rows routed here,
+    // expert outputs, and their gradient mirrors), the peers' mappings of theirs, local landing buffers
+    bool peer = false;
+    size_t cap_send = 0, cap_recv = 0;            // rows
+    void* pb[4] = {nullptr, nullptr, nullptr, nullptr};       // A rows, B outputs, Cg row gradients, D input gradients
+    std::vector<void*> peer_ptr[4];               // [rank] -> that rank's buffer as mapped here (own: pb[i])
+    DevBuf recv_all, drecv_all, every, flag;
+    int32_t* h_every = nullptr;                   // pinned [G][E]: every rank's counts
+    std::vector<int> blk, send_off, recv_off;     // [s][d][c] rows; [s][c][d] first row in s's send layout; [d][c][s] in d's receive layout
+    std::vector<int> recv_base;                   // [c] first row of chunk c in this rank's receive layout
 };
 
 namespace {
@@ -151,11 +167,219 @@ int follow(mgpt_moe_ep* ep, cudaStream_t st)
     return 0;
 }
 
+// every rank's kernels enqueued on `st` so far are complete on every rank before what is enqueued on `st` afterwards
+int barrier_on(mgpt_moe_ep* ep, cudaStream_t st)
+{
+    MGPT_NCCL(g_nccl.AllReduce(ep->flag.p, ep->flag.p, 1, NCCL_INT32, NCCL_SUM, ep->comm, st));
+    return 0;
+}
+
+// this rank's blocks of chunk c, pulled from the producers' buffers `which` into `dst` (receive layout) -- or, with
+// back = true, this rank's rows of chunk c pulled back from the owners' buffers into `dst` (send layout)
+int pull_chunk(mgpt_moe_ep* ep, int which, char* dst, int c, bool back)
+{
+    const int G = ep->G, nc = ep->nc, me = ep->rank;
+    const size_t rb = (size_t)ep->C * ep->act;
+    for (int i = 0; i < G; ++i) {
+        const int o = (me + i) % G;                  // every rank starts at a different peer
+        size_t d_row, s_row, rows;
+        if (!back) {
+            rows = ep->blk[((size_t)o * G + me) * nc + c];
+            d_row = ep->recv_off[((size_t)me * nc + c) * G + o];
+            s_row = ep->send_off[((size_t)o * nc + c) * G + me];
+        } else {
+            rows = ep->blk[((size_t)me * G + o) * nc + c];
+            d_row = ep->send_off[((size_t)me * nc + c) * G + o];
+            s_row = ep->recv_off[((size_t)o * nc + c) * G + me];
+        }
+        if (rows)
+            MGPT_CUDA(cudaMemcpyAsync(dst + d_row * rb, (const char*)ep->peer_ptr[which][o] + s_row * rb, rows * rb,
+                                      cudaMemcpyDeviceToDevice, ep->cs));
+    }
+    return 0;
+}
+
 int sum(const std::vector<int>& v)
 {
     int s = 0;
     for (int x : v) s += x;
     return s;
+}
+
+}  // namespace
+
+namespace {
+
+// Allocates the peer-readable buffers, all-gathers their IPC handles over NCCL and maps the peers' buffers.
+int setup_peer(mgpt_moe_ep* ep)
+{
+    const int G = ep->G;
+    const size_t rb = (size_t)ep->C * ep->act;
+    size_t off = 0, nb = 0;
+    MGPT_TRY(mgpt_moe_workspace_view(ep->home, ep->cfg.max_tokens, "row_src", &off, &nb));
+    ep->cap_send = nb / sizeof(int32_t);
+    ep->cap_recv = (size_t)G * ep->cap_send;       // worst case: every rank routes all of its rows here
+    const size_t bytes[4] = {ep->cap_send * rb, ep->cap_recv * rb, ep->cap_send * rb, ep->cap_recv * rb};
+    std::vector<char> mine(4 * IPC_BYTES), all((size_t)G * 4 * IPC_BYTES);
+    for (int i = 0; i < 4; ++i) {
+        MGPT_CUDA(cudaMalloc(&ep->pb[i], bytes[i]));
+        cudaIpcMemHandle_t h;
+        MGPT_CUDA(cudaIpcGetMemHandle(&h, ep->pb[i]));
+        static_assert(sizeof(h) == IPC_BYTES, "handle size");
+        memcpy(mine.data() + i * IPC_BYTES, &h, IPC_BYTES);
+    }
+    DevBuf d_mine, d_all;
+    MGPT_TRY(d_mine.ensure(mine.size()));
+    MGPT_TRY(d_all.ensure(all.size()));
+    MGPT_CUDA(cudaMemcpyAsync(d_mine.p, mine.data(), mine.size(), cudaMemcpyHostToDevice, ep->cs));
+    int nrc = g_nccl.AllGather(d_mine.p, d_all.p, mine.size(), NCCL_BYTES, ep->comm, ep->cs);
+    if (nrc == 0) {
+        cudaMemcpyAsync(all.data(), d_all.p, all.size(), cudaMemcpyDeviceToHost, ep->cs);
+        cudaStreamSynchronize(ep->cs);
+    }
+    d_mine.release();
+    d_all.release();
+    if (nrc != 0) return nccl_fail(nrc, "ncclAllGather(handles)");
+    for (int i = 0; i < 4; ++i) {
+        ep->peer_ptr[i].assign(G, nullptr);
+        for (int g = 0; g < G; ++g) {
+            if (g == ep->rank) {
+                ep->peer_ptr[i][g] = ep->pb[i];
+                continue;
+            }
+            cudaIpcMemHandle_t h;
+            memcpy(&h, all.data() + ((size_t)g * 4 + i) * IPC_BYTES, IPC_BYTES);
+            MGPT_CUDA(cudaIpcOpenMemHandle(&ep->peer_ptr[i][g], h, cudaIpcMemLazyEnablePeerAccess));
+        }
+    }
+    MGPT_TRY(ep->recv_all.ensure(ep->cap_recv * rb));
+    MGPT_TRY(ep->drecv_all.ensure(ep->cap_recv * rb));
+    MGPT_TRY(ep->rows_back.ensure(ep->cap_send * rb));
+    MGPT_TRY(ep->d_back.ensure(ep->cap_send * rb));
+    MGPT_TRY(ep->every.ensure((size_t)G * ep->E * sizeof(int32_t)));
+    MGPT_TRY(ep->flag.ensure(256));
+    MGPT_CUDA(cudaMemsetAsync(ep->flag.p, 0, 256, ep->cs));
+    MGPT_CUDA(cudaHostAlloc(&ep->h_every, (size_t)G * ep->E * sizeof(int32_t), cudaHostAllocDefault));
+    MGPT_CUDA(cudaStreamSynchronize(ep->cs));
+    ep->blk.assign((size_t)G * G * ep->nc, 0);
+    ep->send_off.assign((size_t)G * ep->nc * G, 0);
+    ep->recv_off.assign((size_t)G * ep->nc * G, 0);
+    ep->recv_base.assign(ep->nc, 0);
+    ep->peer = true;
+    return 0;
+}
+
+// forward with the copy-engine transport (see mgpt_moe_ep_config::max_tokens)
+int forward_peer(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, int io, mgpt_stream_t stream)
+{
+    cudaStream_t st = (cudaStream_t)stream;
+    const int G = ep->G, nc = ep->nc, Ec = ep->E_chunk, E = ep->E, me = ep->rank;
+    const size_t rb = (size_t)ep->C * ep->act;
+    if (n_tokens > ep->cfg.max_tokens) return fail(MGPT_MOE_EINVAL, "n_tokens exceeds the max_tokens the layer was created with");
+    const size_t home_bytes = mgpt_moe_stage_workspace_bytes(ep->home, n_tokens, 1);
+    MGPT_TRY(ep->home_ws.ensure(home_bytes));
+    MGPT_TRY(mgpt_moe_route_plan(ep->home, x, n_tokens, io, ep->home_ws.p, ep->home_ws.bytes, stream));
+    size_t off = 0, nb = 0;
+    MGPT_TRY(mgpt_moe_workspace_view(ep->home, n_tokens, "counts", &off, &nb));
+    const int32_t* d_counts = (const int32_t*)((char*)ep->home_ws.p + off);
+    // every rank's counts to every rank (global expert order = chunk, owner, j), while the rows are permuted
+    MGPT_TRY(follow(ep, st));
+    MGPT_TRY(mgpt_moe_route_rows(ep->home, x, io, ep->home_ws.p, ep->home_ws.bytes, ep->pb[0], stream));
+    MGPT_NCCL(g_nccl.AllGather(d_counts, ep->every.p, (size_t)E * sizeof(int32_t), NCCL_BYTES, ep->comm, ep->cs));
+    MGPT_CUDA(cudaMemcpyAsync(ep->h_every, ep->every.p, (size_t)G * E * sizeof(int32_t), cudaMemcpyDeviceToHost, ep->cs));
+    MGPT_CUDA(cudaStreamSynchronize(ep->cs));               // the one host synchronisation: how many rows go where
+    auto M = [&](int s, int c, int d, int j) { return ep->h_every[(size_t)s * E + (c * G + d) * Ec + j]; };
+    for (int s = 0; s < G; ++s)
+        for (int d = 0; d < G; ++d)
+            for (int c = 0; c < nc; ++c) {
+                int rows = 0;
+                for (int j = 0; j < Ec; ++j) rows += pad128(M(s, c, d, j));
+                ep->blk[((size_t)s * G + d) * nc + c] = rows;
+            }
+    for (int r = 0; r < G; ++r) {
+        int so = 0, ro = 0;
+        for (int c = 0; c < nc; ++c)
+            for (int o = 0; o < G; ++o) {
+                ep->send_off[((size_t)r * nc + c) * G + o] = so;
+                so += ep->blk[((size_t)r * G + o) * nc + c];
+                ep->recv_off[((size_t)r * nc + c) * G + o] = ro;
+                ro += ep->blk[((size_t)o * G + r) * nc + c];
+            }
+    }
+    ep->n_send = 0;
+    for (int c = 0; c < nc; ++c) {
+        ep->starts[c] = ep->send_off[((size_t)me * nc + c) * G];
+        ep->recv_base[c] = ep->recv_off[((size_t)me * nc + c) * G];
+        ep->n_recv[c] = 0;
+        for (int o = 0; o < G; ++o) {
+            ep->n_recv[c] += ep->blk[((size_t)o * G + me) * nc + c];
+            ep->n_send += ep->blk[((size_t)me * G + o) * nc + c];
+            for (int j = 0; j < Ec; ++j) ep->h_recv[(o * nc + c) * Ec + j] = M(o, c, me, j);
+        }
+    }
+    for (int c = 0; c < nc; ++c) {
+        MGPT_TRY(ep->local_ws[c].ensure(mgpt_moe_stage_workspace_bytes(ep->locals[c], ep->n_recv[c], 0)));
+        MGPT_TRY(ep->seg_counts[c].ensure((size_t)G * Ec * sizeof(int32_t)));
+        // real counts per (source, local expert of chunk c): column block (c, me) of every source's row of counts
+        MGPT_CUDA(cudaMemcpy2DAsync(ep->seg_counts[c].p, Ec * sizeof(int32_t), (const int32_t*)ep->every.p + (c * G + me) * Ec,
+                                    (size_t)E * sizeof(int32_t), Ec * sizeof(int32_t), G, cudaMemcpyDeviceToDevice, ep->cs));
+    }
+    // the permuted rows of every rank are complete: route_rows was enqueued after the all-gather's snapshot of the
+    // compute stream, so it gets a barrier of its own (the compute stream is idle here, the barrier starts at once)
+    MGPT_TRY(follow(ep, st));
+    MGPT_TRY(barrier_on(ep, ep->cs));
+    for (int c = 0; c < nc; ++c) {
+        MGPT_TRY(pull_chunk(ep, 0, (char*)ep->recv_all.p, c, false));
+        MGPT_CUDA(cudaEventRecord(ep->ev_in[c], ep->cs));
+    }
+    for (int c = 0; c < nc; ++c) {
+        char* in = (char*)ep->recv_all.p + (size_t)ep->recv_base[c] * rb;
+        char* out = (char*)ep->pb[1] + (size_t)ep->recv_base[c] * rb;
+        MGPT_CUDA(cudaStreamWaitEvent(st, ep->ev_in[c], 0));
+        MGPT_TRY(mgpt_moe_experts_forward(ep->locals[c], in, (const int32_t*)ep->seg_counts[c].p, G, ep->n_recv[c], out,
+                                          ep->local_ws[c].p, ep->local_ws[c].bytes, stream));
+        // barrier in the order of the compute stream (beside it, its kernel would wait for the next persistent
+        // kernel to end), then the copies it releases run beside the next chunk's products
+        MGPT_TRY(barrier_on(ep, st));
+        MGPT_CUDA(cudaEventRecord(ep->ev_out[c], st));
+        MGPT_CUDA(cudaStreamWaitEvent(ep->cs, ep->ev_out[c], 0));
+        MGPT_TRY(pull_chunk(ep, 1, (char*)ep->rows_back.p, c, true));
+        MGPT_CUDA(cudaEventRecord(ep->ev_back[c], ep->cs));
+    }
+    MGPT_CUDA(cudaStreamWaitEvent(st, ep->ev_back[nc - 1], 0));
+    MGPT_TRY(mgpt_moe_combine(ep->home, ep->rows_back.p, y, io, ep->home_ws.p, ep->home_ws.bytes, stream));
+    ep->last_n = n_tokens;
+    ep->last_io = io;
+    ep->fwd_done = true;
+    return 0;
+}
+
+int backward_peer(mgpt_moe_ep* ep, const void* x, const void* dy, void* dx, int io, mgpt_stream_t stream)
+{
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nc = ep->nc;
+    const size_t rb = (size_t)ep->C * ep->act;
+    MGPT_TRY(mgpt_moe_combine_backward(ep->home, ep->rows_back.p, dy, io, ep->pb[2], ep->home_ws.p, ep->home_ws.bytes, stream));
+    MGPT_TRY(barrier_on(ep, st));                    // every rank's row gradients are written
+    MGPT_TRY(follow(ep, st));
+    for (int c = 0; c < nc; ++c) {
+        MGPT_TRY(pull_chunk(ep, 2, (char*)ep->drecv_all.p, c, false));
+        MGPT_CUDA(cudaEventRecord(ep->ev_in[c], ep->cs));
+    }
+    for (int c = 0; c < nc; ++c) {
+        char* d_out = (char*)ep->drecv_all.p + (size_t)ep->recv_base[c] * rb;
+        char* d_in = (char*)ep->pb[3] + (size_t)ep->recv_base[c] * rb;
+        MGPT_CUDA(cudaStreamWaitEvent(st, ep->ev_in[c], 0));
+        MGPT_TRY(mgpt_moe_experts_backward_rows(ep->locals[c], d_out, d_in, ep->local_ws[c].p, ep->local_ws[c].bytes, stream));
+        MGPT_TRY(barrier_on(ep, st));
+        MGPT_CUDA(cudaEventRecord(ep->ev_out[c], st));
+        MGPT_CUDA(cudaStreamWaitEvent(ep->cs, ep->ev_out[c], 0));
+        MGPT_TRY(pull_chunk(ep, 3, (char*)ep->d_back.p, c, true));
+        MGPT_CUDA(cudaEventRecord(ep->ev_back[c], ep->cs));
+        MGPT_TRY(mgpt_moe_experts_backward_params(ep->locals[c], d_out, d_in, ep->local_ws[c].p, ep->local_ws[c].bytes, stream));
+    }
+    MGPT_CUDA(cudaStreamWaitEvent(st, ep->ev_back[nc - 1], 0));
+    return mgpt_moe_route_backward(ep->home, x, ep->d_back.p, dx, io, ep->home_ws.p, ep->home_ws.bytes, stream);
 }
 
 }  // namespace
@@ -183,6 +407,19 @@ void mgpt_moe_ep_destroy(mgpt_moe_ep* ep)
     for (DevBuf* b : {&ep->home_ws, &ep->rows, &ep->rows_back, &ep->d_rows, &ep->d_back, &ep->recv_counts}) b->release();
     for (auto* v : {&ep->recv_rows, &ep->out_rows, &ep->d_recv, &ep->d_in, &ep->local_ws, &ep->seg_counts})
         for (auto& b : *v) b.release();
+    for (int i = 0; i < 4; ++i) {
+        for (int g = 0; g < (int)ep->peer_ptr[i].size(); ++g)
+            if (g != ep->rank && ep->peer_ptr[i][g]) cudaIpcCloseMemHandle(ep->peer_ptr[i][g]);
+    }
+    if (ep->peer && ep->comm && g_nccl.AllReduce && ep->flag.p) {
+        // every rank has closed its mappings before any rank frees what they pointed at
+        g_nccl.AllReduce(ep->flag.p, ep->flag.p, 1, NCCL_INT32, NCCL_SUM, ep->comm, ep->cs);
+        cudaStreamSynchronize(ep->cs);
+    }
+    for (int i = 0; i < 4; ++i)
+        if (ep->pb[i]) cudaFree(ep->pb[i]);
+    for (DevBuf* b : {&ep->recv_all, &ep->drecv_all, &ep->every, &ep->flag}) b->release();
+    if (ep->h_every) cudaFreeHost(ep->h_every);
     if (ep->h_counts) cudaFreeHost(ep->h_counts);
     if (ep->h_recv) cudaFreeHost(ep->h_recv);
     for (auto* v : {&ep->ev_in, &ep->ev_out, &ep->ev_back})
@@ -254,6 +491,10 @@ int mgpt_moe_ep_create(const mgpt_moe_ep_config* cfg, const void* id, mgpt_moe_e
         int nrc = g_nccl.CommInitRank(&ep->comm, G, uid, cfg->rank);
         if (nrc != 0) return bail(nccl_fail(nrc, "ncclCommInitRank"));
     }
+    if (G > 1 && cfg->max_tokens > 0) {
+        rc = setup_peer(ep);
+        if (rc) return bail(rc);
+    }
     *out = ep;
     return 0;
 }
@@ -324,6 +565,7 @@ int mgpt_moe_ep_forward(mgpt_moe_ep* ep, const void* x, void* y, int n_tokens, i
     const int G = ep->G, nc = ep->nc, Ec = ep->E_chunk;
     const size_t rb = (size_t)ep->C * ep->act;
     ep->fwd_done = false;
+    if (ep->peer) return forward_peer(ep, x, y, n_tokens, io, stream);
 
     // routing side: router, plan, rows in the padded expert-major layout (experts in global order = chunk, rank, j)
     const size_t home_bytes = mgpt_moe_stage_workspace_bytes(ep->home, n_tokens, 1);
@@ -420,6 +662,7 @@ int mgpt_moe_ep_backward(mgpt_moe_ep* ep, const void* x, const void* dy, void* d
     cudaStream_t st = (cudaStream_t)stream;
     const int nc = ep->nc;
     const size_t rb = (size_t)ep->C * ep->act;
+    if (ep->peer) return backward_peer(ep, x, dy, dx, io, stream);
     MGPT_TRY(ep->d_rows.ensure(ep->rows.bytes));
     MGPT_TRY(ep->d_back.ensure(ep->rows.bytes));
     for (int c = 0; c < nc; ++c) {

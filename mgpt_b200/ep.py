@@ -658,7 +658,9 @@ class NativeExpertParallelMoE:
     binds.  torch is used here for device memory and, in ``create_id``, to hand rank 0's NCCL id to the other ranks."""
 
     def __init__(self, embed_dim, hidden_dim, num_experts, top_k, *, rank=0, world=1, nccl_id=None, mode="bf16",
-                 device=0, lb_alpha=0.01, n_chunks=1):
+                 device=0, lb_alpha=0.01, n_chunks=1, max_tokens=0):
+        """``max_tokens`` > 0 (one node, peer access): rows are pulled by copy engines from peer-readable buffers
+        sized for that many tokens per call (``mgpt_moe_ep_config::max_tokens``); 0: NCCL point-to-point."""
         from . import _lib
         self._lib_mod = _lib
         self.lib = _lib.load()
@@ -668,7 +670,8 @@ class NativeExpertParallelMoE:
         self.E_local = num_experts // world
         self.device = torch.device("cuda", device)
         m = {"fp32": _lib.FP32, "bf16": _lib.BF16}[mode]
-        cfg = _lib.EpConfig(embed_dim, hidden_dim, num_experts, top_k, lb_alpha, m, device, rank, world, n_chunks)
+        cfg = _lib.EpConfig(embed_dim, hidden_dim, num_experts, top_k, lb_alpha, m, device, rank, world, n_chunks,
+                            int(max_tokens))
         self._h = ct.c_void_p()
         idbuf = (ct.c_char * _lib.EP_ID_BYTES).from_buffer_copy(nccl_id) if nccl_id is not None else None
         _lib.check(self.lib.mgpt_moe_ep_create(ct.byref(cfg), idbuf, ct.byref(self._h)))

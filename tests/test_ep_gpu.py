@@ -41,10 +41,10 @@ def test_stage_entry_points_one_gpu(mode, tol, chunks):
     assert torch.isfinite(y2.float()).all()
 
 
-def _native(mode, rank, world, chunks=1, nccl_id=None):
+def _native(mode, rank, world, chunks=1, nccl_id=None, max_tokens=0):
     from mgpt_b200.ep import NativeExpertParallelMoE
     return lambda w: NativeExpertParallelMoE(w.C, w.H, w.E, w.k, rank=rank, world=world, nccl_id=nccl_id, mode=mode,
-                                             device=rank, lb_alpha=w.alpha, n_chunks=chunks)
+                                             device=rank, lb_alpha=w.alpha, n_chunks=chunks, max_tokens=max_tokens)
 
 
 @pytest.mark.parametrize("chunks", [1, 2])
@@ -86,10 +86,18 @@ def _worker(rank, world, port, q):
             layer.close_peer()
         # the same through the C ABI alone (the library's own NCCL communicator and exchange stream)
         from mgpt_b200.ep import NativeExpertParallelMoE
-        for chunks in (1, 2):
+        for chunks, max_tokens in ((1, 0), (2, 0), (1, 2048), (2, 2048)):      # NCCL rows; rows pulled by copy engines
             nid = NativeExpertParallelMoE.create_id()
             layer = run_rank(w, rank, world, None, f"cuda:{rank}", 2e-2, io=torch.bfloat16,
-                             make_layer=_native("bf16", rank, world, chunks, nid))
+                             make_layer=_native("bf16", rank, world, chunks, nid, max_tokens))
+            if max_tokens:
+                # a second step through the same buffers with fewer tokens; one with too many is refused
+                xs = torch.ones(96, w.C, dtype=torch.bfloat16, device=f"cuda:{rank}")
+                y1 = layer.forward(xs)
+                dx1 = layer.backward(xs)
+                assert torch.isfinite(y1.float()).all() and torch.isfinite(dx1.float()).all()
+                with pytest.raises(Exception):
+                    layer.forward(torch.ones(max_tokens + 1, w.C, dtype=torch.bfloat16, device=f"cuda:{rank}"))
             layer.check_status()
             layer.close()
         dist.barrier()
