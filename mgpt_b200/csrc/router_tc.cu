@@ -31,7 +31,7 @@ namespace {
 using namespace tcx;
 
 constexpr int RT_BM = 128, RT_BK = 64;
-constexpr int RT_THREADS = 64 + 128;              // warp 0: TMA, warp 1: MMA, warps 2-5: row norms + epilogue
+constexpr int RT_THREADS = 64 + 128 + 128;        // warp 0: TMA, warp 1: MMA, warps 2-5: row norms, warps 6-9: epilogue
 constexpr uint32_t RT_A_BYTES = RT_BM * RT_BK * 2;
 constexpr uint32_t RT_TMEM_COLS = 256;            // two accumulators of up to 128 columns
 
@@ -39,7 +39,7 @@ template <int NE> struct RtCfg {
     static constexpr uint32_t B_BYTES = 2u * NE * RT_BK * 2;     // hi and mid pieces
     static constexpr uint32_t STAGE = RT_A_BYTES + B_BYTES;
     static constexpr int STAGES = (int)((196608u) / STAGE) > 8 ? 8 : (int)((196608u) / STAGE);
-    static constexpr uint32_t SMEM = STAGES * STAGE + 1024 + 256;
+    static constexpr uint32_t SMEM = STAGES * STAGE + 1024 + 256 + 1024;     // tiles, alignment slack, barriers, row norms
 };
 
 struct RtP {
@@ -74,6 +74,8 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
     auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
     const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+    auto norm_full = [&](int b) { return bars + 8u * (2 * STAGES + 5 + b); };
+    float* norm_s = reinterpret_cast<float*>(tiles + STAGES * Cfg::STAGE + 256);      // [2][128]: sum of squares per row
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -83,6 +85,7 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full(b), 1);
             mbar_init(acc_empty(b), 4);
+            mbar_init(norm_full(b), 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -142,16 +145,16 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 if (ok) umma_commit(acc_full(buf));
             }
         }
-    } else {
-        const int q = warp & 3;                   // TMEM lane quarter of this warp
-        const int row = q * 32 + lane;
-        const float wmax = p.rstat[0], bmax = p.rstat[1];
+    } else if (warp < 6) {
+        // Row norms: ||x_row||^2 from the tiles the tensor core reads (16-byte pieces of a row are permuted by the
+        // 128-byte swizzle, which a sum of squares does not mind; lane l starts at piece l so a quarter warp covers all
+        // banks).  Warps of their own: the epilogue of a tile takes about as long as the loads of the next one, and
+        // while these warps did both, no stage was released during an epilogue and the ring stood still.
+        const int row = (warp & 3) * 32 + lane;
         uint32_t it = 0, t = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.n_tiles; tile += gridDim.x, ++t) {
             const uint32_t buf = t & 1u;
-            // ||x_row||^2 from the tiles the tensor core reads (16-byte pieces of a row are permuted by the 128-byte
-            // swizzle, which a sum of squares does not mind; lane l starts at piece l so a quarter warp covers all banks)
             float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};          // independent chains: one warp per scheduler hides no latency
             for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
@@ -177,8 +180,23 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 if (lane == 0) mbar_arrive(empty(s));
             }
             if (!ok) break;
+            // the epilogue has read this buffer's norms of two tiles ago (it arrives on acc_empty after reading them)
+            if (t >= 2 && !mbar_wait(acc_empty(buf), ((t >> 1) - 1) & 1, p.status, ERR_ACC_WAIT)) break;
+            norm_s[buf * 128 + row] = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(norm_full(buf));
+        }
+    } else {
+        const int q = warp & 3;                   // TMEM lane quarter of this warp
+        const int row = q * 32 + lane;
+        const float wmax = p.rstat[0], bmax = p.rstat[1];
+        uint32_t t = 0;
+        for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++t) {
+            const uint32_t buf = t & 1u;
             if (!mbar_wait(acc_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
+            if (!mbar_wait(norm_full(buf), (t >> 1) & 1, p.status, ERR_ACC_WAIT)) break;
             tc_fence_after();
+            const float ss = norm_s[buf * 128 + row];
             const uint32_t t_lane = tmem_base + buf * 128 + ((uint32_t)(q * 32) << 16);
             constexpr int NLD = NE < 32 ? 1 : NE / 32;
             float lg[NLD * 32];
@@ -199,7 +217,6 @@ tc_router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
             const bool live = tok < p.N;
             // error bound of this token's logits against the reference's, and the margin that makes an order final
             const float u = 5.9604645e-8f;
-            const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
             const float xn = sqrtf(ss) * 1.001f;
             const float bound = (1.5f * (float)p.C * u + 1.52587890625e-5f) * xn * wmax * 1.01f + 4.0f * u * (xn * wmax + bmax);
             const float tau = 2.0f * bound;
