@@ -251,6 +251,26 @@ class _RawCuda:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+def peer_offsets(counts):
+    """counts[source, destination, chunk, j]: real rows that `source` routes to local expert j of chunk `chunk` on
+    `destination`.  Returns (blk[source, destination, chunk] padded rows of the block, send_off[source, chunk,
+    destination] its first row in the source's send layout ([chunk][destination] blocks back to back),
+    recv_off[destination, chunk, source] its first row in the destination's receive layout ([chunk][source])).
+    Every expert's segment is padded to a multiple of 128 rows."""
+    import numpy as np
+    M = np.asarray(counts).astype(np.int64)
+    G, nc = M.shape[0], M.shape[2]
+    blk = ((M + 127) // 128 * 128).sum(3)
+    send_off = np.zeros((G, nc, G), dtype=np.int64)
+    recv_off = np.zeros((G, nc, G), dtype=np.int64)
+    for r in range(G):
+        a = blk[r].T.reshape(-1)                       # [chunk][destination] of source r
+        send_off[r] = (np.cumsum(a) - a).reshape(nc, G)
+        b = blk[:, r, :].T.reshape(-1)                 # [chunk][source] into destination r
+        recv_off[r] = (np.cumsum(b) - b).reshape(nc, G)
+    return blk, send_off, recv_off
+
+
 class _CopyLanes:
     """A few streams used as one for copy-engine transfers: blocks from different peers go out on different lanes
     (one copy at a time does not fill the NVLink ports when the blocks are small), waits and records apply to all."""
@@ -473,15 +493,7 @@ class ExpertParallelMoE:
         send_counts = counts.view(nc, G, Ec).permute(1, 0, 2).contiguous()             # [destination, chunk, j]
         every = torch.empty((G,) + tuple(send_counts.shape), dtype=send_counts.dtype, device=send_counts.device)
         dist.all_gather_into_tensor(every, send_counts, group=self.group)               # [source, destination, chunk, j]
-        M = every.cpu().numpy().astype(np.int64)
-        blk = ((M + 127) // 128 * 128).sum(3)                                           # [source, destination, chunk]
-        send_off = np.zeros((G, nc, G), dtype=np.int64)                                 # [source][chunk][destination]
-        recv_off = np.zeros((G, nc, G), dtype=np.int64)                                 # [destination][chunk][source]
-        for r in range(G):
-            a = blk[r].T.reshape(-1)                                                    # [chunk][destination] of source r
-            send_off[r] = (np.cumsum(a) - a).reshape(nc, G)
-            b = blk[:, r, :].T.reshape(-1)                                              # [chunk][source] into destination r
-            recv_off[r] = (np.cumsum(b) - b).reshape(nc, G)
+        blk, send_off, recv_off = peer_offsets(every.cpu().numpy())
         return every, blk, send_off, recv_off
 
     def _forward_peer(self, x):

@@ -138,3 +138,35 @@ def test_a_rank_that_never_posts_its_counts_times_the_others_out():
     res = _spawn(_absent_worker, 2, (), timeout=60)
     assert res[1] == "absent"
     assert res[0].startswith("error after") and "expert calls 0" in res[0], res[0]
+
+
+def test_peer_offsets_reproduce_the_all_to_all():
+    """The copy-engine transport pulls block (source -> destination, chunk) from the source's send layout into the
+    destination's receive layout; the offsets both sides derive from the all-gathered counts must describe the
+    same blocks an all-to-all with those split sizes would deliver, back to back and without overlap."""
+    import numpy as np
+    from mgpt_b200.ep import peer_offsets
+    rng = np.random.default_rng(5)
+    for G, nc, Ec in ((2, 1, 4), (4, 2, 2), (8, 2, 1), (3, 3, 2)):
+        counts = rng.integers(0, 700, size=(G, G, nc, Ec))
+        counts[rng.random(counts.shape) < 0.3] = 0                       # experts nobody routes to
+        blk, send_off, recv_off = peer_offsets(counts)
+        pad = (counts + 127) // 128 * 128
+        assert np.array_equal(blk, pad.sum(3))
+        # every rank's send buffer: rows labelled (source, running row index)
+        send = [np.arange(int(blk[s].sum())) + 1_000_000 * s for s in range(G)]
+        for d in range(G):
+            recv = np.full(int(blk[:, d].sum()), -1, dtype=np.int64)
+            for c in range(nc):
+                for s in range(G):
+                    n, so, ro = int(blk[s, d, c]), int(send_off[s, c, d]), int(recv_off[d, c, s])
+                    assert (recv[ro: ro + n] == -1).all()                 # no two blocks land on the same rows
+                    recv[ro: ro + n] = send[s][so: so + n]
+            assert (recv >= 0).all()                                      # and together they fill the layout
+            # what all_to_all_single with these split sizes delivers, chunk by chunk: source-major blocks
+            want = []
+            for c in range(nc):
+                for s in range(G):
+                    start = int(blk[s].T.reshape(-1)[: c * G + d].sum())  # [chunk][destination] order on the source
+                    want.append(send[s][start: start + int(blk[s, d, c])])
+            assert np.array_equal(recv, np.concatenate(want))
