@@ -727,11 +727,27 @@ def run_ours(args, w):
             ep_phases = {k: round(v, 3) for k, v in layer.phase_ms().items()}
             layer.phase_events = None
             layer.stages.check_status()
+        counts_native = None
+        if native:
+            # what every rank received from rank 0, per local expert: together, rank 0's counts over all experts
+            try:
+                mine = layer.last_recv_counts[0].to(dev)
+                gathered = torch.empty(world * mine.numel(), dtype=mine.dtype, device=dev)
+                dist.all_gather_into_tensor(gathered, mine)
+                gathered = gathered.view(world, -1).cpu().tolist()
+                Ec = E_local // chunks
+                counts_native = [0] * w.E
+                for r in range(world):
+                    for l in range(E_local):
+                        c, j = divmod(l, Ec)
+                        counts_native[c * (w.E // chunks) + r * Ec + j] = int(gathered[r][l])
+            except Exception:
+                counts_native = None
         if rank == 0 and single is not None:
             # rank 0's tokens through the expert-parallel layer against the same tokens through the one-GPU layer
             # (same weights; the load-balance term uses this rank's own counts in both)
-            if native:      # rows received per local expert, summed over the sources = this rank's experts' global counts
-                counts_ep = None
+            if native:
+                counts_ep = counts_native
             else:
                 counts_ep = layer.stages.routing_view("counts", torch.int32).cpu().tolist()
             ep_check = {"y_rel_l2": rel_l2(last["y"], single["y"]),
