@@ -581,13 +581,13 @@ def run_ours(args, w):
     ep_check = None
     single = None
 
+    bind_to_gpu_numa_node(local)            # before any pinned allocation: host buffers land next to this rank's GPU
     if world == 1:
         res = single = single_gpu_pass(args, w, rank, dev)
         parallelism = "single GPU"
     else:
         from mgpt_b200.ep import ExpertParallelMoE
 
-        bind_to_gpu_numa_node(local)        # before any pinned allocation: host buffers land next to this rank's GPU
         # NCCL's stream at high priority: an exchange that becomes ready together with a persistent compute kernel is
         # placed first (the compute CTAs that find their SM taken start late and take fewer work items)
         try:
