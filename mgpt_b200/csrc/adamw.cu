@@ -68,7 +68,8 @@ adamw_matrix_kernel(float* const* __restrict__ w_ptrs, const float* const* __res
 #pragma unroll
     for (int i = ty; i < 32; i += 8) {
         const int c = c0 + i, r = r0 + tx;
-        if (r < rows && c < cols) dstT[(size_t)e * rows * cols + (size_t)c * rows + r] = __float2bfloat16(tile[tx][i]);
+        if (r < rows && c < cols)       // the transposed copy [cols, rows] is tile-major (common.cuh)
+            dstT[(size_t)e * tile_major_elems(cols, rows) + tile_major_index(rows, c, r)] = __float2bfloat16(tile[tx][i]);
     }
 }
 

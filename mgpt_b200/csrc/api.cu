@@ -189,12 +189,20 @@ int mgpt_moe_create(const mgpt_moe_config* cfg, mgpt_moe_layer** out)
         }
         const size_t n = (size_t)E * C * H;
         bf16** s[6] = {&L->sWg, &L->sWu, &L->sWd, &L->sWgT, &L->sWuT, &L->sWdT};
-        for (auto p : s) {
-            e = cudaMalloc(p, n * sizeof(bf16));
+        // the transposed copies are tile-major with zero padding up to whole 128 x 64 blocks
+        const size_t ns[6] = {n, n, n, E * tile_major_elems(H, C), E * tile_major_elems(H, C), E * tile_major_elems(C, H)};
+        for (int i = 0; i < 6; ++i) {
+            e = cudaMalloc(s[i], ns[i] * sizeof(bf16));
+            if (e == cudaSuccess && i >= 3) e = cudaMemset(*s[i], 0, ns[i] * sizeof(bf16));
             if (e != cudaSuccess) {
                 mgpt_moe_destroy(L);
                 return cuda_fail(e, "cudaMalloc(shadows)");
             }
+        }
+        e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) {
+            mgpt_moe_destroy(L);
+            return cuda_fail(e, "clearing the weight copies");
         }
     }
     *out = L;

@@ -97,6 +97,21 @@ struct Dims {
 Workspace make_workspace(const Dims& d, int n_tokens, int kind = 0);
 
 // Device-side tables of per-expert pointers (index = expert).
+// The transposed BF16 weight copies (the B operands of the forward products) are stored tile-major: per expert the
+// [rows, cols] matrix is cut into blocks of 128 rows x 64 columns, 16 KiB each and contiguous, ordered [row block]
+// [column block] -- exactly the box one TMA load of a pipeline stage fetches.  A forward-only (decode) batch streams
+// every weight byte from DRAM once; from the row-major copy a box was 128 pieces of 128 bytes at the row pitch.
+// rows and cols are padded up to whole blocks; the padding is zero (allocation is cleared, writers never touch it).
+__host__ __device__ inline size_t tile_major_elems(int rows, int cols)
+{
+    return (size_t)((rows + 127) / 128 * 128) * (size_t)((cols + 63) / 64 * 64);
+}
+__host__ __device__ inline size_t tile_major_index(int cols, int r, int c)
+{
+    const int kb = (cols + 63) / 64;
+    return ((size_t)((r >> 7) * kb + (c >> 6)) * 128 + (r & 127)) * 64 + (c & 63);
+}
+
 struct ExpertPtrs {
     const void** Wg;  const void** Wu;  const void** Wd;     // [C,H],[C,H],[H,C]
     const float** bg; const float** bu; const float** bd;
@@ -129,7 +144,7 @@ struct mgpt_moe_layer {
 
     // BF16 shadows, contiguous over experts (BF16 mode only)
     mgpt::bf16 *sWg = nullptr, *sWu = nullptr, *sWd = nullptr;      // [E][C][H],[E][C][H],[E][H][C]
-    mgpt::bf16 *sWgT = nullptr, *sWuT = nullptr, *sWdT = nullptr;   // [E][H][C],[E][H][C],[E][C][H]
+    mgpt::bf16 *sWgT = nullptr, *sWuT = nullptr, *sWdT = nullptr;   // transposed copies ([H,C],[H,C],[C,H] per expert), tile-major: see tile_major_index
     mgpt::bf16* sWr = nullptr;                                      // router weight [C][E8], E8 = E rounded up to 8
     mgpt::bf16* sWrT2 = nullptr;     // router weight transposed and split in two BF16 pieces: [2][NE][C], Wr^T ~ hi + mid
     float* d_rstat = nullptr;        // {max_e ||Wr[:,e]||_2, max_e |br[e]|}, slightly inflated (screened router's error bound)

@@ -289,6 +289,9 @@ struct RowsP {
     // MODE_DX only: row tiles are token tiles (no experts); the epilogue adds the expert rows of each token
     int fixed_tiles;            // number of 128-token tiles
     int n_valid_rows;           // tokens
+    // MODE_GATEUP / MODE_DOWN: the B operand is a tile-major weight copy (common.cuh): its map is [blocks * 128 rows,
+    // 64 columns]; block (expert e, row block rb, column block kb) starts at row ((e * b_row_blocks + rb) * b_kb + kb) * 128
+    int b_row_blocks, b_kb;
     const bf16* gather_src;     // dXg rows [*, n_out]
     const int32_t* gather_pos;  // [tokens, gather_k] row of dXg for (token, j)
     int gather_k;
@@ -486,8 +489,13 @@ tc_rows_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     const int kx = (second ? kb - p.kblocks : kb) * BK;
                     tma_load_2d(a_dst, second ? &tmA1 : &tmA0, kx, row0, pipe.full(s));
                     if (MODE == MODE_GATEUP) {
-                        tma_load_2d(b_dst, &tmB0, kx, brow, pipe.full(s));
-                        tma_load_2d(b_dst + HALF_B, &tmB1, kx, brow, pipe.full(s));
+                        const int y = ((p.tile_expert[row_tile] * p.b_row_blocks + (n0 >> 7)) * p.b_kb + kb) * 128;
+                        tma_load_2d(b_dst, &tmB0, 0, y, pipe.full(s));
+                        tma_load_2d(b_dst + HALF_B, &tmB1, 0, y, pipe.full(s));
+                    } else if (MODE == MODE_DOWN) {
+                        const int y = ((p.tile_expert[row_tile] * p.b_row_blocks + (n0 >> 7)) * p.b_kb + kb) * 128;
+                        tma_load_2d(b_dst, &tmB0, 0, y, pipe.full(s));
+                        tma_load_2d(b_dst + HALF_B, &tmB0, 0, y + p.b_kb * 128, pipe.full(s));
                     } else {
                         const CUtensorMap* mb = second ? &tmB1 : &tmB0;
                         tma_load_2d(b_dst, mb, kx, brow, pipe.full(s));
@@ -976,9 +984,10 @@ int prepare(mgpt_moe_layer* L, const Workspace& w, char* ws)
     MGPT_TRY(make_map(&s->dYg, dyg, rc, C, 128));
     MGPT_TRY(make_map(&s->dG, ws + w.dG, rc, H, 128));
     MGPT_TRY(make_map(&s->dU, ws + w.dU, rc, H, 128));
-    MGPT_TRY(make_map(&s->WgT, L->sWgT, E * H, C, 128));
-    MGPT_TRY(make_map(&s->WuT, L->sWuT, E * H, C, 128));
-    MGPT_TRY(make_map(&s->WdT, L->sWdT, E * C, H, 128));
+    // tile-major copies: one 16 KiB block per (128 rows, 64 columns), seen as a tall matrix of 64 columns
+    MGPT_TRY(make_map(&s->WgT, L->sWgT, E * tile_major_elems(d.H, d.C) / 64, 64, 128));
+    MGPT_TRY(make_map(&s->WuT, L->sWuT, E * tile_major_elems(d.H, d.C) / 64, 64, 128));
+    MGPT_TRY(make_map(&s->WdT, L->sWdT, E * tile_major_elems(d.C, d.H) / 64, 64, 128));
     MGPT_TRY(make_map(&s->Wg, L->sWg, E * C, H, 128));
     MGPT_TRY(make_map(&s->Wu, L->sWu, E * C, H, 128));
     MGPT_TRY(make_map(&s->Wd, L->sWd, E * H, C, 128));
@@ -1097,6 +1106,7 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     p.status = L->d_status;
     // gate/up + SwiGLU: K = C, 128 hidden units per item
     p.kblocks = cdiv(d.C, BK); p.n_out = d.H; p.b_rows_per_expert = d.H; p.n_col_tiles = cdiv(d.H, BN / 2);
+    p.b_row_blocks = cdiv(d.H, 128); p.b_kb = cdiv(d.C, BK);
     p.bias0 = L->master.bg; p.bias1 = L->master.bu;
     p.G = w.inference ? nullptr : (bf16*)(ws + w.G);
     p.U = w.inference ? nullptr : (bf16*)(ws + w.U);
@@ -1106,6 +1116,7 @@ int tc_experts_forward(mgpt_moe_layer* L, const Workspace& w, char* ws, cudaStre
     L->stage_end(ST_GATEUP, st);
     // down: K = H
     p.kblocks = cdiv(d.H, BK); p.n_out = d.C; p.b_rows_per_expert = d.C; p.n_col_tiles = cdiv(d.C, BN);
+    p.b_row_blocks = cdiv(d.C, 128); p.b_kb = cdiv(d.H, BK);
     p.bias0 = L->master.bd; p.bias1 = nullptr;
     L->stage_begin(ST_DOWN, st);
     p.sched = s->sched + 2;

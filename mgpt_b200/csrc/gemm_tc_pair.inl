@@ -91,7 +91,12 @@ __device__ __forceinline__ bool pair_issue_loads(const PipeP& pipe, const RowsP&
         tma_load_2d_pair(a_dst, second ? tmA1 : tmA0, kx, row0, lead_full);
         if (MODE == MODE_GATEUP) {
             // the 256 accumulator columns are [128 gate | 128 up]: the leader holds the gate rows, the peer the up rows
-            tma_load_2d_pair(b_dst, rank == 0 ? tmB0 : tmB1, kx, brow, lead_full);
+            // (tile-major weight copies: block row of (expert, 128-row block, k-block))
+            const int y = ((w.e * p.b_row_blocks + (w.n0 >> 7)) * p.b_kb + kb) * 128;
+            tma_load_2d_pair(b_dst, rank == 0 ? tmB0 : tmB1, 0, y, lead_full);
+        } else if (MODE == MODE_DOWN) {
+            const int y = ((w.e * p.b_row_blocks + (w.n0 >> 7) + (int)rank) * p.b_kb + kb) * 128;
+            tma_load_2d_pair(b_dst, tmB0, 0, y, lead_full);
         } else {
             tma_load_2d_pair(b_dst, second ? tmB1 : tmB0, kx, brow + (int)rank * (BN / 2), lead_full);
         }

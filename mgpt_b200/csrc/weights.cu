@@ -21,7 +21,7 @@ shadow_kernel(const void* const* __restrict__ src_ptrs, int rows, int cols,
     const int e = blockIdx.z;
     const float* src = (const float*)src_ptrs[e];
     bf16* d = dst + (size_t)e * rows * cols;
-    bf16* dT = dstT + (size_t)e * rows * cols;
+    bf16* dT = dstT + (size_t)e * tile_major_elems(cols, rows);       // the transposed matrix is [cols, rows]
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     for (int i = ty; i < 32; i += 8) {
@@ -35,7 +35,7 @@ shadow_kernel(const void* const* __restrict__ src_ptrs, int rows, int cols,
     __syncthreads();
     for (int i = ty; i < 32; i += 8) {
         const int c = c0 + i, r = r0 + tx;
-        if (r < rows && c < cols) dT[(size_t)c * rows + r] = __float2bfloat16(tile[tx][i]);
+        if (r < rows && c < cols) dT[tile_major_index(rows, c, r)] = __float2bfloat16(tile[tx][i]);
     }
 }
 
