@@ -276,14 +276,16 @@ router_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const
 // ahead through registers, which is enough only when a dozen CTAs per SM hide each other's waits).  Same arithmetic:
 // one warp pass per token, lane el owns experts el, el+32, ..., acc = fadd(acc, fmul(x, w)) in channel order.
 // Needs C % 32 == 0, E == 32*EPL and 16-byte aligned x and Wr.
-template <typename TIn, int EPL>
+// TPW tokens per warp: 4 for the list pass (fewer instructions per token), 1 for decode batches without a list
+// (tokens 0..N-1; the shortest chains per lane, so that a handful of CTAs finish soonest).
+template <typename TIn, int EPL, int TPW>
 __global__ void __launch_bounds__(R_WARPS * 32)
 router_list_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, const float* __restrict__ br,
-                   int C, int E, int k, float* __restrict__ logits, float* __restrict__ probs,
+                   int N, int C, int E, int k, float* __restrict__ logits, float* __restrict__ probs,
                    int32_t* __restrict__ top_idx, float* __restrict__ top_p,
                    const int32_t* __restrict__ list, const int32_t* __restrict__ list_count)
 {
-    constexpr int TPW = 4, TOK = R_WARPS * TPW, WCOLS = 32 * EPL, THREADS = R_WARPS * 32;
+    constexpr int TOK = R_WARPS * TPW, WCOLS = 32 * EPL, THREADS = R_WARPS * 32;
     constexpr int ST = EPL <= 2 ? 4 : 2;            // stages: 36 KiB of static shared memory at most
     constexpr int XV = 16 / sizeof(TIn);            // elements per 16-byte piece
     constexpr int XPT = R_CK / XV;                  // pieces per token per chunk
@@ -293,10 +295,10 @@ router_list_kernel(const TIn* __restrict__ x, const float* __restrict__ Wr, cons
     __shared__ int stok[TOK];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n_active = *list_count;
+    const int n_active = list ? *list_count : N;
     const int tok0 = blockIdx.x * TOK;
     if (tok0 >= n_active) return;
-    for (int i = tid; i < TOK; i += THREADS) stok[i] = tok0 + i < n_active ? list[tok0 + i] : -1;
+    for (int i = tid; i < TOK; i += THREADS) stok[i] = tok0 + i < n_active ? (list ? list[tok0 + i] : tok0 + i) : -1;
     __syncthreads();
 
     auto issue = [&](int ci, int buf) {
@@ -646,6 +648,16 @@ int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, i
 {
     // Decode-sized batches: too few tokens to fill the device, what is left is the latency of one CTA, which is the
     // length of its dependent addition chains: one token per warp pass keeps it shortest.
+    if (!list && N <= 1024 && C % R_CK == 0 && E % 32 == 0 && E <= 128 && E != 96 && ((uintptr_t)x & 15) == 0 &&
+        ((uintptr_t)Wr & 15) == 0) {
+        // the chunks through the cp.async ring: with a handful of CTAs, nothing else hides the loads of a chunk
+        const int grid = (N + R_WARPS - 1) / R_WARPS;
+        if (E == 32) router_list_kernel<TIn, 1, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, nullptr, nullptr);
+        else if (E == 64) router_list_kernel<TIn, 2, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, nullptr, nullptr);
+        else router_list_kernel<TIn, 4, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, nullptr, nullptr);
+        MGPT_LAUNCHED("router_list_kernel<decode>");
+        return 0;
+    }
     if (!list && N <= 1024) {
         if (E <= 8) return router_fwd_launch<TIn, 8, 1, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
         if (E <= 16) return router_fwd_launch<TIn, 16, 1, 1>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, st, list, list_count);
@@ -657,9 +669,9 @@ int router_fwd_dispatch(const TIn* x, const float* Wr, const float* br, int N, i
     // CTAs (16 tokens) so that the few thousand listed tokens still spread over every SM.
     if (list && C % R_CK == 0 && E % 32 == 0 && E <= 128 && E != 96 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)Wr & 15) == 0) {
         const int grid = (N + 15) / 16;
-        if (E == 32) router_list_kernel<TIn, 1><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
-        else if (E == 64) router_list_kernel<TIn, 2><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
-        else router_list_kernel<TIn, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        if (E == 32) router_list_kernel<TIn, 1, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        else if (E == 64) router_list_kernel<TIn, 2, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, list, list_count);
+        else router_list_kernel<TIn, 4, 4><<<grid, R_WARPS * 32, 0, st>>>(x, Wr, br, N, C, E, k, logits, probs, top_idx, top_p, list, list_count);
         MGPT_LAUNCHED("router_list_kernel");
         return 0;
     }
